@@ -1,0 +1,31 @@
+// Internal launcher prototypes shared between the .cu files and the C-ABI layer.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+// Generic strided / batched int8 GEMM on dp4a.  Strides in elements.
+int a4c_launch_gemm_simt(const void* A, long long a_rs, long long a_cs, long long a_bs, const void* B,
+                         long long b_ks, long long b_ns, long long b_bs, const int32_t* bias, void* C,
+                         long long ldc, long long c_bs, long long batch, long long M, int K, int N, int shift,
+                         int rounding, int relu, int out_dtype, int a_unsigned, cudaStream_t stream);
+
+// tcgen05 / TMA / TMEM int8 GEMM: A [M,K] K-contiguous, Wt [N,K] K-contiguous.
+// cta_pair = 0: one CTA per 128x256 tile; 1: a CTA pair (cta_group::2) per 256x256 tile.
+int a4c_launch_dense_tc(const void* A, long long lda, const void* Wt, long long ldw, const int32_t* bias,
+                        void* Y, long long ldy, long long M, int K, int N, int shift, int rounding, int relu,
+                        int out_dtype, int a_unsigned, int cta_pair, int* status_word, cudaStream_t stream);
+// 0 if the tensor-core path can take this problem, else an A4C_ERR_* code saying why not.
+int a4c_dense_tc_supported(const void* A, long long lda, const void* Wt, long long ldw, const void* Y,
+                           long long ldy, long long M, int K, int N, int out_dtype);
+
+int a4c_launch_layernorm(const int8_t* x, long long ldx, const int16_t* gamma, const int16_t* beta,
+                         const int8_t* addend, long long ldadd, int8_t* out, long long ldo, long long rows,
+                         int cols, int eps_q0, int out_shift, int rounding, cudaStream_t stream);
+
+int a4c_launch_softmax(const int8_t* x, long long ldx, const void* addend, long long ldadd, void* out,
+                       long long ldo, long long rows, int cols, int mode, int B, int S, int Dmax, int inv_shift,
+                       int use_clb, int exp_kq, int out_dtype, cudaStream_t stream);
+
+int a4c_launch_add(const void* a, long long lda, const void* b, long long ldb, void* out, long long ldo,
+                   long long rows, long long cols, int shift, int rounding, int dtype, cudaStream_t stream);

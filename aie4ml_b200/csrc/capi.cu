@@ -1,0 +1,157 @@
+// extern "C" entry points declared in include/aie4ml_b200.h: argument validation on the host,
+// kernel selection, and the per-device status word the tensor-core kernels report into.
+#include <mutex>
+
+#include "../../include/aie4ml_b200.h"
+#include "a4c_common.cuh"
+#include "a4c_kernels.h"
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+std::mutex g_mutex;
+int* g_status[kMaxDevices] = {nullptr};
+thread_local const char* t_last_cuda_error = "no error";
+
+bool note(cudaError_t e) {
+    if (e != cudaSuccess) {
+        t_last_cuda_error = cudaGetErrorString(e);
+        return false;
+    }
+    return true;
+}
+
+// The status word of the current device, allocated (and zeroed) on first use.
+int* status_word() {
+    int dev = 0;
+    if (!note(cudaGetDevice(&dev)) || dev < 0 || dev >= kMaxDevices) return nullptr;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (g_status[dev] == nullptr) {
+        int* p = nullptr;
+        if (!note(cudaMalloc(&p, sizeof(int)))) return nullptr;
+        if (!note(cudaMemset(p, 0, sizeof(int)))) { cudaFree(p); return nullptr; }
+        g_status[dev] = p;
+    }
+    return g_status[dev];
+}
+
+inline bool valid_round(int r) { return r >= 0 && r < A4C_RND_COUNT; }
+inline bool valid_dtype(int d) { return d >= 0 && d <= 2; }
+
+int finish() {
+    const cudaError_t e = cudaPeekAtLastError();
+    return note(e) ? A4C_OK : A4C_ERR_CUDA;
+}
+
+}  // namespace
+
+extern "C" {
+
+int a4c_version(void) { return 100; }
+
+const char* a4c_error_string(int code) {
+    switch (code) {
+        case A4C_OK: return "ok";
+        case A4C_ERR_INVALID_ARG: return "invalid argument (shape, shift or enum value)";
+        case A4C_ERR_ALIGNMENT: return "pointer or pitch alignment not supported by the selected kernel";
+        case A4C_ERR_UNSUPPORTED: return "no kernel for this request";
+        case A4C_ERR_CUDA: return "a CUDA call failed (see a4c_last_cuda_error)";
+        case A4C_ERR_TOO_LARGE: return "problem exceeds a stated maximum";
+        case A4C_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+        default: return "unknown error code";
+    }
+}
+
+const char* a4c_last_cuda_error(void) { return t_last_cuda_error; }
+
+int a4c_device_status(int* status, void* stream) {
+    if (status == nullptr) return A4C_ERR_INVALID_ARG;
+    int* word = status_word();
+    if (word == nullptr) return A4C_ERR_CUDA;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!note(cudaStreamSynchronize(s))) return A4C_ERR_CUDA;
+    if (!note(cudaMemcpy(status, word, sizeof(int), cudaMemcpyDeviceToHost))) return A4C_ERR_CUDA;
+    if (*status != 0) {
+        cudaMemset(word, 0, sizeof(int));
+        return A4C_ERR_DEVICE_TIMEOUT;
+    }
+    return A4C_OK;
+}
+
+int a4c_dense_i8(const void* A, int64_t lda, const int8_t* Wt, int64_t ldw, const int32_t* bias, void* Y,
+                 int64_t ldy, int64_t M, int K, int N, int shift, int rounding, int relu, int out_dtype,
+                 int a_unsigned, int algo, void* stream) {
+    if (A == nullptr || Wt == nullptr || Y == nullptr) return A4C_ERR_INVALID_ARG;
+    if (M < 0 || K <= 0 || N <= 0 || lda < K || ldw < K || ldy < N) return A4C_ERR_INVALID_ARG;
+    if (shift < 0 || shift > 31 || !valid_round(rounding) || !valid_dtype(out_dtype)) return A4C_ERR_INVALID_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    int use = algo;
+    if (algo == A4C_ALGO_AUTO)
+        use = a4c_dense_tc_supported(A, lda, Wt, ldw, Y, ldy, M, K, N, out_dtype) == A4C_OK ? A4C_ALGO_TCGEN05
+                                                                                          : A4C_ALGO_SIMT;
+    int rc;
+    if (use == A4C_ALGO_TCGEN05) {
+        int* word = status_word();
+        if (word == nullptr) return A4C_ERR_CUDA;
+        rc = a4c_launch_dense_tc(A, lda, Wt, ldw, bias, Y, ldy, M, K, N, shift, rounding, relu, out_dtype,
+                                 a_unsigned, 0, word, s);
+    } else if (use == A4C_ALGO_SIMT) {
+        rc = a4c_launch_gemm_simt(A, lda, 1, 0, Wt, 1, ldw, 0, bias, Y, ldy, 0, 1, M, K, N, shift, rounding, relu,
+                                  out_dtype, a_unsigned, s);
+    } else {
+        return A4C_ERR_INVALID_ARG;
+    }
+    if (rc != A4C_OK) { if (rc == A4C_ERR_CUDA) note(cudaGetLastError()); return rc; }
+    return finish();
+}
+
+int a4c_bmm_i8(const void* A, int64_t lda, int64_t stride_a, const int8_t* B, int64_t ldb, int64_t stride_b,
+               void* C, int64_t ldc, int64_t stride_c, int64_t batch, int M, int K, int N, int trans_a,
+               int trans_b, int shift, int rounding, int out_dtype, int a_unsigned, void* stream) {
+    if (A == nullptr || B == nullptr || C == nullptr) return A4C_ERR_INVALID_ARG;
+    if (batch < 0 || M <= 0 || K <= 0 || N <= 0 || ldc < N) return A4C_ERR_INVALID_ARG;
+    if (lda < (trans_a ? M : K) || ldb < (trans_b ? K : N)) return A4C_ERR_INVALID_ARG;
+    if (shift < 0 || shift > 31 || !valid_round(rounding) || !valid_dtype(out_dtype)) return A4C_ERR_INVALID_ARG;
+    // A(m,k): row stride lda / column stride 1, swapped when the stored operand is transposed
+    const long long a_rs = trans_a ? 1 : lda, a_cs = trans_a ? lda : 1;
+    // B(k,n): stored [K,N] -> k stride ldb, n stride 1; stored [N,K] -> k stride 1, n stride ldb
+    const long long b_ks = trans_b ? 1 : ldb, b_ns = trans_b ? ldb : 1;
+    const int rc = a4c_launch_gemm_simt(A, a_rs, a_cs, stride_a, B, b_ks, b_ns, stride_b, nullptr, C, ldc, stride_c,
+                                        batch, M, K, N, shift, rounding, 0, out_dtype, a_unsigned,
+                                        (cudaStream_t)stream);
+    if (rc != A4C_OK) return rc;
+    return finish();
+}
+
+int a4c_layernorm_i8(const int8_t* x, int64_t ldx, const int16_t* gamma, const int16_t* beta,
+                     const int8_t* addend, int64_t ldadd, int8_t* out, int64_t ldo, int64_t rows, int cols,
+                     int eps_q0, int out_shift, int rounding, void* stream) {
+    if (x == nullptr || gamma == nullptr || beta == nullptr || out == nullptr) return A4C_ERR_INVALID_ARG;
+    if (ldx < cols || ldo < cols || (addend && ldadd < cols)) return A4C_ERR_INVALID_ARG;
+    const int rc = a4c_launch_layernorm(x, ldx, gamma, beta, addend, ldadd, out, ldo, rows, cols, eps_q0, out_shift,
+                                        rounding, (cudaStream_t)stream);
+    if (rc != A4C_OK) return rc;
+    return finish();
+}
+
+int a4c_softmax_i8(const int8_t* x, int64_t ldx, const void* addend, int64_t ldadd, void* out, int64_t ldo,
+                   int64_t rows, int cols, int mode, int B, int S, int Dmax, int inv_shift, int use_clb,
+                   int exp_kq, int out_dtype, void* stream) {
+    if (x == nullptr || out == nullptr) return A4C_ERR_INVALID_ARG;
+    if (ldx < cols || ldo < cols || (addend && ldadd < cols)) return A4C_ERR_INVALID_ARG;
+    const int rc = a4c_launch_softmax(x, ldx, addend, ldadd, out, ldo, rows, cols, mode, B, S, Dmax, inv_shift,
+                                      use_clb, exp_kq, out_dtype, (cudaStream_t)stream);
+    if (rc != A4C_OK) return rc;
+    return finish();
+}
+
+int a4c_add_sat(const void* a, int64_t lda, const void* b, int64_t ldb, void* out, int64_t ldo, int64_t rows,
+                int64_t cols, int shift, int rounding, int dtype, void* stream) {
+    if (a == nullptr || b == nullptr || out == nullptr) return A4C_ERR_INVALID_ARG;
+    if (lda < cols || ldb < cols || ldo < cols) return A4C_ERR_INVALID_ARG;
+    const int rc = a4c_launch_add(a, lda, b, ldb, out, ldo, rows, cols, shift, rounding, dtype, (cudaStream_t)stream);
+    if (rc != A4C_OK) return rc;
+    return finish();
+}
+
+}  // extern "C"

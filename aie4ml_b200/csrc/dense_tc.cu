@@ -1,0 +1,419 @@
+// int8 x int8 -> int32 Dense on the sm_100a tensor cores.
+//
+//   Y[m,n] = clamp(round_shift(sum_k A[m,k]*W[k,n] + bias[n], shift), lo, hi)      (lo = max(lo,0) with ReLU)
+//
+// which is dense_single::run of aie4ml (dense_bias_relu.cpp:67-166): int32 accumulation, bias as
+// the accumulator's initial value, SRS (rounding shift + saturation), ReLU after the saturation.
+//
+// Structure (one persistent CTA per SM, 192 threads, warp-specialised):
+//   warp 0     TMA producer: A tile [128 x 128B] and W^T tile [256 x 128B] per stage, 128-byte swizzle,
+//              4-stage shared-memory ring, mbarrier expect-tx completion
+//   warp 1     MMA issuer: one elected lane issues tcgen05.mma.kind::i8 (M=128, N=256, K=32), four per
+//              stage; tcgen05.commit releases the stage; accumulators live in TMEM, two of them
+//              (2 x 256 columns) so the epilogue of tile i overlaps the main loop of tile i+1
+//   warps 2-5  epilogue: tcgen05.ld the accumulator (lane = row), add bias, rounding shift, saturate,
+//              pack four int8 per word, 16-byte global stores
+// Every wait is bounded: when a wait gives up, the CTA records a code in the status word, stops
+// issuing work, lets what is in flight land, frees its TMEM and returns.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "a4c_common.cuh"
+#include "a4c_kernels.h"
+
+namespace {
+
+constexpr int BM = 128;          // rows of A per CTA tile
+constexpr int BN = 256;          // output features per tile (UMMA N)
+constexpr int BK = 128;          // K bytes per stage = one 128-byte swizzle row
+constexpr int UMMA_K = 32;       // K per tcgen05.mma for 8-bit operands
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK;                 // 16 KB
+constexpr int B_BYTES = BN * BK;                 // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;   // 48 KB
+constexpr int ACC_STAGES = 2;
+constexpr int TMEM_COLS = ACC_STAGES * BN;       // 512
+constexpr int NUM_THREADS = 192;
+constexpr int EPI_THREADS = 128;
+
+struct SmemTail {
+    int32_t bias[ACC_STAGES][BN];
+    uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t tmem_full[ACC_STAGES];
+    uint64_t tmem_empty[ACC_STAGES];
+    uint32_t tmem_base;
+    volatile int abort_flag;
+};
+constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + sizeof(SmemTail);
+
+// ---- PTX wrappers ------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// Bounded wait.  Returns false when the CTA is aborting (this wait or another one gave up).
+__device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                       int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = a4c_globaltimer();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 255u) == 0) {
+            if (*abort_flag) return false;
+            if (a4c_globaltimer() - t0 > A4C_SPIN_LIMIT_NS) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        :: "r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, 8-row
+// groups 1024 bytes apart.  Bits: [0,14) address>>4, [16,30) leading byte offset>>4 (unused for a
+// swizzled K-major tile whose K extent is one swizzle row), [32,46) stride byte offset>>4,
+// [46,48) descriptor version 1, [61,64) swizzle mode 2 = 128B.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor for kind::i8: [4,6) D format 2 = s32, [7,10) A format (0 = u8, 1 = s8),
+// [10,13) B format, bits 15/16 = 0 (both operands K-major), [17,23) N>>3, [24,29) M>>4.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool a_unsigned) {
+    return (2u << 4) | ((a_unsigned ? 0u : 1u) << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 :: "r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct TcArgs {
+    const int32_t* bias;
+    uint8_t* Y;
+    long long ldy;
+    long long M;
+    int K, N;
+    int num_m_tiles, num_n_tiles;
+    int shift, lo, hi;
+    uint32_t mask, c0;   // rounding constants (see round_shift_i32_t)
+    uint32_t idesc;
+    int* status;
+};
+
+template <int MODE>
+__device__ __forceinline__ int requant(int acc, const TcArgs& g) {
+    int v = acc;
+    if (MODE >= 0) v = round_shift_i32_t<MODE>(acc, g.shift, g.mask, g.c0);
+    return min(max(v, g.lo), g.hi);
+}
+
+// MODE = rounding token, or -1 when shift == 0 (no rounding step).
+template <int MODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+dense_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, TcArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    SmemTail* tail = reinterpret_cast<SmemTail*>(smem + (size_t)STAGES * STAGE_BYTES);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int num_tiles = g.num_m_tiles * g.num_n_tiles;
+    const int num_kb = (g.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&tail->full[s], 1); mbar_init(&tail->empty[s], 1); }
+        for (int s = 0; s < ACC_STAGES; ++s) { mbar_init(&tail->tmem_full[s], 1); mbar_init(&tail->tmem_empty[s], EPI_THREADS); }
+        tail->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // whole warp: allocate all 512 TMEM columns, publish the base address
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(smem_u32(&tail->tmem_base)), "r"((uint32_t)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tail->tmem_base;
+    volatile int* abort_flag = &tail->abort_flag;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                const int m0 = (tile / g.num_n_tiles) * BM;
+                const int n0 = (tile % g.num_n_tiles) * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(&tail->empty[stage], phase ^ 1u, abort_flag, g.status, 101);
+                    if (!ok) break;
+                    uint8_t* sa = smem + (size_t)stage * STAGE_BYTES;
+                    mbar_arrive_expect_tx(&tail->full[stage], STAGE_BYTES);
+                    tma_load_2d(sa, &tmap_a, &tail->full[stage], kb * BK, m0);
+                    tma_load_2d(sa + A_BYTES, &tmap_b, &tail->full[stage], kb * BK, n0);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            int stage = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                ok = mbar_wait(&tail->tmem_empty[acc], acc_phase ^ 1u, abort_flag, g.status, 102);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(&tail->full[stage], phase, abort_flag, g.status, 103);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + (size_t)stage * STAGE_BYTES);
+                    const uint64_t adesc = make_smem_desc(sa);
+                    const uint64_t bdesc = make_smem_desc(sa + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // advancing K inside the swizzle row: +32 bytes = +2 in the (address >> 4) field
+                        umma_i8(d_tmem, adesc + (uint64_t)(k * (UMMA_K >> 4)), bdesc + (uint64_t)(k * (UMMA_K >> 4)),
+                                g.idesc, (uint32_t)((kb | k) != 0));
+                    }
+                    umma_commit(&tail->empty[stage]);  // stage reusable once these MMAs have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                umma_commit(&tail->tmem_full[acc]);  // accumulator complete
+                if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1u; }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue (warps 2..5) ----------------
+        const int quad = warp & 3;           // TMEM lane quadrant this warp may read
+        const int et = threadIdx.x - 64;     // 0..127
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            const int m0 = (tile / g.num_n_tiles) * BM;
+            const int n0 = (tile % g.num_n_tiles) * BN;
+            // stage this tile's bias slice (zero where there is none)
+            for (int i = et; i < BN; i += EPI_THREADS) {
+                const int n = n0 + i;
+                tail->bias[acc][i] = (g.bias != nullptr && n < g.N) ? __ldg(g.bias + n) : 0;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (ok) ok = mbar_wait(&tail->tmem_full[acc], acc_phase, abort_flag, g.status, 104);
+            if (ok) {
+                tc_fence_after();
+                const long long row = (long long)m0 + quad * 32 + lane;
+                uint8_t* yrow = g.Y + row * g.ldy + n0;
+                const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    if (n0 + c * 32 >= g.N) break;   // warp-uniform
+                    uint32_t r[32];
+                    tmem_ld32(taddr + (uint32_t)(c * 32), r);
+                    uint32_t w[8];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        int o[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int col = c * 32 + q * 4 + e;
+                            const int v = (int)(r[q * 4 + e] + (uint32_t)tail->bias[acc][col]);
+                            o[e] = requant<MODE>(v, g);
+                        }
+                        w[q] = (uint32_t)(o[0] & 0xFF) | ((uint32_t)(o[1] & 0xFF) << 8) |
+                               ((uint32_t)(o[2] & 0xFF) << 16) | ((uint32_t)o[3] << 24);
+                    }
+                    if (row < g.M) {
+                        const int col0 = n0 + c * 32;
+                        if (col0 < g.N)
+                            *reinterpret_cast<uint4*>(yrow + c * 32) = make_uint4(w[0], w[1], w[2], w[3]);
+                        if (col0 + 16 < g.N)
+                            *reinterpret_cast<uint4*>(yrow + c * 32 + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(&tail->tmem_empty[acc]);
+            }
+            if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1u; }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    __syncthreads();
+    if (*abort_flag) {
+        // let TMA copies and MMAs that were already issued land before the CTA gives up its
+        // shared memory and TMEM
+        const uint64_t t0 = a4c_globaltimer();
+        while (a4c_globaltimer() - t0 < 2000000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// 2-D uint8 tensor map over a row-major [rows, cols] matrix with row pitch `ld` bytes,
+// box = [box_rows, 128 bytes], 128-byte swizzle, out-of-range elements read as zero.
+bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int MODE>
+cudaError_t launch_mode(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& g, int grid, cudaStream_t s) {
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(dense_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)SMEM_BYTES);
+    });
+    if (attr_err != cudaSuccess) return attr_err;
+    dense_tc_kernel<MODE><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(ma, mb, g);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+int a4c_dense_tc_supported(const void* A, long long lda, const void* Wt, long long ldw, const void* Y,
+                           long long ldy, long long M, int K, int N, int out_dtype) {
+    if (out_dtype != A4C_I8 && out_dtype != A4C_U8) return A4C_ERR_UNSUPPORTED;
+    if (N % 16 != 0 || K < 16) return A4C_ERR_UNSUPPORTED;
+    if (lda % 16 || ldw % 16 || ldy % 16) return A4C_ERR_ALIGNMENT;
+    if (((uintptr_t)A | (uintptr_t)Wt | (uintptr_t)Y) & 15u) return A4C_ERR_ALIGNMENT;
+    if (M > 2147483647LL - BM || lda < K || ldw < K) return A4C_ERR_INVALID_ARG;
+    const long long tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    if (tiles > 2147483647LL) return A4C_ERR_TOO_LARGE;
+    return A4C_OK;
+}
+
+int a4c_launch_dense_tc(const void* A, long long lda, const void* Wt, long long ldw, const int32_t* bias,
+                        void* Y, long long ldy, long long M, int K, int N, int shift, int rounding, int relu,
+                        int out_dtype, int a_unsigned, int cta_pair, int* status_word, cudaStream_t stream) {
+    if (cta_pair) return A4C_ERR_UNSUPPORTED;
+    const int sup = a4c_dense_tc_supported(A, lda, Wt, ldw, Y, ldy, M, K, N, out_dtype);
+    if (sup != A4C_OK) return sup;
+    if (M == 0) return A4C_OK;
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, A, M, K, lda, BM) || !make_map(&mb, Wt, N, K, ldw, BN)) return A4C_ERR_CUDA;
+    TcArgs g;
+    g.bias = bias; g.Y = (uint8_t*)Y; g.ldy = ldy; g.M = M; g.K = K; g.N = N;
+    g.num_m_tiles = (int)((M + BM - 1) / BM);
+    g.num_n_tiles = (N + BN - 1) / BN;
+    g.shift = shift;
+    dtype_range(out_dtype, g.lo, g.hi);
+    if (relu && g.lo < 0) g.lo = 0;
+    const RoundParams rp = make_round_params(shift, rounding);
+    g.mask = rp.mask; g.c0 = rp.c0;
+    g.idesc = make_idesc(BM, BN, a_unsigned != 0);
+    g.status = status_word;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long tiles = (long long)g.num_m_tiles * g.num_n_tiles;
+    const int grid = (int)(tiles < sms ? tiles : sms);
+    cudaError_t err;
+    if (shift == 0) err = launch_mode<-1>(ma, mb, g, grid, stream);
+    else switch (rounding) {
+        case A4C_RND_FLOOR: err = launch_mode<A4C_RND_FLOOR>(ma, mb, g, grid, stream); break;
+        case A4C_RND_CEIL: err = launch_mode<A4C_RND_CEIL>(ma, mb, g, grid, stream); break;
+        case A4C_RND_POSITIVE_INF: err = launch_mode<A4C_RND_POSITIVE_INF>(ma, mb, g, grid, stream); break;
+        case A4C_RND_NEGATIVE_INF: err = launch_mode<A4C_RND_NEGATIVE_INF>(ma, mb, g, grid, stream); break;
+        case A4C_RND_SYMMETRIC_INF: err = launch_mode<A4C_RND_SYMMETRIC_INF>(ma, mb, g, grid, stream); break;
+        case A4C_RND_SYMMETRIC_ZERO: err = launch_mode<A4C_RND_SYMMETRIC_ZERO>(ma, mb, g, grid, stream); break;
+        case A4C_RND_CONV_EVEN: err = launch_mode<A4C_RND_CONV_EVEN>(ma, mb, g, grid, stream); break;
+        case A4C_RND_CONV_ODD: err = launch_mode<A4C_RND_CONV_ODD>(ma, mb, g, grid, stream); break;
+        default: return A4C_ERR_INVALID_ARG;
+    }
+    return err == cudaSuccess ? A4C_OK : A4C_ERR_CUDA;
+}

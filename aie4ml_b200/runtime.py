@@ -1,0 +1,397 @@
+"""The CUDA runtime that replaces the reference's AIE emitter / placement / simulator tail.
+
+It walks the lowered IR (logical nodes + execution entries produced by Resolve / Pack) and
+builds a *plan*: one HBM buffer per stored tensor, zero-copy views for Split / Slice / Concat /
+fanout / transposed operands (the reference realises those as memory-tile DMA descriptors,
+``src/aie4ml/passes/fold_views.py:69-150`` and ``passes/transport/*``), and an ordered list of
+kernel launches through the C ABI.  A row op followed by an exact-type Add is fused into one
+launch when the intermediate has no other consumer (the analogue of the reference's "direct"
+neighbour transport, ``passes/transport/classify.py:25-49``).
+
+PyTorch is used only for device memory, streams and CUDA-graph capture.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from . import lib as _lib
+from .ir import BackendContext, input_tensor_for_role
+from .op_impls.precision import DTYPE_CODE, ROUNDING_CODE, resolve_exact_storage_dtype
+
+ESZ = {'int8': 1, 'uint8': 1, 'int16': 2, 'int32': 4}
+NP_DT = {'int8': np.int8, 'uint8': np.uint8, 'int16': np.int16, 'int32': np.int32}
+
+
+def _torch():
+    import torch
+
+    return torch
+
+
+@dataclass(frozen=True)
+class View:
+    """A strided window into a root buffer.  Offsets and strides in elements."""
+
+    root: str
+    offset: int
+    shape: Tuple[int, ...]
+    strides: Tuple[int, ...]
+    fmt: str
+
+    @property
+    def esz(self) -> int:
+        return ESZ[self.fmt]
+
+
+def padded_pitch(cols: int, esz: int) -> int:
+    """Row pitch in elements so that every row starts on a 16-byte boundary (TMA and 128-bit
+    accesses need that; e.g. a 5- or 10-wide int8 output gets pitch 16)."""
+    return (cols * esz + 15) // 16 * 16 // esz
+
+
+def contiguous_strides(shape: Sequence[int], esz: int) -> Tuple[int, ...]:
+    if not shape:
+        return ()
+    strides = [1] * len(shape)
+    pitch = padded_pitch(int(shape[-1]), esz)
+    acc = pitch
+    for i in range(len(shape) - 2, -1, -1):
+        strides[i] = acc
+        acc *= int(shape[i])
+    return tuple(strides)
+
+
+def collapse_2d(view: View, what: str) -> Tuple[int, int, int, int]:
+    """(element offset, rows, cols, pitch) of a view whose leading axes fold into rows."""
+    shape, strides = view.shape, view.strides
+    if strides[-1] != 1:
+        raise NotImplementedError(f'{what}: last axis must be contiguous.')
+    cols = int(shape[-1])
+    if len(shape) == 1:
+        return view.offset, 1, cols, cols
+    lead = [(int(s), int(st)) for s, st in zip(shape[:-1], strides[:-1]) if int(s) != 1]
+    if not lead:
+        return view.offset, 1, cols, max(cols, int(strides[-2]))
+    for (_, st_outer), (s_inner, st_inner) in zip(lead[:-1], lead[1:]):
+        if st_outer != st_inner * s_inner:
+            raise NotImplementedError(f'{what}: leading axes of the view do not fold into uniform rows '
+                                      f'(shape {shape}, strides {strides}).')
+    rows = 1
+    for s, _ in lead:
+        rows *= s
+    return view.offset, rows, cols, lead[-1][1]
+
+
+def collapse_batched(view: View, what: str) -> Tuple[int, int, int, int, int, int]:
+    """(offset, batch, rows, cols, pitch, batch stride) of a stack of matrices."""
+    shape, strides = view.shape, view.strides
+    if len(shape) < 2 or strides[-1] != 1:
+        raise NotImplementedError(f'{what}: expected a stack of row-major matrices.')
+    rows, cols, pitch = int(shape[-2]), int(shape[-1]), int(strides[-2])
+    lead = [(int(s), int(st)) for s, st in zip(shape[:-2], strides[:-2]) if int(s) != 1]
+    if not lead:
+        return view.offset, 1, rows, cols, pitch, 0
+    for (_, st_outer), (s_inner, st_inner) in zip(lead[:-1], lead[1:]):
+        if st_outer != st_inner * s_inner:
+            raise NotImplementedError(f'{what}: batch axes of the view do not fold into one stride '
+                                      f'(shape {shape}, strides {strides}).')
+    batch = 1
+    for s, _ in lead:
+        batch *= s
+    return view.offset, batch, rows, cols, pitch, lead[-1][1]
+
+
+class Plan:
+    """Buffers, views, device constants and the launch list of one lowered model."""
+
+    def __init__(self, ctx: BackendContext, device: Optional[str] = None, fuse_rowop_add: bool = True,
+                 dense_algo: int = _lib.ALGO_AUTO):
+        torch = _torch()
+        self.ctx = ctx
+        self.lib = _lib.load()
+        if not torch.cuda.is_available():
+            raise RuntimeError('aie4ml_b200 executes on a CUDA device only; no GPU is visible and there is no '
+                               'CPU execution path.')
+        self.device = torch.device(device or f'cuda:{torch.cuda.current_device()}')
+        self.dense_algo = int(dense_algo)
+        graph = ctx.ir.logical
+        self.graph = graph
+
+        # 1. storage format of every activation tensor
+        self.fmt: Dict[str, str] = {}
+        for name, t in graph.tensors.items():
+            if t.is_parameter:
+                continue
+            self.fmt[name] = resolve_exact_storage_dtype(t.precision, namespace='tensor', layer_name=name).format
+            if self.fmt[name] not in ('int8', 'uint8', 'int16'):
+                raise NotImplementedError(f'{name}: activation format {self.fmt[name]!r} has no kernel.')
+
+        # 2. aliases introduced by view placeholders
+        self.alias: Dict[str, Tuple[str, int, int]] = {}
+        for node in graph.nodes:
+            if not node.is_placeholder:
+                continue
+            if 'concat_view' in node.traits:
+                data = node.traits['concat_view'].data
+                for piece in data['slices']:
+                    self._add_alias(piece['input'], data['output'], int(data['axis']), int(piece['start']), node.name)
+            elif 'slice_view' in node.traits:
+                data = node.traits['slice_view'].data
+                for piece in data['slices']:
+                    self._add_alias(piece['output'], data['source'], int(data['axis']), int(piece['start']), node.name)
+            else:
+                raise NotImplementedError(f'{node.name}: placeholder without a view trait.')
+
+        # 3. logical op list (dicts), fusion, then roots and views
+        self.ops: List[Dict[str, Any]] = []
+        self.params_np: Dict[str, np.ndarray] = {}
+        for node in graph.nodes:
+            if node.is_placeholder:
+                continue
+            inst = ctx.ir.execution.get(node.name)
+            if inst is None:
+                raise RuntimeError(f'{node.name}: not resolved; run the pass pipeline first.')
+            op = inst.variant.plan_op(inst)
+            if op['kind'] == 'dense':
+                self.params_np[op['weight']] = inst.artifacts['packed_weights']
+                if op['bias']:
+                    self.params_np[op['bias']] = inst.artifacts['packed_bias']
+            elif op['kind'] == 'layer_norm':
+                self.params_np[op['gamma']] = inst.artifacts['packed_gamma']
+                self.params_np[op['beta']] = inst.artifacts['packed_beta']
+            elif op['kind'] == 'matmul':
+                if input_tensor_for_role(node, 'rhs').is_parameter:
+                    raise NotImplementedError(f'{node.name}: a constant RHS of rank > 2 has no kernel; '
+                                              'express it as dense.')
+            self.ops.append(op)
+        self.fused: List[str] = []
+        if fuse_rowop_add:
+            self._fuse_rowop_add()
+
+        self.views: Dict[str, View] = {}
+        self.buffers: Dict[str, Any] = {}
+        live = set(graph.input_tensor_names) | set(graph.output_tensor_names)
+        for op in self.ops:
+            for key in ('lhs', 'rhs', 'out', 'addend'):
+                if op.get(key):
+                    live.add(op[key])
+        for name in sorted(live):
+            self._view(name)
+
+        # 4. device constants
+        self.params: Dict[str, Any] = {}
+        for key, arr in self.params_np.items():
+            self.params[key] = torch.from_numpy(np.ascontiguousarray(arr)).to(self.device)
+
+        # 5. launches
+        self.launches: List[Tuple[Callable, tuple]] = []
+        for op in self.ops:
+            self.launches.append(self._compile(op))
+        self.graph_exec = None
+
+    # ---- views ---------------------------------------------------------------------------------
+    def _add_alias(self, child: str, parent: str, axis: int, start: int, node_name: str) -> None:
+        if child in self.alias:
+            raise NotImplementedError(f'{node_name}: tensor {child!r} would need two storage locations '
+                                      '(chained or overlapping view ops); insert a copy in the model.')
+        self.alias[child] = (parent, axis, start)
+
+    def _view(self, name: str) -> View:
+        if name in self.views:
+            return self.views[name]
+        torch = _torch()
+        t = self.graph.tensors[name]
+        fmt = self.fmt[name]
+        shape = tuple(int(s) for s in t.shape)
+        if name in self.alias:
+            parent, axis, start = self.alias[name]
+            pv = self._view(parent)
+            if pv.fmt != fmt:
+                raise ValueError(f'{name}: view of {parent!r} changes the storage type ({pv.fmt} -> {fmt}).')
+            view = View(root=pv.root, offset=pv.offset + start * pv.strides[axis], shape=shape, strides=pv.strides,
+                        fmt=fmt)
+        else:
+            strides = contiguous_strides(shape, ESZ[fmt])
+            total = (shape[0] * strides[0]) if shape else 1
+            self.buffers[name] = torch.zeros(total * ESZ[fmt], dtype=torch.uint8, device=self.device)
+            view = View(root=name, offset=0, shape=shape, strides=strides, fmt=fmt)
+        self.views[name] = view
+        return view
+
+    def ptr(self, view: View, offset: Optional[int] = None) -> int:
+        off = view.offset if offset is None else offset
+        return self.buffers[view.root].data_ptr() + off * view.esz
+
+    def tensor_of(self, name: str):
+        """A torch tensor (strided) over the view's storage, typed by the tensor's format."""
+        torch = _torch()
+        v = self._view(name)
+        dt = {'int8': torch.int8, 'uint8': torch.uint8, 'int16': torch.int16}[v.fmt]
+        base = self.buffers[v.root].view(dt)
+        return base.as_strided(v.shape, v.strides, v.offset)
+
+    # ---- fusion --------------------------------------------------------------------------------
+    def _fuse_rowop_add(self) -> None:
+        """layer_norm/softmax -> add (same type, shift 0) becomes one launch when the row op's output
+        feeds nothing else, is not a graph output or a view, and the other addend already exists."""
+        graph = self.graph
+        produced_at = {op['out']: i for i, op in enumerate(self.ops)}
+        aliased = set(self.alias) | {p for p, _, _ in self.alias.values()}
+        drop = set()
+        for i, op in enumerate(self.ops):
+            if op['kind'] != 'add' or op['shift'] != 0:
+                continue
+            for mid_key, other_key in (('lhs', 'rhs'), ('rhs', 'lhs')):
+                mid, other = op[mid_key], op[other_key]
+                j = produced_at.get(mid)
+                if j is None or j in drop:
+                    continue
+                prod = self.ops[j]
+                if prod['kind'] not in ('layer_norm', 'softmax') or prod.get('addend'):
+                    continue
+                t = graph.tensors[mid]
+                if len(t.consumers) != 1 or mid in graph.output_tensor_names or mid in aliased:
+                    continue
+                if produced_at.get(other, -1) > j:  # addend must exist when the row op runs
+                    continue
+                if self.fmt[mid] != self.fmt[op['out']] or self.fmt[other] != self.fmt[mid]:
+                    continue
+                prod['addend'] = other
+                prod['fused_out'] = op['out']
+                self.fused.append(f"{prod['name']}+{op['name']}")
+                drop.add(i)
+                break
+        if drop:
+            for op in self.ops:
+                if op.get('fused_out'):
+                    op['out'] = op.pop('fused_out')
+            self.ops = [op for i, op in enumerate(self.ops) if i not in drop]
+
+    # ---- launch compilation --------------------------------------------------------------------
+    def _compile(self, op: Dict[str, Any]) -> Tuple[Callable, tuple]:
+        kind, name = op['kind'], op['name']
+        L = self.lib
+        if kind == 'dense':
+            if op['transpose_lhs']:
+                raise NotImplementedError(f'{name}: dense over a transposed input view has no kernel yet.')
+            a, y = self._view(op['lhs']), self._view(op['out'])
+            a_off, M, K, lda = collapse_2d(a, f'{name}: input')
+            y_off, My, N, ldy = collapse_2d(y, f'{name}: output')
+            if (M, K, N) != (My, op['K'], op['N']):
+                raise ValueError(f'{name}: shape mismatch between views (M={M}/{My}, K={K}/{op["K"]}, N={N}/{op["N"]}).')
+            w = self.params[op['weight']]
+            bias = self.params[op['bias']] if op['bias'] else None
+            args = (self.ptr(a, a_off), lda, w.data_ptr(), int(w.shape[1]), bias.data_ptr() if bias is not None else None,
+                    self.ptr(y, y_off), ldy, M, K, N, op['shift'], ROUNDING_CODE[op['rounding']], int(op['relu']),
+                    DTYPE_CODE[op['out_dtype']], int(op['lhs_dtype'] == 'uint8'), self.dense_algo)
+            return L.a4c_dense_i8, args
+        if kind == 'matmul':
+            a, b, c = self._view(op['lhs']), self._view(op['rhs']), self._view(op['out'])
+            a_off, ba, ar, ac, lda, sa = collapse_batched(a, f'{name}: lhs')
+            b_off, bb, br, bc, ldb, sb = collapse_batched(b, f'{name}: rhs')
+            c_off, bc_, M, N, ldc, sc = collapse_batched(c, f'{name}: output')
+            Ka = ar if op['transpose_lhs'] else ac
+            Ma = ac if op['transpose_lhs'] else ar
+            Kb = bc if op['transpose_rhs'] else br
+            Nb = br if op['transpose_rhs'] else bc
+            if Ma != M or Nb != N or Ka != Kb:
+                raise ValueError(f'{name}: operand shapes do not contract (A {a.shape}, B {b.shape}, C {c.shape}).')
+            if ba != bc_ or bb not in (1, bc_):
+                raise ValueError(f'{name}: batch extents differ (A {ba}, B {bb}, C {bc_}).')
+            if bb == 1:
+                sb = 0
+            args = (self.ptr(a, a_off), lda, sa, self.ptr(b, b_off), ldb, sb, self.ptr(c, c_off), ldc, sc, bc_, M, Ka, N,
+                    int(op['transpose_lhs']), int(op['transpose_rhs']), op['shift'], ROUNDING_CODE[op['rounding']],
+                    DTYPE_CODE[op['out_dtype']], int(op['lhs_dtype'] == 'uint8'))
+            return L.a4c_bmm_i8, args
+        if kind in ('layer_norm', 'softmax', 'add'):
+            x, y = self._view(op['lhs']), self._view(op['out'])
+            x_off, rows, cols, ldx = collapse_2d(x, f'{name}: input')
+            y_off, rows_y, cols_y, ldy = collapse_2d(y, f'{name}: output')
+            if (rows, cols) != (rows_y, cols_y):
+                raise ValueError(f'{name}: input and output views differ in shape.')
+            add_ptr, ldadd = None, 0
+            other = op.get('addend') if kind != 'add' else op['rhs']
+            if other:
+                o = self._view(other)
+                o_off, ro, co, ldadd = collapse_2d(o, f'{name}: addend')
+                if (ro, co) != (rows, cols):
+                    raise ValueError(f'{name}: addend shape differs from the output.')
+                add_ptr = self.ptr(o, o_off)
+            if kind == 'layer_norm':
+                args = (self.ptr(x, x_off), ldx, self.params[op['gamma']].data_ptr(), self.params[op['beta']].data_ptr(),
+                        add_ptr, ldadd, self.ptr(y, y_off), ldy, rows, cols, op['eps_q0'], op['out_shift'],
+                        ROUNDING_CODE[op['rounding']])
+                return L.a4c_layernorm_i8, args
+            if kind == 'softmax':
+                args = (self.ptr(x, x_off), ldx, add_ptr, ldadd, self.ptr(y, y_off), ldy, rows, cols,
+                        0 if op['approximation'] == 'hccs' else 1, op['B'], op['S'], op['Dmax'], op['inv_shift'],
+                        int(op['use_clb']), op['exp_kq'], DTYPE_CODE[op['out_dtype']])
+                return L.a4c_softmax_i8, args
+            args = (self.ptr(x, x_off), ldx, add_ptr, ldadd, self.ptr(y, y_off), ldy, rows, cols, op['shift'],
+                    ROUNDING_CODE[op['rounding']], DTYPE_CODE[op['out_dtype']])
+            return L.a4c_add_sat, args
+        raise NotImplementedError(f'{name}: no launch rule for op kind {kind!r}.')
+
+    # ---- execution -----------------------------------------------------------------------------
+    def launch_all(self, stream_handle: int) -> None:
+        for (fn, args), op in zip(self.launches, self.ops):
+            rc = fn(*args, stream_handle)
+            if rc != 0:
+                _lib.check(rc, f"{op['name']} ({op['kind']})")
+
+    def run(self, use_graph: bool = True) -> None:
+        """Execute every launch on the current stream (replaying a captured CUDA graph once one exists)."""
+        torch = _torch()
+        if use_graph and self.graph_exec is not None:
+            self.graph_exec.replay()
+            return
+        self.launch_all(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def capture(self) -> None:
+        """Capture the launch list into a CUDA graph (after one eager warm-up run)."""
+        torch = _torch()
+        self.run(use_graph=False)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.launch_all(torch.cuda.current_stream(self.device).cuda_stream)
+        self.graph_exec = g
+
+    def check_status(self) -> None:
+        torch = _torch()
+        _lib.device_status(torch.cuda.current_stream(self.device).cuda_stream)
+
+    # ---- export --------------------------------------------------------------------------------
+    def export(self) -> Dict[str, Any]:
+        """The lowered plan as plain data: what the CPU oracle evaluates and what a dump records."""
+        ops: List[Dict[str, Any]] = []
+        params: Dict[str, np.ndarray] = {}
+        for node in self.graph.nodes:
+            if node.is_placeholder:
+                if 'slice_view' in node.traits:
+                    d = node.traits['slice_view'].data
+                    ops.append({'kind': 'slice', 'name': node.name, 'source': d['source'], 'axis': d['axis'],
+                                'slices': [dict(s) for s in d['slices']]})
+                else:
+                    d = node.traits['concat_view'].data
+                    ops.append({'kind': 'concat', 'name': node.name, 'out': d['output'], 'axis': d['axis'],
+                                'inputs': [s['input'] for s in d['slices']]})
+                continue
+            inst = self.ctx.ir.execution.get(node.name)
+            op = inst.variant.plan_op(inst)
+            if op['kind'] == 'dense':
+                params[op['weight']] = inst.artifacts['weights_kn']
+                if op['bias']:
+                    params[op['bias']] = inst.artifacts['packed_bias']
+            elif op['kind'] == 'layer_norm':
+                params[op['gamma']] = inst.artifacts['packed_gamma']
+                params[op['beta']] = inst.artifacts['packed_beta']
+            ops.append(op)
+        return {'inputs': list(self.graph.input_tensor_names), 'outputs': list(self.graph.output_tensor_names),
+                'ops': ops, 'params': params, 'fused': list(self.fused),
+                'formats': dict(self.fmt)}

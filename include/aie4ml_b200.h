@@ -1,0 +1,138 @@
+/*
+ * aie4ml_b200 -- C ABI of the sm_100a kernels that execute aie4ml's lowered, quantized operators.
+ *
+ * This is the drop-in boundary under the Python runtime.  The reference project (aie4ml) has no FFI
+ * for this path: it generates a Vitis C++ project and runs it through `make`
+ * (src/aie4ml/model.py:82-147, src/aie4ml/simulation.py:337-341).  Each entry point below therefore
+ * cites the reference KERNEL whose arithmetic it replaces and the reference parameter block that
+ * defines its arguments.
+ *
+ * Conventions
+ *   - every pointer is DEVICE memory owned by the caller (except where a name ends in _host);
+ *   - pitches (ld*) and strides are in ELEMENTS of the tensor they describe;
+ *   - calls are asynchronous on `stream` (a cudaStream_t passed as void*; NULL = default stream);
+ *   - the return value is 0 or a negative A4C_ERR_* code; invalid shapes / alignment are rejected
+ *     on the host before anything is launched; nothing here calls exit() or traps;
+ *   - rounding codes: 0 floor, 1 ceil, 2 positive_inf (round half up), 3 negative_inf,
+ *     4 symmetric_inf (half away from zero), 5 symmetric_zero (half toward zero), 6 conv_even,
+ *     7 conv_odd -- the AIE-API rounding tokens the reference's resolver emits
+ *     (src/aie4ml/op_impls/utils/precision.py:13-21) plus the ones it does not;
+ *   - dtype codes: 0 int8, 1 uint8, 2 int16;
+ *   - saturation is always on, as in every reference kernel
+ *     (templates/firmware/variants/dense_bias_relu/parameters.h.jinja:26-29).
+ */
+#ifndef AIE4ML_B200_H
+#define AIE4ML_B200_H
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define A4C_API __attribute__((visibility("default")))
+#else
+#define A4C_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define A4C_OK 0
+#define A4C_ERR_INVALID_ARG (-1)
+#define A4C_ERR_ALIGNMENT (-2)
+#define A4C_ERR_UNSUPPORTED (-3)
+#define A4C_ERR_CUDA (-4)
+#define A4C_ERR_TOO_LARGE (-5)
+#define A4C_ERR_DEVICE_TIMEOUT (-6)
+
+/* GEMM kernel selection for a4c_dense_i8 */
+#define A4C_ALGO_AUTO 0
+#define A4C_ALGO_SIMT 1      /* dp4a tiles, any shape / stride */
+#define A4C_ALGO_TCGEN05 2   /* tcgen05 + TMA + TMEM, one CTA per 128x256 tile */
+
+/* Library version (major*10000 + minor*100 + patch). */
+A4C_API int a4c_version(void);
+
+/* Human-readable text for an A4C_ERR_* code (static storage). */
+A4C_API const char* a4c_error_string(int code);
+
+/* Text of the last CUDA runtime error seen by this library on the calling thread (static storage). */
+A4C_API const char* a4c_last_cuda_error(void);
+
+/*
+ * Reads (and clears) the current device's kernel status word after synchronising `stream`.
+ * 0 = every bounded device-side wait completed; otherwise the code of the first wait that gave up
+ * (101 producer/empty slot, 102 MMA/accumulator free, 103 MMA/operands landed, 104 epilogue/accumulator
+ * ready).  Returns A4C_OK, or A4C_ERR_DEVICE_TIMEOUT when *status != 0, or A4C_ERR_CUDA.
+ */
+A4C_API int a4c_device_status(int* status, void* stream);
+
+/*
+ * Dense: Y = relu?( saturate( round_shift( A . W + bias, shift ) ) ), int8 x int8 -> int32 accumulate.
+ * Replaces dense_single/first/middle/last::run
+ * (src/aie4ml/templates/nnet_utils/dense_bias_relu/dense_bias_relu.cpp:67-430); arguments are the
+ * fields of its parameter block (templates/firmware/variants/dense_bias_relu/parameters.h.jinja:1-31:
+ * SHIFT, ROUNDING, USE_BIAS, USE_RELU, data_t/result_t).
+ *   A   [M, K]  int8 (or uint8 when a_unsigned), K contiguous, row pitch lda
+ *   Wt  [N, K]  int8, the weight matrix TRANSPOSED so K is contiguous, row pitch ldw
+ *   bias[N]     int32 at the accumulator's fixed point, or NULL
+ *   Y   [M, N]  out_dtype, row pitch ldy
+ * algo: A4C_ALGO_AUTO picks tcgen05 when its alignment rules hold (lda, ldw, ldy*elt multiples of 16
+ * bytes, 16-byte aligned bases, N multiple of 16, 8-bit output), else the SIMT kernel.
+ */
+A4C_API int a4c_dense_i8(const void* A, int64_t lda, const int8_t* Wt, int64_t ldw, const int32_t* bias, void* Y,
+                 int64_t ldy, int64_t M, int K, int N, int shift, int rounding, int relu, int out_dtype,
+                 int a_unsigned, int algo, void* stream);
+
+/*
+ * Batched dynamic MatMul: C_b = saturate( round_shift( op(A_b) . op(B_b), shift ) ), b = 0..batch-1.
+ * Replaces matmul_single/first/middle/last::run
+ * (src/aie4ml/templates/nnet_utils/matmul/matmul.cpp:32-390; TRANSPOSE_A/B :60-77) applied once per
+ * leading index -- the rank-2 contract of op_impls/families/matmul/resolver.py:440-463, batched.
+ *   stored A_b: [M, K] (or [K, M] when trans_a), pitch lda, batch stride stride_a; uint8 when a_unsigned
+ *   stored B_b: [K, N] (or [N, K] when trans_b), pitch ldb, batch stride stride_b; always int8
+ *   C_b: [M, N] out_dtype, pitch ldc, batch stride stride_c
+ */
+A4C_API int a4c_bmm_i8(const void* A, int64_t lda, int64_t stride_a, const int8_t* B, int64_t ldb, int64_t stride_b,
+               void* C, int64_t ldc, int64_t stride_c, int64_t batch, int M, int K, int N, int trans_a,
+               int trans_b, int shift, int rounding, int out_dtype, int a_unsigned, void* stream);
+
+/*
+ * Integer LayerNorm over rows of `cols` (a power of two) int8 values, int8 out.
+ * Replaces layernorm_i8::run / layernorm_i8_tiled::run
+ * (src/aie4ml/templates/nnet_utils/layer_norm/layer_norm.cpp:15-231); arguments follow
+ * templates/firmware/variants/layer_norm/parameters.h.jinja:1-24 (EPS_Q0, OUT_SHIFT, ROUNDING;
+ * GAMMA_SHIFT is the constant 7).  gamma is int16 Q7, beta int16 Q15, both [cols].
+ * addend (or NULL): an int8 tensor shaped like the output; when given, the kernel stores
+ * saturate(layernorm(x) + addend) -- the exact-type Add of elementwise_add.cpp:12-37 fused in.
+ */
+A4C_API int a4c_layernorm_i8(const int8_t* x, int64_t ldx, const int16_t* gamma, const int16_t* beta,
+                     const int8_t* addend, int64_t ldadd, int8_t* out, int64_t ldo, int64_t rows, int cols,
+                     int eps_q0, int out_shift, int rounding, void* stream);
+
+/*
+ * Quantized Softmax over rows of int8, output uint8 (dtype 1) or int16 (dtype 2).
+ * mode 0 = HCCS clipped-linear surrogate: replaces softmax_i8::softmax_row / softmax_i8_tiled::run
+ *          (src/aie4ml/templates/nnet_utils/softmax/softmax.cpp:20-88, 159-239); B, S, Dmax, inv_shift,
+ *          use_clb as in templates/firmware/variants/softmax/parameters.h.jinja:1-44.
+ * mode 1 = accurate integer exp: replaces softmax_exp_i8::run / softmax_exp_i8_tiled::run + exp_score16
+ *          (softmax.cpp:252-384); exp_kq = EXP_KQ in [1, 128].
+ * addend (or NULL): tensor of the OUTPUT dtype; when given the kernel stores saturate(softmax(x) + addend).
+ */
+A4C_API int a4c_softmax_i8(const int8_t* x, int64_t ldx, const void* addend, int64_t ldadd, void* out, int64_t ldo,
+                   int64_t rows, int cols, int mode, int B, int S, int Dmax, int inv_shift, int use_clb,
+                   int exp_kq, int out_dtype, void* stream);
+
+/*
+ * Elementwise out = saturate( round_shift( a + b, shift ) ) over [rows, cols] tensors of one dtype.
+ * Replaces elementwise_add_kernel::run
+ * (src/aie4ml/templates/nnet_utils/elementwise_add/elementwise_add.cpp:12-37; SHIFT, ROUNDING from
+ * templates/firmware/variants/elementwise_add/parameters.h.jinja:1-20).
+ */
+A4C_API int a4c_add_sat(const void* a, int64_t lda, const void* b, int64_t ldb, void* out, int64_t ldo, int64_t rows,
+                int64_t cols, int shift, int rounding, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* AIE4ML_B200_H */
