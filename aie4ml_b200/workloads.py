@@ -20,12 +20,18 @@ Inputs = Dict[str, np.ndarray]
 ROUNDING_BY_NAME = {'half_up': 'RND_HALF_UP', 'conv_even': 'RND_CONV', 'floor': 'TRN', 'sym_inf': 'RND'}
 
 
-def _codes(rng, lo: int, hi: int, shape) -> np.ndarray:
-    return rng.integers(lo, hi + 1, size=shape, dtype=np.int64)
+def _codes(rng, lo: int, hi: int, shape, dtype=np.int64) -> np.ndarray:
+    return rng.integers(lo, hi + 1, size=shape, dtype=dtype)
 
 
 def _gauss_i8(rng, sigma: float, shape) -> np.ndarray:
-    return np.clip(np.rint(rng.normal(0.0, sigma, size=shape)), -128, 127).astype(np.int8)
+    out = np.empty(shape, dtype=np.int8)
+    flat = out.reshape(-1)
+    step = 1 << 24  # draw in slabs: a 2^30-element float64 normal array would need 8 GiB
+    for i in range(0, flat.size, step):
+        n = min(step, flat.size - i)
+        flat[i:i + n] = np.clip(np.rint(rng.standard_normal(n, dtype=np.float32) * np.float32(sigma)), -128, 127)
+    return out
 
 
 def _dense(b: GraphBuilder, rng, name: str, x: str, k: int, n: int, *, in_frac: int, out_frac: int, shift: int,
@@ -53,7 +59,7 @@ def mlp_cfg1(batch: int = 1024, rounding: str = 'half_up', seed: int = 0) -> Tup
         cur = _dense(b, rng, f'fc{i}', cur, dims[i], dims[i + 1], in_frac=4, out_frac=4, shift=7, w_lim=127,
                      bias_lim=1 << 12, relu=i < 3, rnd=rnd)
     b.output(cur)
-    return b, {'x': _codes(rng, -128, 127, (batch, 16)).astype(np.int8)}
+    return b, {'x': _codes(rng, -128, 127, (batch, 16), np.int8)}
 
 
 def dense_cfg2(M: int, K: int, N: int, rounding: str = 'half_up', seed: int = 1) -> Tuple[GraphBuilder, Inputs]:
@@ -65,7 +71,7 @@ def dense_cfg2(M: int, K: int, N: int, rounding: str = 'half_up', seed: int = 1)
     y = _dense(b, rng, 'fc', x, K, N, in_frac=4, out_frac=4, shift=10, w_lim=127, bias_lim=1 << 16, relu=True, rnd=rnd,
                w_lo=-128)
     b.output(y)
-    return b, {'x': _codes(rng, -128, 127, (M, K)).astype(np.int8)}
+    return b, {'x': _codes(rng, -128, 127, (M, K), np.int8)}
 
 
 def encoder_cfg3(batch: int = 4096, softmax: str = 'exp', rounding: str = 'half_up', seed: int = 2,
@@ -137,11 +143,11 @@ def rowops_cfg4(rows: int = 1 << 20, cols: int = 1024, op: str = 'layer_norm', r
     if op == 'layer_norm':
         out_p = intent(8, 4, rounding=rnd)
         mid = b.layer_norm('ln', x, gamma, beta, out_p, eps_q0=1)
-        inputs['r'] = _codes(rng, -128, 127, (rows, cols)).astype(np.int8)
+        inputs['r'] = _codes(rng, -128, 127, (rows, cols), np.int8)
     elif op in ('softmax_exp', 'softmax_hccs'):
         out_p = intent(8, 8, signed=False, rounding=rnd)
         mid = b.softmax('sm', x, out_p)
-        inputs['r'] = _codes(rng, 0, 255, (rows, cols)).astype(np.uint8)
+        inputs['r'] = _codes(rng, 0, 255, (rows, cols), np.uint8)
     else:
         raise ValueError(f'unknown row op {op!r}')
     r = b.input('r', (rows, cols), out_p)
@@ -171,4 +177,4 @@ def wide_mlp_cfg5(batch: int = 262144, rounding: str = 'half_up', seed: int = 4)
     y = _dense(b, rng, 'head1', h, 1024, 10, in_frac=4, out_frac=4, shift=9, w_lim=127, bias_lim=1 << 14, relu=False,
                rnd=rnd)
     b.output(y)
-    return b, {'x': _codes(rng, -128, 127, (batch, 512)).astype(np.int8)}
+    return b, {'x': _codes(rng, -128, 127, (batch, 512), np.int8)}

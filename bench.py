@@ -1,0 +1,407 @@
+#!/usr/bin/env python
+"""Benchmark: int8 inferences/s of the lowered-graph hot path on B200, with roofline and CPU baseline.
+
+    python bench.py --gpus N --steps K --warmup W [--workload NAME] [--impl reference]
+
+One step = one pass of the workload's lowered graph over one batch of seeded synthetic input.
+The default workload is the single int8 Dense of the Dense sweep at its largest point
+(M=131072, K=N=8192: requant shift 10, round-half-up, int8 saturation, fused bias + ReLU).
+With N > 1 GPUs every rank runs the same per-GPU batch on its own shard (weak scaling, no
+data-path collective) and rank 0 prints ONE JSON line.
+
+`value`   device-resident throughput (inputs already in HBM), whole job, max-over-ranks time.
+`e2e`     same metric through the model API with HOST (pinned) buffers: H2D of the inputs and D2H of
+          the outputs inside the timed region.
+`roofline` achieved / peak for the dominant kernel, timed live with CUDA events.
+`cpu_baseline` the C edition of the CPU oracle on a bounded sample of the same workload.
+`--impl reference` times that CPU implementation alone (the reference's own execution path is the
+          AMD Vitis simulator, which cannot run here) and prints the same line shape.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = ('dense', 'cfg1', 'cfg3_exp', 'cfg3_hccs', 'cfg4_ln', 'cfg4_sm_exp', 'cfg4_sm_hccs', 'cfg5')
+
+
+# ------------------------------------------------------------------------------------------------
+# workload table
+# ------------------------------------------------------------------------------------------------
+def build_workload(name: str, args):
+    """-> dict(builder, inputs, units, unit_name, desc, ops_per_unit, bytes_per_unit, bound)"""
+    from aie4ml_b200 import workloads as W
+
+    r = args.rounding
+    if name == 'dense':
+        M, K, N = args.m, args.k, args.n
+        b, inp = W.dense_cfg2(M, K, N, rounding=r)
+        return dict(builder=b, inputs=inp, units=M, desc=f'dense_cfg2 M={M} K={K} N={N} shift=10 relu bias {r}',
+                    ops_per_unit=2.0 * K * N, bytes_per_unit=K + N + (K * N + 4 * N) / M, bound='tensor',
+                    kernel='dense')
+    if name == 'cfg1':
+        b, inp = W.mlp_cfg1(args.batch or 1024, rounding=r)
+        return dict(builder=b, inputs=inp, units=args.batch or 1024, desc=f'mlp_cfg1 16-64-32-32-5 batch={args.batch or 1024} {r}',
+                    ops_per_unit=8512.0, bytes_per_unit=16 + 5, bound='hbm', kernel='dense')
+    if name in ('cfg3_exp', 'cfg3_hccs'):
+        batch = args.batch or 4096
+        b, inp = W.encoder_cfg3(batch, softmax=name.split('_')[1], rounding=r)
+        return dict(builder=b, inputs=inp, units=batch, desc=f'encoder_cfg3 {name[5:]} batch={batch} seq=128 d=256 h=4 ffn=1024 {r}',
+                    ops_per_unit=218103808.0, bytes_per_unit=2 * 128 * 256, bound='tensor', kernel='dense')
+    if name in ('cfg4_ln', 'cfg4_sm_exp', 'cfg4_sm_hccs'):
+        rows = args.batch or (1 << 20)
+        op = {'cfg4_ln': 'layer_norm', 'cfg4_sm_exp': 'softmax_exp', 'cfg4_sm_hccs': 'softmax_hccs'}[name]
+        b, inp = W.rowops_cfg4(rows, 1024, op, rounding=r)
+        return dict(builder=b, inputs=inp, units=rows, desc=f'rowops_cfg4 {op}+add rows={rows} cols=1024 {r}',
+                    ops_per_unit=0.0, bytes_per_unit=3 * 1024 + (4 * 1024 / rows if op == 'layer_norm' else 0),
+                    bound='hbm', kernel=op)
+    if name == 'cfg5':
+        batch = args.batch or 262144
+        b, inp = W.wide_mlp_cfg5(batch, rounding=r)
+        return dict(builder=b, inputs=inp, units=batch, desc=f'wide_mlp_cfg5 batch={batch} {r}',
+                    ops_per_unit=18894848.0, bytes_per_unit=512 + 10, bound='tensor', kernel='dense')
+    raise SystemExit(f'unknown workload {name!r}; choose from {WORKLOADS}')
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline (the oracle's C edition; the only place the benchmark executes oracle/)
+# ------------------------------------------------------------------------------------------------
+def load_cpu_oracle():
+    """Build the C oracle for this host's CPU (falls back to the portable in-tree build)."""
+    src = ROOT / 'oracle' / 'oracle_c.c'
+    out = Path('/tmp') / f'liboracle_native_{os.getpid()}.so'
+    try:
+        subprocess.run(['make', '-C', str(ROOT / 'oracle'), f'OUT={out}', 'ARCH=-march=native'], check=True,
+                       capture_output=True, timeout=120)
+        return ctypes.CDLL(str(out)), 'native'
+    except Exception:
+        so = ROOT / 'oracle' / 'liboracle.so'
+        if not so.exists():
+            subprocess.run(['make', '-C', str(ROOT / 'oracle')], check=True, capture_output=True)
+        return ctypes.CDLL(str(so)), 'x86-64-v3'
+
+
+def cpu_run_plan(lib, plan, inputs, rows: int):
+    """Run the exported plan on the first `rows` leading entries of each input with the C oracle.
+    Returns seconds spent inside the oracle calls."""
+    sys.path.insert(0, str(ROOT / 'tests'))
+    import oracle_c_api as C
+
+    env = {k: np.ascontiguousarray(v[:rows]) for k, v in inputs.items()}
+    params = plan['params']
+    elapsed = 0.0
+    for op in plan['ops']:
+        kind = op['kind']
+        t0 = time.perf_counter()
+        if kind == 'dense':
+            a = env[op['lhs']]
+            y = C.dense(lib, a.reshape(-1, a.shape[-1]), params[op['weight']], params[op['bias']] if op['bias'] else None,
+                        shift=op['shift'], tok=op['rounding'], relu=op['relu'], out_dtype=op['out_dtype'])
+            env[op['out']] = y.reshape(*a.shape[:-1], -1)
+        elif kind == 'matmul':
+            a, b = env[op['lhs']], env[op['rhs']]
+            env[op['out']] = C.bmm(lib, a, b, shift=op['shift'], tok=op['rounding'], trans_a=op['transpose_lhs'],
+                                   trans_b=op['transpose_rhs'], out_dtype=op['out_dtype'])
+        elif kind == 'add':
+            a = env[op['lhs']]
+            env[op['out']] = C.add(lib, a.reshape(-1, a.shape[-1]), env[op['rhs']].reshape(-1, a.shape[-1]),
+                                   shift=op['shift'], tok=op['rounding'], dtype=op['out_dtype']).reshape(a.shape)
+        elif kind == 'layer_norm':
+            a = env[op['lhs']]
+            env[op['out']] = C.layer_norm(lib, a.reshape(-1, a.shape[-1]), params[op['gamma']], params[op['beta']],
+                                          eps_q0=op['eps_q0'], out_shift=op['out_shift'], tok=op['rounding']).reshape(a.shape)
+        elif kind == 'softmax':
+            a = env[op['lhs']]
+            env[op['out']] = C.softmax(lib, a.reshape(-1, a.shape[-1]), mode=op['approximation'], B=op['B'], S=op['S'],
+                                       Dmax=op['Dmax'], inv_shift=op['inv_shift'], use_clb=op['use_clb'],
+                                       exp_kq=op['exp_kq'], out_dtype=op['out_dtype']).reshape(a.shape)
+        elif kind == 'slice':
+            src = env[op['source']]
+            for item in op['slices']:
+                idx = [slice(None)] * src.ndim
+                idx[op['axis']] = slice(item['start'], item['start'] + item['extent'])
+                env[item['output']] = np.ascontiguousarray(src[tuple(idx)])
+            continue
+        elif kind == 'concat':
+            env[op['out']] = np.concatenate([env[n] for n in op['inputs']], axis=op['axis'])
+            continue
+        elapsed += time.perf_counter() - t0
+    return elapsed
+
+
+def cpu_baseline(wl, plan, target_seconds: float = 12.0):
+    lib, arch = load_cpu_oracle()
+    lib.orc_num_threads.restype = ctypes.c_int
+    cores = int(lib.orc_num_threads())
+    units = wl['units']
+    probe = max(1, min(units, 16))
+    t = max(cpu_run_plan(lib, plan, wl['inputs'], probe), 1e-6)
+    rows = int(max(probe, min(units, probe * target_seconds / t)))
+    t = cpu_run_plan(lib, plan, wl['inputs'], rows)
+    return {'value': rows / t, 'unit': 'inferences/s', 'cores': cores, 'kind': 'port',
+            'sample': f'first {rows} of {units} units of the workload, C/OpenMP oracle ({arch}), {t:.2f} s'}
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ('clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+              'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(['nvidia-smi', f'--query-gpu={self.FIELDS}', '--format=csv,noheader,nounits',
+                                      '-i', str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([x.strip() for x in out.splitlines()[0].split(',')])
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self):
+        sm = [int(s[0]) for s in self.samples if s and s[0].isdigit()]
+        mx = [int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()]
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+        reasons = sorted({n for s in self.samples for n, v in zip(names, s[2:6]) if v.lower().startswith('active')})
+        return {'sm_mhz': int(np.median(sm)) if sm else None, 'sm_max_mhz': max(mx) if mx else None,
+                'reasons': reasons, 'samples': len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+def measured_peaks():
+    path = ROOT / 'MEASURED_PEAKS.json'
+    if path.exists():
+        d = json.loads(path.read_text())
+        return {'hbm_gbs': float(d['hbm_gbs']), 'bf16_tflops': float(d['bf16_tflops']), 'source': 'measured'}
+    return {'hbm_gbs': 6650.0, 'bf16_tflops': 1590.0, 'source': 'fallback'}
+
+
+def known_traffic(kernel: str):
+    """DRAM bytes per algorithmic byte for a kernel, from the committed ncu summaries (or None)."""
+    path = ROOT / 'profiles' / 'dram_traffic.json'
+    if path.exists():
+        return json.loads(path.read_text()).get(kernel)
+    return None
+
+
+def run_reference_arm(args, rank: int, world: int):
+    if rank != 0:
+        return
+    wl = build_workload(args.workload, args)
+    from aie4ml_b200 import from_graph
+
+    plan = from_graph(wl['builder']).export_plan()
+    lib, arch = load_cpu_oracle()
+    lib.orc_num_threads.restype = ctypes.c_int
+    cores = int(lib.orc_num_threads())
+    probe = max(1, min(wl['units'], 16))
+    t = max(cpu_run_plan(lib, plan, wl['inputs'], probe), 1e-6)
+    budget = 150.0 / max(1, args.steps + args.warmup)
+    rows = int(max(probe, min(wl['units'], probe * min(budget, 20.0) / t)))
+    for _ in range(args.warmup):
+        cpu_run_plan(lib, plan, wl['inputs'], rows)
+    t0 = time.perf_counter()
+    spent = 0.0
+    for _ in range(args.steps):
+        spent += cpu_run_plan(lib, plan, wl['inputs'], rows)
+    wall = time.perf_counter() - t0
+    value = rows * args.steps / spent
+    sample = f'each step = first {rows} of {wl["units"]} units, C/OpenMP oracle ({arch}), {cores} threads'
+    print(json.dumps({
+        'impl': 'reference', 'metric': 'int8 inferences/s', 'value': value, 'unit': 'inferences/s', 'n_gpus': args.gpus,
+        'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': 1e3 * wall / args.steps, 'higher_is_better': True,
+        'scaling': 'weak', 'vs_baseline': None, 'dtype': 'int8', 'data': 'synthetic',
+        'config': {'workload': wl['desc']},
+        'cpu_baseline': {'value': value, 'unit': 'inferences/s', 'cores': cores, 'kind': 'port', 'sample': sample},
+        'e2e': {'value': value, 'unit': 'inferences/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'note': "the reference's own executor is the AMD Vitis x86 simulator, unavailable on this box; this arm is "
+                'the CPU restatement of its kernels',
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=5)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--workload', default='dense', choices=WORKLOADS)
+    ap.add_argument('--m', type=int, default=131072)
+    ap.add_argument('--k', type=int, default=8192)
+    ap.add_argument('--n', type=int, default=8192)
+    ap.add_argument('--batch', type=int, default=0)
+    ap.add_argument('--rounding', default='half_up', choices=['half_up', 'conv_even', 'floor', 'sym_inf'])
+    ap.add_argument('--no-cpu', action='store_true', help='skip the CPU baseline leg')
+    ap.add_argument('--no-e2e', action='store_true')
+    ap.add_argument('--no-graph', action='store_true')
+    ap.add_argument('--algo', type=int, default=0, help='dense kernel: 0 auto, 1 simt, 2 tcgen05')
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
+
+    rank = int(os.environ.get('RANK', 0))
+    world = int(os.environ.get('WORLD_SIZE', 1))
+    local_rank = int(os.environ.get('LOCAL_RANK', 0))
+
+    if args.impl == 'reference':
+        run_reference_arm(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from aie4ml_b200 import from_graph
+
+    if not torch.cuda.is_available():
+        raise SystemExit('bench.py: no CUDA device visible; the product path has no CPU fallback '
+                         '(use --impl reference for the CPU arm).')
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=torch.device('cuda', local_rank))
+
+    wl = build_workload(args.workload, args)
+    model = from_graph(wl['builder'])
+    model.context.aie_config['DenseAlgo'] = args.algo
+    model.build()
+    plan = model.plan
+    graph = model.context.ir.logical
+    in_names, out_names = list(graph.input_tensor_names), list(graph.output_tensor_names)
+
+    # pinned host buffers (the e2e leg copies from / to these every step)
+    host_in = {n: torch.from_numpy(np.ascontiguousarray(wl['inputs'][n])).pin_memory() for n in in_names}
+    host_out = {n: torch.empty(plan.tensor_of(n).shape, dtype=plan.tensor_of(n).dtype).pin_memory() for n in out_names}
+    h2d = sum(t.numel() * t.element_size() for t in host_in.values())
+    d2h = sum(t.numel() * t.element_size() for t in host_out.values())
+    for n in in_names:
+        plan.tensor_of(n).copy_(host_in[n], non_blocking=True)
+    torch.cuda.synchronize()
+
+    launches_per_step = len(plan.launches)
+    if not args.no_graph and launches_per_step > 1:
+        plan.capture()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device='cuda')
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing --------------------------------------------------------------
+    for _ in range(args.warmup):
+        plan.run()
+    plan.check_status()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        ev[0].record()
+        for i in range(args.steps):
+            plan.run()
+            ev[i + 1].record()
+        torch.cuda.synchronize()
+    barrier()
+    plan.check_status()
+    total_ms = max_over_ranks(ev[0].elapsed_time(ev[-1]))
+    step_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    ms_per_step = total_ms / args.steps
+    value = world * wl['units'] / (ms_per_step * 1e-3)
+
+    # ---- end-to-end timing: host pinned buffers -> H2D -> launches -> D2H ----------------------
+    e2e = None
+    if not args.no_e2e:
+        def e2e_step():
+            for n in in_names:
+                plan.tensor_of(n).copy_(host_in[n], non_blocking=True)
+            plan.run()
+            for n in out_names:
+                host_out[n].copy_(plan.tensor_of(n), non_blocking=True)
+
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k2 = max(3, min(args.steps, 10))
+        e0.record()
+        for _ in range(k2):
+            e2e_step()
+        e1.record()
+        torch.cuda.synchronize()
+        barrier()
+        e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / k2
+        e2e = {'value': world * wl['units'] / (e2e_ms * 1e-3), 'unit': 'inferences/s', 'h2d_bytes_per_step': h2d,
+               'd2h_bytes_per_step': d2h, 'ms_per_step': e2e_ms}
+
+    # ---- roofline of the dominant kernel --------------------------------------------------------
+    peaks = measured_peaks()
+    kernel_ms = float(np.mean(step_ms))  # per-step device time on this rank (one dominant kernel per step for `dense`)
+    if wl['bound'] == 'tensor':
+        achieved = wl['ops_per_unit'] * wl['units'] / (kernel_ms * 1e-3) / 1e12
+        peak = 2.0 * peaks['bf16_tflops']  # int8 dense tensor peak = 2x the bf16 rate on this part
+        roof = {'bound': 'tensor', 'achieved': achieved, 'peak': peak, 'unit': 'TFLOP/s', 'frac': achieved / peak,
+                'traffic': None, 'peak_source': f"2 x bf16_tflops of {peaks['source']} peaks (int8 rate = 2 x bf16)"}
+    else:
+        achieved = wl['bytes_per_unit'] * wl['units'] / (kernel_ms * 1e-3) / 1e9
+        roof = {'bound': 'hbm', 'achieved': achieved, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s',
+                'frac': achieved / peaks['hbm_gbs'], 'traffic': None, 'peak_source': f"hbm_gbs of {peaks['source']} peaks"}
+    ratio = known_traffic(wl['kernel'])
+    if ratio is not None:
+        roof['traffic'] = ratio * wl['bytes_per_unit'] * wl['units']
+    roof['kernel_ms'] = kernel_ms
+    roof['whole_step'] = launches_per_step > 1
+
+    if rank == 0:
+        line = {
+            'metric': 'int8 inferences/s', 'value': value, 'unit': 'inferences/s', 'n_gpus': world, 'steps': args.steps,
+            'warmup': args.warmup, 'ms_per_step': ms_per_step, 'higher_is_better': True, 'scaling': 'weak',
+            'vs_baseline': None, 'dtype': 'int8', 'data': 'synthetic',
+            'config': {'workload': wl['desc'], 'per_gpu_units': wl['units'], 'sharding': f'batch rows x{world}, no collective',
+                       'l2': 'inputs+outputs exceed the 126 MB L2' if h2d + d2h > 2 * 126e6 else 'working set fits L2',
+                       'cuda_graph': plan.graph_exec is not None, 'fused': plan.fused},
+            'roofline': roof, 'clocks': clocks.summary(), 'gpu_launches': launches_per_step * args.steps,
+        }
+        if e2e is not None:
+            line['e2e'] = e2e
+        if not args.no_cpu:
+            line['cpu_baseline'] = cpu_baseline(wl, model.export_plan())
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()

@@ -1,0 +1,110 @@
+"""Helpers for the GPU parity tests: device buffers from NumPy arrays and C-ABI calls."""
+
+import ctypes
+
+import numpy as np
+import torch
+
+from aie4ml_b200 import lib as a4c
+from aie4ml_b200.op_impls.precision import DTYPE_CODE, ROUNDING_CODE
+
+NP = {'int8': np.int8, 'uint8': np.uint8, 'int16': np.int16}
+TD = {'int8': torch.int8, 'uint8': torch.uint8, 'int16': torch.int16}
+
+
+def dev(arr):
+    return torch.from_numpy(np.ascontiguousarray(arr)).cuda()
+
+
+def stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def padded(arr, pitch, fill=0x5A):
+    """Copy a 2-D array into a wider row-major buffer (row pitch `pitch`), poison in the padding."""
+    rows, cols = arr.shape
+    buf = np.full((rows, pitch), fill, dtype=arr.dtype)
+    buf[:, :cols] = arr
+    return buf
+
+
+def pack_wt(w_kn):
+    """[K, N] int8 weights -> [N, Kp] K-contiguous with the pitch padded to 16."""
+    K, N = w_kn.shape
+    kp = (K + 15) // 16 * 16
+    out = np.zeros((N, kp), dtype=np.int8)
+    out[:, :K] = w_kn.T
+    return out
+
+
+def dense(a, w_kn, bias, *, shift, tok, relu, out_dtype='int8', algo=0, lda=None, ldy=None):
+    L = a4c.load()
+    M, K = a.shape
+    N = w_kn.shape[1]
+    lda = lda or (K + 15) // 16 * 16
+    esz = np.dtype(NP[out_dtype]).itemsize
+    ldy = ldy or (N * esz + 15) // 16 * 16 // esz
+    a_d = dev(padded(a, lda))
+    wt = dev(pack_wt(w_kn))
+    b_d = dev(bias.astype(np.int32)) if bias is not None else None
+    y_d = torch.full((M, ldy), 0x5A if esz == 1 else 0x5A5A, dtype=TD[out_dtype], device='cuda')
+    rc = L.a4c_dense_i8(a_d.data_ptr(), lda, wt.data_ptr(), wt.shape[1], b_d.data_ptr() if b_d is not None else None,
+                        y_d.data_ptr(), ldy, M, K, N, shift, ROUNDING_CODE[tok], int(relu), DTYPE_CODE[out_dtype],
+                        int(a.dtype == np.uint8), algo, stream())
+    a4c.check(rc, 'a4c_dense_i8')
+    a4c.device_status(stream())
+    y = y_d.cpu().numpy()
+    pad = y[:, N:]
+    assert (pad == (0x5A if esz == 1 else 0x5A5A)).all(), 'kernel wrote into the row padding'
+    return y[:, :N]
+
+
+def bmm(a, b, *, shift, tok, trans_a=False, trans_b=False, out_dtype='int8'):
+    L = a4c.load()
+    batch = a.shape[0]
+    M = a.shape[2] if trans_a else a.shape[1]
+    K = a.shape[1] if trans_a else a.shape[2]
+    N = b.shape[1] if trans_b else b.shape[2]
+    a_d, b_d = dev(a), dev(b)
+    c_d = torch.zeros((batch, M, N), dtype=TD[out_dtype], device='cuda')
+    rc = L.a4c_bmm_i8(a_d.data_ptr(), a.shape[2], a.shape[1] * a.shape[2], b_d.data_ptr(), b.shape[2],
+                      b.shape[1] * b.shape[2], c_d.data_ptr(), N, M * N, batch, M, K, N, int(trans_a), int(trans_b), shift,
+                      ROUNDING_CODE[tok], DTYPE_CODE[out_dtype], int(a.dtype == np.uint8), stream())
+    a4c.check(rc, 'a4c_bmm_i8')
+    return c_d.cpu().numpy()
+
+
+def layer_norm(x, gamma, beta, *, eps_q0, out_shift, tok, addend=None):
+    L = a4c.load()
+    rows, cols = x.shape
+    x_d, g_d, b_d = dev(x), dev(gamma.astype(np.int16)), dev(beta.astype(np.int16))
+    a_d = dev(addend) if addend is not None else None
+    o_d = torch.zeros((rows, cols), dtype=torch.int8, device='cuda')
+    rc = L.a4c_layernorm_i8(x_d.data_ptr(), cols, g_d.data_ptr(), b_d.data_ptr(), a_d.data_ptr() if a_d is not None else None,
+                            cols, o_d.data_ptr(), cols, rows, cols, eps_q0, out_shift, ROUNDING_CODE[tok], stream())
+    a4c.check(rc, 'a4c_layernorm_i8')
+    return o_d.cpu().numpy()
+
+
+def softmax(x, *, mode, B=0, S=0, Dmax=0, inv_shift=15, use_clb=False, exp_kq=0, out_dtype='uint8', addend=None):
+    L = a4c.load()
+    rows, cols = x.shape
+    x_d = dev(x)
+    a_d = dev(addend) if addend is not None else None
+    o_d = torch.zeros((rows, cols), dtype=TD[out_dtype], device='cuda')
+    rc = L.a4c_softmax_i8(x_d.data_ptr(), cols, a_d.data_ptr() if a_d is not None else None, cols, o_d.data_ptr(), cols,
+                          rows, cols, 0 if mode == 'hccs' else 1, B, S, Dmax, inv_shift, int(use_clb), exp_kq,
+                          DTYPE_CODE[out_dtype], stream())
+    a4c.check(rc, 'a4c_softmax_i8')
+    return o_d.cpu().numpy()
+
+
+def add(a, b, *, shift, tok, dtype):
+    L = a4c.load()
+    rows, cols = a.shape
+    a_d, b_d = dev(a), dev(b)
+    o_d = torch.zeros((rows, cols), dtype=TD[dtype], device='cuda')
+    rc = L.a4c_add_sat(a_d.data_ptr(), cols, b_d.data_ptr(), cols, o_d.data_ptr(), cols, rows, cols, shift,
+                       ROUNDING_CODE[tok], DTYPE_CODE[dtype], stream())
+    a4c.check(rc, 'a4c_add_sat')
+    return o_d.cpu().numpy()

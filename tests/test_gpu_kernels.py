@@ -1,0 +1,206 @@
+"""Kernel-level parity: every C-ABI entry point against the CPU oracle, bit-exact, on seeded inputs."""
+
+import numpy as np
+import pytest
+
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+TOKENS = oracle.ROUNDING_TOKENS
+SIMT, TC = 1, 2
+
+
+def _rand_dense(seed, M, K, N, unsigned=False, big_bias=True):
+    rng = np.random.default_rng(seed)
+    a = rng.integers(0, 256, (M, K)).astype(np.uint8) if unsigned else rng.integers(-128, 128, (M, K)).astype(np.int8)
+    w = rng.integers(-128, 128, (K, N)).astype(np.int8)
+    bias = rng.integers(-(1 << 16), 1 << 16, N).astype(np.int32) if big_bias else None
+    return a, w, bias
+
+
+@pytest.mark.parametrize('shape', [(1, 16, 5), (7, 16, 64), (33, 50, 21), (64, 64, 32), (130, 100, 10), (257, 33, 65)])
+@pytest.mark.parametrize('tok', ['positive_inf', 'conv_even'])
+def test_dense_simt_odd_shapes(shape, tok):
+    import gpu_util as G
+
+    M, K, N = shape
+    a, w, bias = _rand_dense(hash(shape) % 1000, M, K, N)
+    for shift, relu in ((7, True), (0, False), (10, False)):
+        got = G.dense(a, w, bias, shift=shift, tok=tok, relu=relu, algo=SIMT)
+        np.testing.assert_array_equal(got, oracle.dense(a, w, bias, shift=shift, tok=tok, relu=relu))
+
+
+@pytest.mark.parametrize('tok', TOKENS)
+def test_dense_simt_every_rounding_mode_and_dtype(tok):
+    import gpu_util as G
+
+    a, w, bias = _rand_dense(11, 96, 72, 48)
+    for shift, od in ((1, 'int16'), (9, 'int8'), (9, 'uint8'), (31, 'int8')):
+        got = G.dense(a, w, bias, shift=shift, tok=tok, relu=False, out_dtype=od, algo=SIMT)
+        np.testing.assert_array_equal(got, oracle.dense(a, w, bias, shift=shift, tok=tok, relu=False, out_dtype=od))
+    u, w2, _ = _rand_dense(12, 40, 64, 32, unsigned=True)
+    np.testing.assert_array_equal(G.dense(u, w2, None, shift=8, tok=tok, relu=False, algo=SIMT),
+                                  oracle.dense(u, w2, None, shift=8, tok=tok, relu=False))
+
+
+@pytest.mark.parametrize('shape', [(128, 128, 256), (128, 256, 16), (100, 16, 48), (300, 1024, 272), (1000, 200, 512),
+                                   (4096, 512, 1024), (129, 4096, 256)])
+def test_dense_tcgen05_shapes(shape):
+    import gpu_util as G
+
+    M, K, N = shape
+    a, w, bias = _rand_dense(sum(shape), M, K, N)
+    got = G.dense(a, w, bias, shift=10, tok='positive_inf', relu=True, algo=TC)
+    np.testing.assert_array_equal(got, oracle.dense(a, w, bias, shift=10, tok='positive_inf', relu=True))
+
+
+@pytest.mark.parametrize('tok', TOKENS)
+def test_dense_tcgen05_every_rounding_mode(tok):
+    import gpu_util as G
+
+    a, w, bias = _rand_dense(21, 384, 384, 320)
+    for shift, relu, od in ((9, False, 'int8'), (3, True, 'int8'), (12, False, 'uint8'), (0, False, 'int8')):
+        got = G.dense(a, w, bias, shift=shift, tok=tok, relu=relu, out_dtype=od, algo=TC)
+        np.testing.assert_array_equal(got, oracle.dense(a, w, bias, shift=shift, tok=tok, relu=relu, out_dtype=od))
+
+
+def test_dense_tcgen05_unsigned_lhs_no_bias_and_many_tiles():
+    import gpu_util as G
+
+    u, w, _ = _rand_dense(31, 640, 256, 768, unsigned=True)
+    np.testing.assert_array_equal(G.dense(u, w, None, shift=11, tok='conv_even', relu=False, algo=TC),
+                                  oracle.dense(u, w, None, shift=11, tok='conv_even', relu=False))
+    # more tiles than SMs: the persistent loop and both accumulator stages get reused
+    a, w, bias = _rand_dense(32, 128 * 40, 128, 1024)
+    np.testing.assert_array_equal(G.dense(a, w, bias, shift=8, tok='floor', relu=True, algo=TC),
+                                  oracle.dense(a, w, bias, shift=8, tok='floor', relu=True))
+
+
+def test_dense_auto_picks_a_working_kernel_and_rejects_bad_arguments():
+    import gpu_util as G
+    from aie4ml_b200 import lib as a4c
+
+    a, w, bias = _rand_dense(41, 256, 256, 256)
+    np.testing.assert_array_equal(G.dense(a, w, bias, shift=10, tok='positive_inf', relu=True, algo=0),
+                                  oracle.dense(a, w, bias, shift=10, tok='positive_inf', relu=True))
+    a2, w2, b2 = _rand_dense(42, 9, 20, 5)  # N = 5: the tensor-core path cannot take it, auto must still work
+    np.testing.assert_array_equal(G.dense(a2, w2, b2, shift=7, tok='positive_inf', relu=False, algo=0),
+                                  oracle.dense(a2, w2, b2, shift=7, tok='positive_inf', relu=False))
+    with pytest.raises(a4c.A4cError):
+        G.dense(a2, w2, b2, shift=7, tok='positive_inf', relu=False, algo=TC)
+    with pytest.raises(a4c.A4cError):
+        G.dense(a, w, bias, shift=40, tok='positive_inf', relu=False)
+
+
+def test_bmm_attention_shapes():
+    import gpu_util as G
+
+    rng = np.random.default_rng(51)
+    q = rng.integers(-128, 128, (6, 128, 64)).astype(np.int8)
+    k = rng.integers(-128, 128, (6, 128, 64)).astype(np.int8)
+    v = rng.integers(-128, 128, (6, 128, 64)).astype(np.int8)
+    p = rng.integers(0, 256, (6, 128, 128)).astype(np.uint8)
+    np.testing.assert_array_equal(G.bmm(q, k, shift=9, tok='positive_inf', trans_b=True),
+                                  oracle.matmul(q, k, shift=9, tok='positive_inf', transpose_b=True))
+    np.testing.assert_array_equal(G.bmm(p, v, shift=8, tok='conv_even'), oracle.matmul(p, v, shift=8, tok='conv_even'))
+    a = rng.integers(-128, 128, (3, 20, 37)).astype(np.int8)   # stored [K, M]
+    b = rng.integers(-128, 128, (3, 20, 11)).astype(np.int8)
+    np.testing.assert_array_equal(G.bmm(a, b, shift=4, tok='floor', trans_a=True, out_dtype='int16'),
+                                  oracle.matmul(a, b, shift=4, tok='floor', transpose_a=True, out_dtype='int16'))
+
+
+def _ln_inputs(seed, rows, cols):
+    rng = np.random.default_rng(seed)
+    x = np.clip(np.rint(rng.normal(2, 32, (rows, cols))), -128, 127).astype(np.int8)
+    x[0] = 7
+    x[1] = -128
+    x[2, ::2], x[2, 1::2] = 127, -128
+    x[3] = 0
+    x[3, 0] = 1
+    return x, rng
+
+
+@pytest.mark.parametrize('cols', [32, 64, 256, 1024, 4096])
+@pytest.mark.parametrize('tok', ['positive_inf', 'conv_even', 'floor', 'symmetric_inf'])
+def test_layer_norm(cols, tok):
+    import gpu_util as G
+
+    x, rng = _ln_inputs(cols, 77, cols)
+    gamma = rng.integers(-256, 257, cols)
+    beta = rng.integers(-256, 257, cols)
+    for out_shift in (4, 0, 15):
+        np.testing.assert_array_equal(G.layer_norm(x, gamma, beta, eps_q0=1, out_shift=out_shift, tok=tok),
+                                      oracle.layer_norm(x, gamma, beta, eps_q0=1, out_shift=out_shift, tok=tok))
+    big_g = rng.integers(-32768, 32768, cols)
+    big_b = rng.integers(-32768, 32768, cols)
+    np.testing.assert_array_equal(G.layer_norm(x, big_g, big_b, eps_q0=3, out_shift=6, tok=tok),
+                                  oracle.layer_norm(x, big_g, big_b, eps_q0=3, out_shift=6, tok=tok))
+    addend = rng.integers(-128, 128, x.shape).astype(np.int8)
+    fused = G.layer_norm(x, gamma, beta, eps_q0=1, out_shift=4, tok=tok, addend=addend)
+    want = oracle.add(oracle.layer_norm(x, gamma, beta, eps_q0=1, out_shift=4, tok=tok), addend, out_dtype='int8')
+    np.testing.assert_array_equal(fused, want)
+
+
+def test_layer_norm_every_rounding_mode():
+    import gpu_util as G
+
+    x, rng = _ln_inputs(5, 40, 256)
+    gamma = rng.integers(-2000, 2000, 256)
+    beta = rng.integers(-20000, 20000, 256)
+    for tok in TOKENS:
+        np.testing.assert_array_equal(G.layer_norm(x, gamma, beta, eps_q0=1, out_shift=5, tok=tok),
+                                      oracle.layer_norm(x, gamma, beta, eps_q0=1, out_shift=5, tok=tok), err_msg=tok)
+
+
+@pytest.mark.parametrize('cols', [32, 96, 128, 1024, 2048])
+@pytest.mark.parametrize('out_dtype', ['uint8', 'int16'])
+def test_softmax_both_modes(cols, out_dtype):
+    import gpu_util as G
+
+    x, rng = _ln_inputs(cols + 1, 61, cols)
+    np.testing.assert_array_equal(G.softmax(x, mode='exp', exp_kq=23, out_dtype=out_dtype),
+                                  oracle.softmax_exp(x, exp_kq=23, out_dtype=out_dtype))
+    np.testing.assert_array_equal(G.softmax(x, mode='exp', exp_kq=128, out_dtype=out_dtype),
+                                  oracle.softmax_exp(x, exp_kq=128, out_dtype=out_dtype))
+    B = min(255, 32767 // cols)
+    S = 1 if B < 100 else 3
+    Dmax = (B - max(1, -(-256 // cols))) // S
+    np.testing.assert_array_equal(G.softmax(x, mode='hccs', B=B, S=S, Dmax=Dmax, out_dtype=out_dtype),
+                                  oracle.softmax_hccs(x, B=B, S=S, Dmax=Dmax, out_dtype=out_dtype))
+    np.testing.assert_array_equal(G.softmax(x, mode='hccs', B=B, S=S, Dmax=Dmax, inv_shift=14, use_clb=True, out_dtype=out_dtype),
+                                  oracle.softmax_hccs(x, B=B, S=S, Dmax=Dmax, inv_shift=14, use_clb=True, out_dtype=out_dtype))
+    lo, hi = (0, 256) if out_dtype == 'uint8' else (-32768, 32768)
+    addend = rng.integers(lo, hi, x.shape).astype(G.NP[out_dtype])
+    fused = G.softmax(x, mode='exp', exp_kq=46, out_dtype=out_dtype, addend=addend)
+    want = oracle.add(oracle.softmax_exp(x, exp_kq=46, out_dtype=out_dtype), addend, out_dtype=out_dtype)
+    np.testing.assert_array_equal(fused, want)
+
+
+@pytest.mark.parametrize('dtype', ['int8', 'uint8', 'int16'])
+def test_add_saturating(dtype):
+    import gpu_util as G
+
+    rng = np.random.default_rng(71)
+    lo, hi = {'int8': (-128, 128), 'uint8': (0, 256), 'int16': (-32768, 32768)}[dtype]
+    a = rng.integers(lo, hi, (37, 256)).astype(G.NP[dtype])
+    b = rng.integers(lo, hi, (37, 256)).astype(G.NP[dtype])
+    np.testing.assert_array_equal(G.add(a, b, shift=0, tok='conv_even', dtype=dtype),
+                                  oracle.add(a, b, shift=0, tok='conv_even', out_dtype=dtype))
+    for tok in TOKENS:
+        np.testing.assert_array_equal(G.add(a, b, shift=1, tok=tok, dtype=dtype),
+                                      oracle.add(a, b, shift=1, tok=tok, out_dtype=dtype), err_msg=tok)
+
+
+def test_empty_inputs_are_no_ops():
+    import gpu_util as G
+    import torch
+    from aie4ml_b200 import lib as a4c
+
+    L = a4c.load()
+    buf = torch.zeros(4096, dtype=torch.int8, device='cuda')
+    p = buf.data_ptr()
+    assert L.a4c_dense_i8(p, 64, p, 64, None, p, 64, 0, 64, 64, 7, 2, 0, 0, 0, 0, G.stream()) == 0
+    assert L.a4c_add_sat(p, 64, p, 64, p, 64, 0, 64, 0, 6, 0, G.stream()) == 0
+    assert L.a4c_layernorm_i8(p, 64, p, p, None, 0, p, 64, 0, 64, 1, 4, 6, G.stream()) == 0
+    assert L.a4c_softmax_i8(p, 64, None, 0, p, 64, 0, 64, 1, 0, 0, 0, 15, 0, 23, 1, G.stream()) == 0

@@ -1,0 +1,98 @@
+"""Whole lowered graphs through the model API (front door -> passes -> plan -> C ABI) against the
+oracle evaluating the exported plan, bit-exact, plus size-independent properties at larger sizes."""
+
+import numpy as np
+import pytest
+
+from aie4ml_b200 import from_graph
+from aie4ml_b200 import workloads as W
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(builder, inputs, **cfg):
+    model = from_graph(builder)
+    model.context.aie_config.update(cfg)
+    model.compile()
+    got = model.predict(inputs, quantize_in=False, dequantize_out=False)
+    want = oracle.run_plan(model.export_plan(), inputs)
+    (name, ref), = want.items()
+    np.testing.assert_array_equal(np.asarray(got), ref.astype(np.int64))
+    return model
+
+
+@pytest.mark.parametrize('rounding', ['half_up', 'conv_even'])
+def test_cfg1_mlp(rounding):
+    _check(*W.mlp_cfg1(1024, rounding=rounding))
+
+
+@pytest.mark.parametrize('shape', [(1024, 1024, 1024), (512, 4096, 1024), (256, 1024, 4096)])
+def test_cfg2_dense(shape):
+    _check(*W.dense_cfg2(*shape))
+
+
+@pytest.mark.parametrize('softmax', ['exp', 'hccs'])
+@pytest.mark.parametrize('rounding', ['half_up', 'conv_even'])
+def test_cfg3_encoder_block(softmax, rounding):
+    model = _check(*W.encoder_cfg3(3, softmax=softmax, rounding=rounding))
+    kinds = [op['kind'] for op in model.plan.ops]
+    assert kinds.count('matmul') == 8 and kinds.count('softmax') == 4 and kinds.count('layer_norm') == 2
+
+
+@pytest.mark.parametrize('op', ['layer_norm', 'softmax_exp', 'softmax_hccs'])
+def test_cfg4_rowop_plus_add_fused_and_unfused(op):
+    b, inp = W.rowops_cfg4(513, 1024, op)
+    fused = _check(b, inp)
+    assert len(fused.plan.launches) == 1 and fused.plan.fused
+    b2, inp2 = W.rowops_cfg4(513, 1024, op)
+    unfused = _check(b2, inp2, FusionPolicy={'rowop_add': False})
+    assert len(unfused.plan.launches) == 2
+
+
+def test_cfg5_wide_mlp_with_fanout_and_concat():
+    model = _check(*W.wide_mlp_cfg5(300))
+    # both branch tails write straight into the concat buffer: no copy kernel, 10 dense launches
+    assert len(model.plan.launches) == 10
+    assert model.plan.views['b0_fc3_out'].root == model.plan.views['b1_fc3_out'].root == 'cat_out'
+
+
+def test_cuda_graph_replay_matches_eager():
+    b, inp = W.encoder_cfg3(2, softmax='exp')
+    model = from_graph(b)
+    model.compile()
+    eager = model.predict(inp, quantize_in=False, dequantize_out=False)
+    model.plan.capture()
+    replay = model.predict(inp, quantize_in=False, dequantize_out=False)
+    np.testing.assert_array_equal(eager, replay)
+
+
+def test_float_boundary_quantise_dequantise():
+    b, inp = W.mlp_cfg1(64)
+    model = from_graph(b)
+    model.compile()
+    xf = inp['x'].astype(np.float64) / 16.0
+    yf = model.predict(xf)
+    yi = model.predict(inp, quantize_in=False, dequantize_out=False)
+    np.testing.assert_array_equal(yf, yi / 16.0)
+
+
+def test_dense_linearity_property_at_scale():
+    """With shift 0 and int16-free ranges the kernel is linear: Y(a1) + Y(a2) == Y(a1 + a2) when nothing
+    saturates -- checked on a problem too large for the oracle to evaluate quickly."""
+    import gpu_util as G
+
+    rng = np.random.default_rng(5)
+    M, K, N = 8192, 1024, 2048
+    a1 = rng.integers(-3, 4, (M, K)).astype(np.int8)
+    a2 = rng.integers(-3, 4, (M, K)).astype(np.int8)
+    w = rng.integers(-1, 2, (K, N)).astype(np.int8)
+    y1 = G.dense(a1, w, None, shift=0, tok='floor', relu=False, out_dtype='int8', algo=2).astype(np.int64)
+    y2 = G.dense(a2, w, None, shift=0, tok='floor', relu=False, out_dtype='int8', algo=2).astype(np.int64)
+    y12 = G.dense((a1 + a2).astype(np.int8), w, None, shift=0, tok='floor', relu=False, out_dtype='int8', algo=2).astype(np.int64)
+    ok = (np.abs(y1 + y2) < 127) & (np.abs(y1) < 127) & (np.abs(y2) < 127) & (np.abs(y12) < 127)
+    assert ok.mean() > 0.5
+    np.testing.assert_array_equal((y1 + y2)[ok], y12[ok])
+    # and the two GEMM kernels agree with each other everywhere
+    ys = G.dense(a1, w, None, shift=0, tok='floor', relu=False, out_dtype='int8', algo=1)
+    np.testing.assert_array_equal(ys, y1)

@@ -1,0 +1,217 @@
+"""The oracle itself: hand-checkable rounding / saturation tables, the identities its integer
+recipes must satisfy, float sanity bounds, and agreement between its NumPy and C editions."""
+
+import numpy as np
+import pytest
+
+import oracle_c_api as C
+from oracle import oracle
+
+TOKENS = oracle.ROUNDING_TOKENS
+
+
+def test_round_shift_hand_table():
+    # value / 4 for v = -6..6: exact -1.5, -1.25, -1, -0.75, -0.5, -0.25, 0, 0.25, 0.5, 0.75, 1, 1.25, 1.5
+    v = np.arange(-6, 7)
+    want = {
+        'floor':          [-2, -2, -1, -1, -1, -1, 0, 0, 0, 0, 1, 1, 1],
+        'ceil':           [-1, -1, -1, 0, 0, 0, 0, 1, 1, 1, 1, 2, 2],
+        'positive_inf':   [-1, -1, -1, -1, 0, 0, 0, 0, 1, 1, 1, 1, 2],
+        'negative_inf':   [-2, -1, -1, -1, -1, 0, 0, 0, 0, 1, 1, 1, 1],
+        'symmetric_inf':  [-2, -1, -1, -1, -1, 0, 0, 0, 1, 1, 1, 1, 2],
+        'symmetric_zero': [-1, -1, -1, -1, 0, 0, 0, 0, 0, 1, 1, 1, 1],
+        'conv_even':      [-2, -1, -1, -1, 0, 0, 0, 0, 0, 1, 1, 1, 2],
+        'conv_odd':       [-1, -1, -1, -1, -1, 0, 0, 0, 1, 1, 1, 1, 1],
+    }
+    for tok in TOKENS:
+        np.testing.assert_array_equal(oracle.round_shift(v, 2, tok), want[tok], err_msg=tok)
+
+
+def test_round_shift_against_float_reference():
+    rng = np.random.default_rng(0)
+    v = rng.integers(-(1 << 30), 1 << 30, 4000)
+    for shift in (1, 3, 7, 10, 20):
+        x = v.astype(np.float64) / (1 << shift)
+        np.testing.assert_array_equal(oracle.round_shift(v, shift, 'floor'), np.floor(x))
+        np.testing.assert_array_equal(oracle.round_shift(v, shift, 'ceil'), np.ceil(x))
+        np.testing.assert_array_equal(oracle.round_shift(v, shift, 'positive_inf'), np.floor(x + 0.5))
+        np.testing.assert_array_equal(oracle.round_shift(v, shift, 'conv_even'), np.round(x))
+        away = np.where(x >= 0, np.floor(x + 0.5), np.ceil(x - 0.5))
+        np.testing.assert_array_equal(oracle.round_shift(v, shift, 'symmetric_inf'), away)
+    np.testing.assert_array_equal(oracle.round_shift(v, 0, 'conv_even'), v)
+
+
+def test_srs_saturates_every_dtype():
+    v = np.array([-70000, -32769, -32768, -129, -128, -1, 0, 127, 128, 255, 256, 32767, 32768, 70000])
+    np.testing.assert_array_equal(oracle.srs(v, 0, 'floor', 'int8'), np.clip(v, -128, 127))
+    np.testing.assert_array_equal(oracle.srs(v, 0, 'floor', 'uint8'), np.clip(v, 0, 255))
+    np.testing.assert_array_equal(oracle.srs(v, 0, 'floor', 'int16'), np.clip(v, -32768, 32767))
+
+
+def test_dense_relu_after_saturation_and_bias():
+    a = np.array([[127, 127], [-128, -128], [1, -1]], dtype=np.int8)
+    w = np.array([[127, -128], [127, -128]], dtype=np.int8)
+    bias = np.array([5, -5], dtype=np.int32)
+    y = oracle.dense(a, w, bias, shift=4, tok='positive_inf', relu=False)
+    acc = a.astype(np.int64) @ w.astype(np.int64) + bias
+    np.testing.assert_array_equal(y, np.clip(np.floor(acc / 16 + 0.5), -128, 127))
+    yr = oracle.dense(a, w, bias, shift=4, tok='positive_inf', relu=True)
+    np.testing.assert_array_equal(yr, np.maximum(y, 0))
+
+
+def test_dense_within_one_lsb_of_float_evaluation():
+    # mirrors the reference's own check (scripts/check_onnx_bit_exact.py:37-46,170-179): requantised
+    # float evaluation vs integer kernel, at most 1 LSB apart
+    rng = np.random.default_rng(1)
+    a = rng.integers(-128, 128, (64, 96)).astype(np.int8)
+    w = rng.integers(-127, 128, (96, 48)).astype(np.int8)
+    bias = rng.integers(-4096, 4096, 48).astype(np.int32)
+    y = oracle.dense(a, w, bias, shift=9, tok='conv_even', relu=False)
+    f = (a.astype(np.float64) @ w.astype(np.float64) + bias) / 512.0
+    assert np.abs(y - np.clip(np.rint(f), -128, 127)).max() <= 1
+
+
+def test_matmul_transposes():
+    rng = np.random.default_rng(2)
+    a = rng.integers(-128, 128, (3, 8, 16)).astype(np.int8)
+    b = rng.integers(-128, 128, (3, 16, 12)).astype(np.int8)
+    ref = oracle.matmul(a, b, shift=5, tok='floor')
+    np.testing.assert_array_equal(oracle.matmul(np.swapaxes(a, 1, 2).copy(), b, shift=5, tok='floor', transpose_a=True), ref)
+    np.testing.assert_array_equal(oracle.matmul(a, np.swapaxes(b, 1, 2).copy(), shift=5, tok='floor', transpose_b=True), ref)
+    u = rng.integers(0, 256, (3, 8, 16)).astype(np.uint8)
+    np.testing.assert_array_equal(oracle.matmul(u, b, shift=8, tok='positive_inf'),
+                                  np.clip(np.floor(np.matmul(u.astype(np.int64), b.astype(np.int64)) / 256 + 0.5), -128, 127))
+
+
+def test_exp_score_tracks_real_exponential():
+    d = np.arange(256)
+    for kq in (1, 23, 46, 128):
+        e = oracle.exp_score16(d, kq)
+        real = 16384.0 * np.exp2(-(d * kq) / 256.0)
+        assert e[0] == 16384
+        assert np.all(np.diff(e) <= 0)
+        assert np.abs(e - real).max() <= 16384 * 0.004 + 1
+
+
+def test_softmax_reciprocal_identity_and_range():
+    rng = np.random.default_rng(3)
+    x = np.clip(np.rint(rng.normal(0, 32, (64, 1024))), -128, 127).astype(np.int8)
+    for out_dtype in ('uint8', 'int16'):
+        out = oracle.softmax_exp(x, exp_kq=23, out_dtype=out_dtype)
+        assert out.dtype == np.dtype(out_dtype)
+        assert out.min() >= 0
+        m = x.astype(np.int64).max(axis=1, keepdims=True)
+        e = oracle.exp_score16(m - x, 23)
+        s = e.sum(axis=1)
+        numer = oracle.softmax_numer(out_dtype, 15)
+        q = numer // s
+        assert np.all(q * s <= numer) and np.all((q + 1) * s > numer)
+    h = oracle.softmax_hccs(x, B=31, S=1, Dmax=30)
+    assert h.max() <= 255 and h.min() >= 0
+    # rows sum to about 255 (floor losses only)
+    assert np.all(h.astype(np.int64).sum(axis=1) <= 255 * 1.01) and np.all(h.astype(np.int64).sum(axis=1) >= 255 - 1024)
+
+
+def test_softmax_exp_close_to_float_softmax():
+    rng = np.random.default_rng(4)
+    x = np.clip(np.rint(rng.normal(0, 24, (32, 128))), -128, 127).astype(np.int8)
+    frac = 4
+    out = oracle.softmax_exp(x, exp_kq=oracle.exp_kq(frac)).astype(np.float64) / 256.0
+    xf = x.astype(np.float64) / (1 << frac)
+    p = np.exp(xf - xf.max(axis=1, keepdims=True))
+    p /= p.sum(axis=1, keepdims=True)
+    assert np.abs(out - p).max() <= 3.0 / 256.0
+
+
+def test_softmax_clb_matches_definition():
+    x = np.arange(-64, 64, dtype=np.int8)[None, :].repeat(4, axis=0)
+    got = oracle.softmax_hccs(x, B=200, S=3, Dmax=66, inv_shift=14, use_clb=True)
+    d = np.minimum(63 - x.astype(np.int64), 66)
+    score = 200 - 3 * d
+    k = int(np.floor(np.log2(score[0].sum())))
+    inv = 255 << (14 - k)
+    np.testing.assert_array_equal(got, np.clip((score * inv) >> 14, 0, 255))
+
+
+def test_layer_norm_close_to_float_and_inv_std_definition():
+    rng = np.random.default_rng(5)
+    x = np.clip(np.rint(rng.normal(3, 30, (48, 256))), -128, 127).astype(np.int8)
+    gamma = rng.integers(-256, 257, 256)
+    beta = rng.integers(-256, 257, 256)
+    out_shift = 4
+    y = oracle.layer_norm(x, gamma, beta, eps_q0=1, out_shift=out_shift, tok='conv_even').astype(np.float64) / (1 << out_shift)
+    xf = x.astype(np.float64)
+    norm = (xf - xf.mean(axis=1, keepdims=True)) / np.sqrt(xf.var(axis=1, keepdims=True) + 1.0)
+    ref = norm * (gamma / 128.0) + beta / 32768.0
+    assert np.abs(y - np.clip(ref, -8, 127 / 16)).max() <= 3.0 / 16.0
+    # reciprocal std: exact powers of four hit exact Q15 values; var = 1 clamps to 32767
+    np.testing.assert_array_equal(oracle.inv_std_q15(np.array([1, 4, 16, 64, 16384]), 'floor'),
+                                  [32767, 16384, 8192, 4096, 256])
+    v = np.arange(1, 16386)
+    q = oracle.inv_std_q15(v, 'conv_even')
+    assert np.all(np.diff(q) <= 0)
+    assert np.abs(q - np.minimum(32768.0 / np.sqrt(v), 32767)).max() <= 0.51
+
+
+def test_layer_norm_fscale_saturates():
+    # var small and |gamma| large: inv_std * gamma >> 7 exceeds int16 and must clamp (layer_norm.cpp:108-109)
+    x = np.zeros((1, 32), dtype=np.int8)
+    x[0, 0] = 1
+    gamma = np.full(32, 32767)
+    beta = np.zeros(32)
+    y = oracle.layer_norm(x, gamma, beta, eps_q0=1, out_shift=0, tok='floor')
+    assert y[0, 0] == np.clip((1 * 32767) >> 15, -128, 127)
+
+
+@pytest.mark.parametrize('tok', TOKENS)
+def test_c_edition_matches_numpy_dense_and_add(oracle_c, tok):
+    rng = np.random.default_rng(6)
+    a = rng.integers(-128, 128, (37, 50)).astype(np.int8)
+    w = rng.integers(-128, 128, (50, 21)).astype(np.int8)
+    bias = rng.integers(-(1 << 16), 1 << 16, 21).astype(np.int32)
+    for shift, relu, od in ((0, False, 'int16'), (7, True, 'int8'), (10, False, 'uint8'), (3, False, 'int8')):
+        np.testing.assert_array_equal(C.dense(oracle_c, a, w, bias, shift=shift, tok=tok, relu=relu, out_dtype=od),
+                                      oracle.dense(a, w, bias, shift=shift, tok=tok, relu=relu, out_dtype=od))
+    u = rng.integers(0, 256, (37, 50)).astype(np.uint8)
+    np.testing.assert_array_equal(C.dense(oracle_c, u, w, None, shift=8, tok=tok, relu=False),
+                                  oracle.dense(u, w, None, shift=8, tok=tok, relu=False))
+    for dt, lo, hi in (('int8', -128, 128), ('uint8', 0, 256), ('int16', -32768, 32768)):
+        p = rng.integers(lo, hi, (9, 64)).astype(C.NP[dt])
+        q = rng.integers(lo, hi, (9, 64)).astype(C.NP[dt])
+        for shift in (0, 1):
+            np.testing.assert_array_equal(C.add(oracle_c, p, q, shift=shift, tok=tok, dtype=dt),
+                                          oracle.add(p, q, shift=shift, tok=tok, out_dtype=dt))
+
+
+def test_c_edition_matches_numpy_bmm(oracle_c):
+    rng = np.random.default_rng(7)
+    a = rng.integers(-128, 128, (5, 12, 20)).astype(np.int8)
+    b = rng.integers(-128, 128, (5, 20, 9)).astype(np.int8)
+    np.testing.assert_array_equal(C.bmm(oracle_c, a, b, shift=6, tok='conv_even'), oracle.matmul(a, b, shift=6, tok='conv_even'))
+    bt = np.swapaxes(b, 1, 2).copy()
+    np.testing.assert_array_equal(C.bmm(oracle_c, a, bt, shift=6, tok='floor', trans_b=True),
+                                  oracle.matmul(a, bt, shift=6, tok='floor', transpose_b=True))
+    at = np.swapaxes(a, 1, 2).copy()
+    np.testing.assert_array_equal(C.bmm(oracle_c, at, b, shift=2, tok='ceil', trans_a=True, out_dtype='int16'),
+                                  oracle.matmul(at, b, shift=2, tok='ceil', transpose_a=True, out_dtype='int16'))
+
+
+@pytest.mark.parametrize('tok', ['floor', 'positive_inf', 'conv_even', 'symmetric_inf'])
+def test_c_edition_matches_numpy_rowops(oracle_c, tok):
+    rng = np.random.default_rng(8)
+    x = np.clip(np.rint(rng.normal(0, 32, (33, 256))), -128, 127).astype(np.int8)
+    x[0] = 5          # zero variance
+    x[1, :] = -128    # extreme mean
+    x[2, ::2], x[2, 1::2] = 127, -128
+    gamma = rng.integers(-32768, 32768, 256)
+    beta = rng.integers(-32768, 32768, 256)
+    for out_shift in (0, 4, 15):
+        np.testing.assert_array_equal(C.layer_norm(oracle_c, x, gamma, beta, eps_q0=1, out_shift=out_shift, tok=tok),
+                                      oracle.layer_norm(x, gamma, beta, eps_q0=1, out_shift=out_shift, tok=tok))
+    for od in ('uint8', 'int16'):
+        np.testing.assert_array_equal(C.softmax(oracle_c, x, mode='exp', exp_kq=23, out_dtype=od),
+                                      oracle.softmax_exp(x, exp_kq=23, out_dtype=od))
+        np.testing.assert_array_equal(C.softmax(oracle_c, x, mode='hccs', B=120, S=2, Dmax=59, out_dtype=od),
+                                      oracle.softmax_hccs(x, B=120, S=2, Dmax=59, out_dtype=od))
+    np.testing.assert_array_equal(C.softmax(oracle_c, x, mode='hccs', B=120, S=2, Dmax=59, inv_shift=14, use_clb=True),
+                                  oracle.softmax_hccs(x, B=120, S=2, Dmax=59, inv_shift=14, use_clb=True))
