@@ -29,3 +29,13 @@ int a4c_launch_softmax(const int8_t* x, long long ldx, const void* addend, long 
 
 int a4c_launch_add(const void* a, long long lda, const void* b, long long ldb, void* out, long long ldo,
                    long long rows, long long cols, int shift, int rounding, int dtype, cudaStream_t stream);
+
+// Bandwidth-oriented variants of the two row ops (rowops_fast.cu).  They return A4C_ERR_UNSUPPORTED when a
+// request lies outside what they prove exact; the caller then uses the generic kernels above.
+int a4c_launch_layernorm_fast(const int8_t* x, long long ldx, const int16_t* gamma, const int16_t* beta,
+                              const int8_t* addend, long long ldadd, int8_t* out, long long ldo, long long rows,
+                              int cols, int eps_q0, int out_shift, int rounding, int gamma_absmax, int* status,
+                              cudaStream_t stream);
+int a4c_launch_softmax_fast(const int8_t* x, long long ldx, const void* addend, long long ldadd, void* out,
+                            long long ldo, long long rows, int cols, int mode, int B, int S, int Dmax, int inv_shift,
+                            int use_clb, int exp_kq, int out_dtype, int* status, cudaStream_t stream);

@@ -12,6 +12,7 @@ constexpr int kMaxDevices = 64;
 std::mutex g_mutex;
 int* g_status[kMaxDevices] = {nullptr};
 thread_local const char* t_last_cuda_error = "no error";
+int g_rowop_path = 0;  // 0 auto (fast kernels when they apply), 1 generic kernels only
 
 bool note(cudaError_t e) {
     if (e != cudaSuccess) {
@@ -123,11 +124,28 @@ int a4c_bmm_i8(const void* A, int64_t lda, int64_t stride_a, const int8_t* B, in
     return finish();
 }
 
+int a4c_set_option(int option, int value) {
+    if (option == A4C_OPT_ROWOP_PATH && (value == 0 || value == 1)) {
+        g_rowop_path = value;
+        return A4C_OK;
+    }
+    return A4C_ERR_INVALID_ARG;
+}
+
 int a4c_layernorm_i8(const int8_t* x, int64_t ldx, const int16_t* gamma, const int16_t* beta,
                      const int8_t* addend, int64_t ldadd, int8_t* out, int64_t ldo, int64_t rows, int cols,
-                     int eps_q0, int out_shift, int rounding, void* stream) {
+                     int eps_q0, int out_shift, int rounding, int gamma_absmax, void* stream) {
     if (x == nullptr || gamma == nullptr || beta == nullptr || out == nullptr) return A4C_ERR_INVALID_ARG;
     if (ldx < cols || ldo < cols || (addend && ldadd < cols)) return A4C_ERR_INVALID_ARG;
+    if (g_rowop_path == 0 && rows > 0 && cols >= 16 && (cols & (cols - 1)) == 0 && out_shift >= 0 && out_shift <= 15 &&
+        eps_q0 >= 1 && valid_round(rounding) && cols % 16 == 0 && ldx % 16 == 0 && ldo % 16 == 0 &&
+        (((uintptr_t)x | (uintptr_t)out | (uintptr_t)gamma | (uintptr_t)beta) & 15u) == 0 &&
+        (!addend || (ldadd % 16 == 0 && ((uintptr_t)addend & 15u) == 0))) {
+        const int frc = a4c_launch_layernorm_fast(x, ldx, gamma, beta, addend, ldadd, out, ldo, rows, cols, eps_q0,
+                                                  out_shift, rounding, gamma_absmax, status_word(), (cudaStream_t)stream);
+        if (frc == A4C_OK) return finish();
+        if (frc != A4C_ERR_UNSUPPORTED) return frc;
+    }
     const int rc = a4c_launch_layernorm(x, ldx, gamma, beta, addend, ldadd, out, ldo, rows, cols, eps_q0, out_shift,
                                         rounding, (cudaStream_t)stream);
     if (rc != A4C_OK) return rc;
@@ -139,6 +157,16 @@ int a4c_softmax_i8(const int8_t* x, int64_t ldx, const void* addend, int64_t lda
                    int exp_kq, int out_dtype, void* stream) {
     if (x == nullptr || out == nullptr) return A4C_ERR_INVALID_ARG;
     if (ldx < cols || ldo < cols || (addend && ldadd < cols)) return A4C_ERR_INVALID_ARG;
+    if (g_rowop_path == 0 && rows > 0 && cols >= 16 && cols % 16 == 0 && (mode == 0 || mode == 1) && out_dtype == A4C_U8 &&
+        inv_shift >= 1 && ldx % 16 == 0 && ldo % 16 == 0 && (((uintptr_t)x | (uintptr_t)out) & 15u) == 0 &&
+        (!addend || (ldadd % 16 == 0 && ((uintptr_t)addend & 15u) == 0)) &&
+        (mode == 1 ? (exp_kq >= 1 && exp_kq <= 128)
+                   : (B >= 0 && B <= 32767 && S >= 0 && S <= 127 && Dmax >= 0 && Dmax <= 255))) {
+        const int frc = a4c_launch_softmax_fast(x, ldx, addend, ldadd, out, ldo, rows, cols, mode, B, S, Dmax, inv_shift,
+                                                use_clb, exp_kq, out_dtype, status_word(), (cudaStream_t)stream);
+        if (frc == A4C_OK) return finish();
+        if (frc != A4C_ERR_UNSUPPORTED) return frc;
+    }
     const int rc = a4c_launch_softmax(x, ldx, addend, ldadd, out, ldo, rows, cols, mode, B, S, Dmax, inv_shift,
                                       use_clb, exp_kq, out_dtype, (cudaStream_t)stream);
     if (rc != A4C_OK) return rc;

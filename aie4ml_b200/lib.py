@@ -23,6 +23,7 @@ A4C_ERR_TOO_LARGE = -5
 A4C_ERR_DEVICE_TIMEOUT = -6
 
 ALGO_AUTO, ALGO_SIMT, ALGO_TCGEN05 = 0, 1, 2
+OPT_ROWOP_PATH = 0
 
 # name -> (restype, argtypes); mirrors the header declaration by declaration
 SIGNATURES = {
@@ -35,7 +36,8 @@ SIGNATURES = {
     'a4c_bmm_i8': (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'a4c_layernorm_i8': (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64,
-                                 c_int, c_int, c_int, c_int, c_void_p]),
+                                 c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    'a4c_set_option': (c_int, [c_int, c_int]),
     'a4c_softmax_i8': (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int, c_int, c_int,
                                c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'a4c_add_sat': (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_int,

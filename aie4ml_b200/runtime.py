@@ -325,7 +325,7 @@ class Plan:
             if kind == 'layer_norm':
                 args = (self.ptr(x, x_off), ldx, self.params[op['gamma']].data_ptr(), self.params[op['beta']].data_ptr(),
                         add_ptr, ldadd, self.ptr(y, y_off), ldy, rows, cols, op['eps_q0'], op['out_shift'],
-                        ROUNDING_CODE[op['rounding']])
+                        ROUNDING_CODE[op['rounding']], int(np.abs(self.params_np[op['gamma']].astype(np.int64)).max()))
                 return L.a4c_layernorm_i8, args
             if kind == 'softmax':
                 args = (self.ptr(x, x_off), ldx, add_ptr, ldadd, self.ptr(y, y_off), ldy, rows, cols,

@@ -49,6 +49,9 @@ extern "C" {
 #define A4C_ALGO_SIMT 1      /* dp4a tiles, any shape / stride */
 #define A4C_ALGO_TCGEN05 2   /* tcgen05 + TMA + TMEM, one CTA per 128x256 tile */
 
+/* Options for a4c_set_option */
+#define A4C_OPT_ROWOP_PATH 0 /* 0 = auto (bandwidth-oriented row kernels when they apply), 1 = generic kernels only */
+
 /* Library version (major*10000 + minor*100 + patch). */
 A4C_API int a4c_version(void);
 
@@ -58,11 +61,14 @@ A4C_API const char* a4c_error_string(int code);
 /* Text of the last CUDA runtime error seen by this library on the calling thread (static storage). */
 A4C_API const char* a4c_last_cuda_error(void);
 
+/* Process-wide tuning / debugging switch; returns A4C_ERR_INVALID_ARG for an unknown option or value. */
+A4C_API int a4c_set_option(int option, int value);
+
 /*
  * Reads (and clears) the current device's kernel status word after synchronising `stream`.
  * 0 = every bounded device-side wait completed; otherwise the code of the first wait that gave up
  * (101 producer/empty slot, 102 MMA/accumulator free, 103 MMA/operands landed, 104 epilogue/accumulator
- * ready).  Returns A4C_OK, or A4C_ERR_DEVICE_TIMEOUT when *status != 0, or A4C_ERR_CUDA.
+ * ready, 201 / 202 row of a LayerNorm / Softmax input landed).  Returns A4C_OK, or A4C_ERR_DEVICE_TIMEOUT when *status != 0, or A4C_ERR_CUDA.
  */
 A4C_API int a4c_device_status(int* status, void* stream);
 
@@ -104,10 +110,13 @@ A4C_API int a4c_bmm_i8(const void* A, int64_t lda, int64_t stride_a, const int8_
  * GAMMA_SHIFT is the constant 7).  gamma is int16 Q7, beta int16 Q15, both [cols].
  * addend (or NULL): an int8 tensor shaped like the output; when given, the kernel stores
  * saturate(layernorm(x) + addend) -- the exact-type Add of elementwise_add.cpp:12-37 fused in.
+ * gamma_absmax: an upper bound of |gamma[c]| known to the caller (the packer has it), or 0 when unknown.
+ * It only selects between kernels (a bound <= 16383 admits the bandwidth-oriented one); results do not
+ * depend on it as long as it is a true bound.
  */
 A4C_API int a4c_layernorm_i8(const int8_t* x, int64_t ldx, const int16_t* gamma, const int16_t* beta,
                      const int8_t* addend, int64_t ldadd, int8_t* out, int64_t ldo, int64_t rows, int cols,
-                     int eps_q0, int out_shift, int rounding, void* stream);
+                     int eps_q0, int out_shift, int rounding, int gamma_absmax, void* stream);
 
 /*
  * Quantized Softmax over rows of int8, output uint8 (dtype 1) or int16 (dtype 2).

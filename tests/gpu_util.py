@@ -81,7 +81,8 @@ def layer_norm(x, gamma, beta, *, eps_q0, out_shift, tok, addend=None):
     a_d = dev(addend) if addend is not None else None
     o_d = torch.zeros((rows, cols), dtype=torch.int8, device='cuda')
     rc = L.a4c_layernorm_i8(x_d.data_ptr(), cols, g_d.data_ptr(), b_d.data_ptr(), a_d.data_ptr() if a_d is not None else None,
-                            cols, o_d.data_ptr(), cols, rows, cols, eps_q0, out_shift, ROUNDING_CODE[tok], stream())
+                            cols, o_d.data_ptr(), cols, rows, cols, eps_q0, out_shift, ROUNDING_CODE[tok],
+                            int(np.abs(gamma.astype(np.int64)).max()), stream())
     a4c.check(rc, 'a4c_layernorm_i8')
     return o_d.cpu().numpy()
 

@@ -110,6 +110,18 @@ def test_bmm_attention_shapes():
                                   oracle.matmul(a, b, shift=4, tok='floor', transpose_a=True, out_dtype='int16'))
 
 
+@pytest.fixture(params=['auto', 'generic'])
+def rowop_path(request):
+    """Runs a row-op test once with automatic kernel selection (bandwidth-oriented kernels where they
+    apply) and once with the generic integer kernels forced."""
+    from aie4ml_b200 import lib as a4c
+
+    L = a4c.load()
+    assert L.a4c_set_option(a4c.OPT_ROWOP_PATH, 0 if request.param == 'auto' else 1) == 0
+    yield request.param
+    assert L.a4c_set_option(a4c.OPT_ROWOP_PATH, 0) == 0
+
+
 def _ln_inputs(seed, rows, cols):
     rng = np.random.default_rng(seed)
     x = np.clip(np.rint(rng.normal(2, 32, (rows, cols))), -128, 127).astype(np.int8)
@@ -122,27 +134,30 @@ def _ln_inputs(seed, rows, cols):
 
 
 @pytest.mark.parametrize('cols', [32, 64, 256, 1024, 4096])
-@pytest.mark.parametrize('tok', ['positive_inf', 'conv_even', 'floor', 'symmetric_inf'])
-def test_layer_norm(cols, tok):
+@pytest.mark.parametrize('tok', ['positive_inf', 'conv_even', 'floor', 'ceil', 'negative_inf', 'symmetric_inf'])
+def test_layer_norm(cols, tok, rowop_path):
     import gpu_util as G
 
     x, rng = _ln_inputs(cols, 77, cols)
     gamma = rng.integers(-256, 257, cols)
     beta = rng.integers(-256, 257, cols)
-    for out_shift in (4, 0, 15):
+    for out_shift in (4, 0, 13, 15):
         np.testing.assert_array_equal(G.layer_norm(x, gamma, beta, eps_q0=1, out_shift=out_shift, tok=tok),
                                       oracle.layer_norm(x, gamma, beta, eps_q0=1, out_shift=out_shift, tok=tok))
     big_g = rng.integers(-32768, 32768, cols)
     big_b = rng.integers(-32768, 32768, cols)
     np.testing.assert_array_equal(G.layer_norm(x, big_g, big_b, eps_q0=3, out_shift=6, tok=tok),
                                   oracle.layer_norm(x, big_g, big_b, eps_q0=3, out_shift=6, tok=tok))
+    mid_g = rng.integers(-16383, 16384, cols)   # largest gamma the bandwidth-oriented kernel admits
+    np.testing.assert_array_equal(G.layer_norm(x, mid_g, big_b, eps_q0=1, out_shift=2, tok=tok),
+                                  oracle.layer_norm(x, mid_g, big_b, eps_q0=1, out_shift=2, tok=tok))
     addend = rng.integers(-128, 128, x.shape).astype(np.int8)
     fused = G.layer_norm(x, gamma, beta, eps_q0=1, out_shift=4, tok=tok, addend=addend)
     want = oracle.add(oracle.layer_norm(x, gamma, beta, eps_q0=1, out_shift=4, tok=tok), addend, out_dtype='int8')
     np.testing.assert_array_equal(fused, want)
 
 
-def test_layer_norm_every_rounding_mode():
+def test_layer_norm_every_rounding_mode(rowop_path):
     import gpu_util as G
 
     x, rng = _ln_inputs(5, 40, 256)
@@ -155,7 +170,7 @@ def test_layer_norm_every_rounding_mode():
 
 @pytest.mark.parametrize('cols', [32, 96, 128, 1024, 2048])
 @pytest.mark.parametrize('out_dtype', ['uint8', 'int16'])
-def test_softmax_both_modes(cols, out_dtype):
+def test_softmax_both_modes(cols, out_dtype, rowop_path):
     import gpu_util as G
 
     x, rng = _ln_inputs(cols + 1, 61, cols)
@@ -202,5 +217,5 @@ def test_empty_inputs_are_no_ops():
     p = buf.data_ptr()
     assert L.a4c_dense_i8(p, 64, p, 64, None, p, 64, 0, 64, 64, 7, 2, 0, 0, 0, 0, G.stream()) == 0
     assert L.a4c_add_sat(p, 64, p, 64, p, 64, 0, 64, 0, 6, 0, G.stream()) == 0
-    assert L.a4c_layernorm_i8(p, 64, p, p, None, 0, p, 64, 0, 64, 1, 4, 6, G.stream()) == 0
+    assert L.a4c_layernorm_i8(p, 64, p, p, None, 0, p, 64, 0, 64, 1, 4, 6, 0, G.stream()) == 0
     assert L.a4c_softmax_i8(p, 64, None, 0, p, 64, 0, 64, 1, 0, 0, 0, 15, 0, 23, 1, G.stream()) == 0
