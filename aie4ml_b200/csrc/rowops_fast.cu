@@ -1,21 +1,24 @@
 // Bandwidth-oriented LayerNorm and Softmax row kernels (the common cases of rowops.cu).
 //
-// Data movement: every warp owns a ring of row slots in shared memory that is filled by bulk
-// asynchronous copies (cp.async.bulk, completion on an mbarrier), so many rows per SM are in flight
-// without holding registers; results leave through 128-bit global stores.
+// Data movement: every warp owns a ring of slots in shared memory that is filled by bulk asynchronous
+// copies (cp.async.bulk, completion on an mbarrier): the input rows and, when a saturating Add is fused,
+// the addend rows.  Many rows per SM are in flight without holding registers, nothing in the row loop waits
+// on a global load, and results leave through 128-bit global stores.
 //
 // Arithmetic: the integer recipes of the aie4ml kernels (layer_norm.cpp:15-121, softmax.cpp:20-88 and
 // :252-384) are evaluated on the FP32 pipe where that is provably exact:
 //   * an integer n with |n| < 2^22 is carried as the float MAGIC + n (MAGIC = 1.5 * 2^23), whose low
 //     mantissa bits are n in two's complement;
-//   * round(v / 2^s) for the rounding modes floor / ceil / half-up / half-down / half-even is ONE fused
-//     multiply-add fma(v, 2^-s, MAGIC [+ folded constant]) with the matching IEEE rounding direction:
-//     the FMA forms v * 2^-s + MAGIC exactly and rounds once, to an integer because ulp(2^23..2^24) = 1;
+//   * round(v / 2^s) for floor / ceil / half-up / half-down / half-even is ONE fused multiply-add with the
+//     matching IEEE rounding direction (constants of the floor-type modes folded into an addend): the FMA
+//     forms the exact product and rounds once;
+//   * the final rounding writes into a SUBNORMAL: fma(v * 2^-64, 2^-(s+85), 0) has the bit pattern
+//     sign | round(v / 2^s), so the integer result needs no conversion, and min.s32.relu clamps it to
+//     [0, 255] in one instruction (outputs are produced biased by +128 and un-biased with one XOR per word);
 //   * products such as (x - mu) * fscale + beta stay below 2^24 in magnitude, so they are exact.
 // Modes or parameters outside those proofs (symmetric rounding, conv_odd, |gamma| > 16383, shifts < 2,
-// int16 softmax output, negative HCCS scores, inv_shift > 22) take the generic integer kernels.
-#include <mutex>
-
+// int16 softmax output, negative HCCS scores, inv_shift > 22, rows longer than 2048 / 1024) take the generic
+// integer kernels of rowops.cu.
 #include "a4c_common.cuh"
 #include "a4c_kernels.h"
 
@@ -23,28 +26,45 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr int kStages = 4;
-constexpr float MAGIC = 12582912.0f;          // 1.5 * 2^23
+constexpr float MAGIC = 12582912.0f;               // 1.5 * 2^23
 constexpr uint32_t MAGIC_BITS = 0x4B400000u;
+constexpr float TWO_M64 = 5.421010862427522e-20f;  // 2^-64
+constexpr float TWO_P64 = 18446744073709551616.0f; // 2^64
 
+// ---- shared-memory / barrier primitives on 32-bit shared addresses ----------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count) : "memory");
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
 }
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
+__device__ __forceinline__ float4 lds128f(uint32_t a) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
+    return v;
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ float lds32f(uint32_t a) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
 // Bounded wait; on timeout records `code` in the status word and returns false.
-__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int* status, int code) {
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int* status, int code) {
     const uint64_t t0 = a4c_globaltimer();
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -54,22 +74,16 @@ __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int*
         }
     }
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
     if (mbar_try_wait(bar, parity)) return true;
     return mbar_wait_slow(bar, parity, status, code);
 }
-__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 :: "r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+                 :: "r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void stg16(void* p, uint4 v) {
     asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
-__device__ __forceinline__ uint4 ldg16(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
 }
 __device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {
     int d;
@@ -83,56 +97,46 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
     return d;
 }
-// float 2^23 + byte k of w (bytes taken as unsigned)
+// float 2^23 + byte K of w (bytes taken as unsigned)
 template <int K>
 __device__ __forceinline__ float byte_to_f23(uint32_t w) {
-    // result bytes: [w.bK, 0x00, 0x00, 0x4B]; second operand 0x4B000000 supplies bytes 4..7
     return __uint_as_float(prmt(w, 0x4B000000u, 0x7540 + K));
-}
-// pack the low bytes of four MAGIC-offset floats
-__device__ __forceinline__ uint32_t pack_low_bytes(float a, float b, float c, float d) {
-    const uint32_t ab = prmt(__float_as_uint(a), __float_as_uint(b), 0x0040);  // [a0, b0, a0, a0]
-    const uint32_t cd = prmt(__float_as_uint(c), __float_as_uint(d), 0x0040);
-    return prmt(ab, cd, 0x5410);                                              // [a0, b0, c0, d0]
 }
 
 struct RowGeom {
     int nchunks, G, R;
 };
 
-// A warp's view of the row ring: items of R rows each, loaded ahead by kStages.
-struct RingCtx {
-    uint8_t* slots;      // this warp's kStages slots
-    uint64_t* bars;      // this warp's kStages barriers
-    int slot_bytes;      // R * cols
-    const uint8_t* src;  // global base of the input
-    long long ld;        // input row pitch (bytes, int8 elements)
+// One warp's ring.  A slot holds R input rows and, with a fused Add, R addend rows behind them.
+struct Ring {
+    uint32_t slots;   // shared address of slot 0
+    uint32_t bars;    // shared address of barrier 0
+    uint32_t slot_bytes;
+    uint32_t add_off; // offset of the addend rows inside a slot
+    const uint8_t* x; long long ldx;
+    const uint8_t* addend; long long ldadd;  // byte pitch
     long long rows;
-    int cols, R;
+    uint32_t row_bytes, add_row_bytes;
+    int R;
 };
 
-__device__ __forceinline__ void ring_issue(const RingCtx& c, long long item, int stage) {
-    // lane 0 only
+// lane 0 only
+__device__ __forceinline__ void ring_issue(const Ring& c, long long item, int stage) {
     const long long row0 = item * c.R;
     long long nrows = c.rows - row0;
     if (nrows > c.R) nrows = c.R;
-    if (nrows <= 0) return;
-    mbar_expect_tx(&c.bars[stage], (uint32_t)(nrows * c.cols));
-    for (int r = 0; r < (int)nrows; ++r)
-        bulk_load(c.slots + (size_t)stage * c.slot_bytes + (size_t)r * c.cols, c.src + (row0 + r) * c.ld,
-                  (uint32_t)c.cols, &c.bars[stage]);
+    const uint32_t bar = c.bars + stage * 8;
+    const uint32_t dst = c.slots + stage * c.slot_bytes;
+    mbar_expect_tx(bar, (uint32_t)nrows * (c.row_bytes + (c.addend ? c.add_row_bytes : 0u)));
+    for (int r = 0; r < (int)nrows; ++r) {
+        bulk_load(dst + r * c.row_bytes, c.x + (row0 + r) * c.ldx, c.row_bytes, bar);
+        if (c.addend) bulk_load(dst + c.add_off + r * c.add_row_bytes, c.addend + (row0 + r) * c.ldadd, c.add_row_bytes, bar);
+    }
 }
 
 // ------------------------------------------------------------------------------------------------
 // LayerNorm
 // ------------------------------------------------------------------------------------------------
-// Further exactness facts used below:
-//   * a float whose exponent field is zero (a subnormal) has the bit pattern sign | n with value
-//     n * 2^-149, so fma(v * 2^-64, 2^-(s+85), 0) with a directed or nearest-even rounding mode leaves
-//     round(v / 2^s) directly in the low bits, sign-magnitude; min.s32.relu then clamps it to [0, 255] in one
-//     instruction.  Outputs are produced biased by +128 (folded into beta) and un-biased with one XOR per word.
-constexpr float TWO_M64 = 5.421010862427522e-20f;   // 2^-64
-
 struct LnFastArgs {
     const int8_t* x; long long ldx;
     const int16_t* gamma; const int16_t* beta;
@@ -143,18 +147,12 @@ struct LnFastArgs {
     int c0_gamma;       // rounding constant of the (>> 7) step for the floor-type modes
     float c0_out;       // rounding constant + output bias (128 << s_out), folded into beta
     int gamma_absmax;
+    int stages;
     RowGeom geom;
     int* status;
 };
 
-// Q15 reciprocal standard deviation for every variance the int8 kernel can see (var <= 128^2 + eps), one table
-// per rounding token, filled on the device by the defining expression
-//   clamp(round_tok(2^15 * (1.0f / sqrtf((float)var))), 0, 32767)        (layer_norm.cpp:33-39)
-// so the row loop replaces a correctly rounded sqrt + divide + rounding by one cached load.
-constexpr int kInvStdMaxEps = 1024;
-constexpr int kInvStdEntries = 16384 + kInvStdMaxEps + 1;
-__device__ int16_t g_inv_std_table[A4C_RND_COUNT][kInvStdEntries];
-
+// Round a non-negative binary32 value to an integer with an AIE rounding token.
 __device__ __forceinline__ int round_float_tok(float f, int tok) {
     const float fl = floorf(f);
     const float frac = f - fl;
@@ -171,60 +169,71 @@ __device__ __forceinline__ int round_float_tok(float f, int tok) {
     }
 }
 
-__global__ void build_inv_std_table_kernel(int tok) {
-    const int var = blockIdx.x * blockDim.x + threadIdx.x;
-    if (var >= kInvStdEntries) return;
-    int q = 32767;
-    if (var > 0) {
-        const float inv_f32 = __fdiv_rn(1.0f, __fsqrt_rn(__int2float_rn(var)));
-        q = clampi(round_float_tok(__fmul_rn(inv_f32, 32768.0f), tok), 0, 32767);
-    }
-    g_inv_std_table[tok][var] = (int16_t)q;
+// The defining expression of the Q15 reciprocal standard deviation (layer_norm.cpp:33-39):
+// clamp(round_tok(2^15 * (1.0f / sqrtf((float)var))), 0, 32767) with correctly rounded sqrt and divide.
+__device__ __noinline__ int inv_std_exact(int var, int tok) {
+    const float inv_f32 = __fdiv_rn(1.0f, __fsqrt_rn(__int2float_rn(var)));
+    return clampi(round_float_tok(__fmul_rn(inv_f32, 32768.0f), tok), 0, 32767);
 }
 
-// position of column c in the lane-major parameter arrays: lanes of a row group read consecutive 16-byte
-// quads for a fixed (chunk index j, word w), so the 128-bit shared loads are conflict-free
-__device__ __forceinline__ int param_pos(int c, int G) {
-    const int chunk = c >> 4, w = (c >> 2) & 3, k = c & 3;
-    const int j = chunk / G, gl = chunk % G;
-    return (((j * 4 + w) * G + gl) << 2) + k;
+// Same value, usually in a handful of instructions: y ~= 2^15 * rsqrt(var) from the approximate unit is within
+// 0.02 of the exactly rounded product (both relative errors are below 2^-21.4 and y <= 32768); unless y sits
+// that close to a rounding boundary of the mode, rounding y gives the defined result.  The rare boundary cases
+// (and var < 4, where the clamp is near) take the exact path.
+__device__ __forceinline__ int inv_std_q15(int var, int tok, bool nearest) {
+    float y;
+    asm("rsqrt.approx.f32 %0, %1;" : "=f"(y) : "f"(__int2float_rn(var)));
+    y *= 32768.0f;
+    const float fl = floorf(y);
+    const float frac = y - fl;
+    const float dist = nearest ? fabsf(frac - 0.5f) : fminf(frac, 1.0f - frac);
+    if (dist < 0.02f || var < 4) return inv_std_exact(var, tok);
+    int q = (int)fl;
+    if (nearest) q += frac > 0.5f;
+    else if (tok == A4C_RND_CEIL) q += 1;
+    return q;
 }
 
 // FS = 0: conv_even, fscale = rne(inv_std * gamma / 128) in one nearest-even FMA
 // FS = 1: floor-type modes with |gamma| <= 511: inv_std * gamma + c0 is exact in FP32, then one round-down FMA
 // FS = 2: floor-type modes with larger gamma: integer multiply-add and shift
-template <int NCH, int FS>
+template <int NCH, int FS, bool HAS_ADD>
 __global__ void __launch_bounds__(kThreads) layernorm_fast_kernel(LnFastArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
+    // layout: gamma[NCH*4*32*4] | beta[same] | barriers | ring.  Parameters are stored lane-major: position
+    // ((j*4 + w)*32 + lane)*4 + k holds column (j*G + lane)*16 + w*4 + k, so for fixed (j, w) a row group reads
+    // consecutive 16-byte quads (conflict-free) at an offset that is a compile-time constant.
+    constexpr int kParamFloats = NCH * 4 * 32 * 4;
+    const uint32_t s_base = smem_u32(smem);
+    const uint32_t s_gam = s_base, s_bet = s_base + kParamFloats * 4, s_bar = s_base + kParamFloats * 8;
     const int cols = a.cols;
-    float* gam_f = reinterpret_cast<float*>(smem);                      // FS 0: gamma/128, FS 1: gamma
-    int* gam_i = reinterpret_cast<int*>(smem);                          // FS 2: gamma
-    float* bet_f = reinterpret_cast<float*>(smem + (size_t)cols * 4);   // (beta + constants) * 2^-64
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)cols * 8);
-    uint8_t* ring = smem + (size_t)cols * 8 + kWarps * kStages * 8;
-    ring = reinterpret_cast<uint8_t*>(((uintptr_t)ring + 127) & ~(uintptr_t)127);
-
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int G = a.geom.G, R = a.geom.R;
     const int sub = lane / G, gl = lane % G;
     constexpr bool RN = FS == 0;
 
     for (int c = threadIdx.x; c < cols; c += kThreads) {
+        const int chunk = c >> 4, w = (c >> 2) & 3, k = c & 3;
+        const int pos = (((chunk / G) * 4 + w) * 32 + (chunk % G)) * 4 + k;
         const int g = a.gamma[c];
-        const int pos = param_pos(c, G);
-        if (FS == 0) gam_f[pos] = (float)g * 0.0078125f;
-        else if (FS == 1) gam_f[pos] = (float)g;
-        else gam_i[pos] = g;
-        bet_f[pos] = ((float)a.beta[c] + a.c0_out) * TWO_M64;
+        if (FS == 0) reinterpret_cast<float*>(smem)[pos] = (float)g * 0.0078125f;
+        else if (FS == 1) reinterpret_cast<float*>(smem)[pos] = (float)g;
+        else reinterpret_cast<int*>(smem)[pos] = g;
+        reinterpret_cast<float*>(smem)[kParamFloats + pos] = ((float)a.beta[c] + a.c0_out) * TWO_M64;
     }
-    RingCtx rc;
-    rc.slot_bytes = R * cols;
-    rc.slots = ring + (size_t)warp * kStages * rc.slot_bytes;
-    rc.bars = bars + warp * kStages;
-    rc.src = reinterpret_cast<const uint8_t*>(a.x);
-    rc.ld = a.ldx; rc.rows = a.rows; rc.cols = cols; rc.R = R;
+    Ring rc;
+    rc.R = R;
+    rc.row_bytes = (uint32_t)cols; rc.add_row_bytes = (uint32_t)cols;
+    rc.add_off = (uint32_t)(R * cols);
+    rc.slot_bytes = (uint32_t)(R * cols) * (HAS_ADD ? 2u : 1u);
+    rc.bars = s_bar + warp * a.stages * 8;
+    const uint32_t ring0 = (s_bar + kWarps * a.stages * 8 + 127u) & ~127u;
+    rc.slots = ring0 + warp * a.stages * rc.slot_bytes;
+    rc.x = reinterpret_cast<const uint8_t*>(a.x); rc.ldx = a.ldx;
+    rc.addend = HAS_ADD ? reinterpret_cast<const uint8_t*>(a.addend) : nullptr; rc.ldadd = a.ldadd;
+    rc.rows = a.rows;
     if (lane == 0)
-        for (int s = 0; s < kStages; ++s) mbar_init(&rc.bars[s], 1);
+        for (int s = 0; s < a.stages; ++s) mbar_init(rc.bars + s * 8, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
 
@@ -232,7 +241,7 @@ __global__ void __launch_bounds__(kThreads) layernorm_fast_kernel(LnFastArgs a) 
     const long long warp_global = (long long)blockIdx.x * kWarps + warp;
     const long long total_warps = (long long)gridDim.x * kWarps;
     if (lane == 0)
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < a.stages; ++s) {
             const long long it = warp_global + (long long)s * total_warps;
             if (it < n_items) ring_issue(rc, it, s);
         }
@@ -240,89 +249,90 @@ __global__ void __launch_bounds__(kThreads) layernorm_fast_kernel(LnFastArgs a) 
     const float out_mul = __int_as_float((127 - (a.s_out + 85)) << 23);  // 2^-(s_out + 85)
     const float c0g = (float)a.c0_gamma;
     const uint32_t group_mask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (sub * G));
-    const int16_t* inv_table = g_inv_std_table[a.rounding];
     const int clamp_threshold = (32767 * 128) / a.gamma_absmax;  // inv_std above this may overflow int16
-    const bool has_add = a.addend != nullptr;
+    const bool nearest = a.rounding == A4C_RND_CONV_EVEN || a.rounding == A4C_RND_POSITIVE_INF ||
+                         a.rounding == A4C_RND_NEGATIVE_INF;
+    const uint32_t lane_in_slot = (uint32_t)(sub * cols + gl * 16);
+    const uint32_t lane_param = (uint32_t)gl * 16u;
+    const long long step_rows = total_warps * R;
+    long long row = warp_global * R + sub;
     int stage = 0;
     uint32_t parity = 0;
-    for (long long item = warp_global; item < n_items; item += total_warps) {
-        if (!__all_sync(0xffffffffu, mbar_wait(&rc.bars[stage], parity, a.status, 201))) break;
-        const long long row = item * R + sub;
+    for (long long item = warp_global; item < n_items; item += total_warps, row += step_rows) {
+        if (!mbar_wait(rc.bars + stage * 8, parity, a.status, 201)) break;
         const bool row_ok = row < a.rows;
-        uint4 xv[NCH];
-        const uint8_t* slot = rc.slots + (size_t)stage * rc.slot_bytes + (size_t)sub * cols;
+        uint4 xv[NCH], av[NCH];
+        const uint32_t slot = rc.slots + stage * rc.slot_bytes + lane_in_slot;
 #pragma unroll
         for (int j = 0; j < NCH; ++j) {
-            const int chunk = j * G + gl;
-            xv[j] = (row_ok && chunk < a.geom.nchunks) ? *reinterpret_cast<const uint4*>(slot + chunk * 16)
-                                                        : make_uint4(0, 0, 0, 0);
+            const bool ok = row_ok && (j * G + gl) < a.geom.nchunks;
+            xv[j] = ok ? lds128(slot + j * G * 16) : make_uint4(0, 0, 0, 0);
+            if (HAS_ADD) av[j] = ok ? lds128(slot + rc.add_off + j * G * 16) : make_uint4(0, 0, 0, 0);
         }
         __syncwarp();
         if (lane == 0) {
-            const long long nxt = item + (long long)kStages * total_warps;
+            const long long nxt = item + (long long)a.stages * total_warps;
             if (nxt < n_items) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 ring_issue(rc, nxt, stage);
             }
         }
-        if (++stage == kStages) { stage = 0; parity ^= 1u; }
+        if (++stage == a.stages) { stage = 0; parity ^= 1u; }
 
-        int sum_x = 0, sum_sq = 0;
+        int sx0 = 0, sx1 = 0, sq0 = 0, sq1 = 0;  // two accumulator chains each
 #pragma unroll
         for (int j = 0; j < NCH; ++j) {
-            sum_x = dp4a_ss(xv[j].x, 0x01010101u, sum_x); sum_sq = dp4a_ss(xv[j].x, xv[j].x, sum_sq);
-            sum_x = dp4a_ss(xv[j].y, 0x01010101u, sum_x); sum_sq = dp4a_ss(xv[j].y, xv[j].y, sum_sq);
-            sum_x = dp4a_ss(xv[j].z, 0x01010101u, sum_x); sum_sq = dp4a_ss(xv[j].z, xv[j].z, sum_sq);
-            sum_x = dp4a_ss(xv[j].w, 0x01010101u, sum_x); sum_sq = dp4a_ss(xv[j].w, xv[j].w, sum_sq);
+            sx0 = dp4a_ss(xv[j].x, 0x01010101u, sx0); sq0 = dp4a_ss(xv[j].x, xv[j].x, sq0);
+            sx1 = dp4a_ss(xv[j].y, 0x01010101u, sx1); sq1 = dp4a_ss(xv[j].y, xv[j].y, sq1);
+            sx0 = dp4a_ss(xv[j].z, 0x01010101u, sx0); sq0 = dp4a_ss(xv[j].z, xv[j].z, sq0);
+            sx1 = dp4a_ss(xv[j].w, 0x01010101u, sx1); sq1 = dp4a_ss(xv[j].w, xv[j].w, sq1);
         }
-        sum_x = __reduce_add_sync(group_mask, sum_x);
-        sum_sq = __reduce_add_sync(group_mask, sum_sq);
+        const int sum_x = __reduce_add_sync(group_mask, sx0 + sx1);
+        const int sum_sq = __reduce_add_sync(group_mask, sq0 + sq1);
+        // layer_norm.cpp:23-31
         const int mu = (sum_x + (cols >> 1)) >> a.log2c;
         const int centered = (int)((uint32_t)sum_sq - 2u * (uint32_t)mu * (uint32_t)sum_x +
                                    (uint32_t)cols * (uint32_t)mu * (uint32_t)mu);
         int var = centered >> a.log2c;
-        var = max(var, 0) + a.eps_q0;             // <= 16384 + eps_q0 for int8 rows
-        const int inv_std = inv_table[min(var, kInvStdEntries - 1)];
+        var = max(var, 0) + a.eps_q0;
+        const int inv_std = inv_std_q15(var, a.rounding, nearest);
         const float inv_f = (float)inv_std;
         // fscale can leave int16 only when inv_std * max|gamma| / 128 exceeds 32767
         const bool need_clamp = __any_sync(0xffffffffu, inv_std > clamp_threshold);
         const float vdc = 8388608.0f + 128.0f + (float)mu;  // (2^23 + (x ^ 0x80)) - vdc = x - mu
+        uint8_t* orow = reinterpret_cast<uint8_t*>(a.out) + row * a.ldo + gl * 16;
 
 #pragma unroll
         for (int j = 0; j < NCH; ++j) {
-            const int chunk = j * G + gl;
-            if (!(row_ok && chunk < a.geom.nchunks)) continue;
+            if (!(row_ok && (j * G + gl) < a.geom.nchunks)) continue;
             const uint32_t xw[4] = {xv[j].x ^ 0x80808080u, xv[j].y ^ 0x80808080u, xv[j].z ^ 0x80808080u,
                                     xv[j].w ^ 0x80808080u};
             uint32_t aw[4] = {0, 0, 0, 0};
-            if (has_add) {
-                const uint4 av = ldg16(a.addend + row * a.ldadd + (long long)chunk * 16);
-                aw[0] = av.x; aw[1] = av.y; aw[2] = av.z; aw[3] = av.w;
-            }
+            if (HAS_ADD) { aw[0] = av[j].x; aw[1] = av[j].y; aw[2] = av[j].z; aw[3] = av[j].w; }
             uint32_t ow[4];
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
-                const int pos = ((j * 4 + w) * G + gl) << 2;
-                const float4 bq = *reinterpret_cast<const float4*>(bet_f + pos);
+                const uint32_t poff = lane_param + (uint32_t)((j * 4 + w) * 32 * 16);
+                const float4 bq = lds128f(s_bet + poff);
                 const float bet[4] = {bq.x, bq.y, bq.z, bq.w};
                 float F[4];
                 if (FS == 0) {
-                    const float4 gq = *reinterpret_cast<const float4*>(gam_f + pos);
+                    const float4 gq = lds128f(s_gam + poff);
                     F[0] = __fmaf_rn(inv_f, gq.x, MAGIC); F[1] = __fmaf_rn(inv_f, gq.y, MAGIC);
                     F[2] = __fmaf_rn(inv_f, gq.z, MAGIC); F[3] = __fmaf_rn(inv_f, gq.w, MAGIC);
                 } else if (FS == 1) {
-                    const float4 gq = *reinterpret_cast<const float4*>(gam_f + pos);
+                    const float4 gq = lds128f(s_gam + poff);
                     // inv_std * gamma + c0 < 2^24 is exact; floor(. / 128) by a round-down FMA
                     F[0] = __fmaf_rd(__fmaf_rn(inv_f, gq.x, c0g), 0.0078125f, MAGIC);
                     F[1] = __fmaf_rd(__fmaf_rn(inv_f, gq.y, c0g), 0.0078125f, MAGIC);
                     F[2] = __fmaf_rd(__fmaf_rn(inv_f, gq.z, c0g), 0.0078125f, MAGIC);
                     F[3] = __fmaf_rd(__fmaf_rn(inv_f, gq.w, c0g), 0.0078125f, MAGIC);
                 } else {
-                    const int4 gq = *reinterpret_cast<const int4*>(gam_i + pos);
-                    F[0] = __uint_as_float((uint32_t)((inv_std * gq.x + a.c0_gamma) >> 7) + MAGIC_BITS);
-                    F[1] = __uint_as_float((uint32_t)((inv_std * gq.y + a.c0_gamma) >> 7) + MAGIC_BITS);
-                    F[2] = __uint_as_float((uint32_t)((inv_std * gq.z + a.c0_gamma) >> 7) + MAGIC_BITS);
-                    F[3] = __uint_as_float((uint32_t)((inv_std * gq.w + a.c0_gamma) >> 7) + MAGIC_BITS);
+                    const uint4 gq = lds128(s_gam + poff);
+                    F[0] = __uint_as_float((uint32_t)((inv_std * (int)gq.x + a.c0_gamma) >> 7) + MAGIC_BITS);
+                    F[1] = __uint_as_float((uint32_t)((inv_std * (int)gq.y + a.c0_gamma) >> 7) + MAGIC_BITS);
+                    F[2] = __uint_as_float((uint32_t)((inv_std * (int)gq.z + a.c0_gamma) >> 7) + MAGIC_BITS);
+                    F[3] = __uint_as_float((uint32_t)((inv_std * (int)gq.w + a.c0_gamma) >> 7) + MAGIC_BITS);
                 }
                 if (need_clamp) {
 #pragma unroll
@@ -335,14 +345,14 @@ __global__ void __launch_bounds__(kThreads) layernorm_fast_kernel(LnFastArgs a) 
                 for (int k = 0; k < 4; ++k) {
                     const float vd = xf[k] - vdc;                                      // x - mu, exact
                     const float fs = __fmaf_rn(F[k], TWO_M64, -MAGIC * TWO_M64);       // fscale * 2^-64, exact
-                    const float acc = __fmaf_rn(vd, fs, bet[k]);                       // (vd*fscale + beta + c) * 2^-64, exact
+                    const float acc = __fmaf_rn(vd, fs, bet[k]);                       // (vd*fscale + beta + c) * 2^-64
                     const float r = RN ? __fmaf_rn(acc, out_mul, 0.0f) : __fmaf_rd(acc, out_mul, 0.0f);
                     o[k] = __vimin_s32_relu(__float_as_int(r), 255);                   // clamp(round(.) + 128, 0, 255)
                 }
                 // two biased outputs per register as s16x2 lanes
                 uint32_t p01 = prmt((uint32_t)o[0], (uint32_t)o[1], 0x5410);
                 uint32_t p23 = prmt((uint32_t)o[2], (uint32_t)o[3], 0x5410);
-                if (has_add) {
+                if (HAS_ADD) {
                     // fused saturating Add (elementwise_add.cpp:30-33, SHIFT = 0): sign-extended addend pairs,
                     // packed add + min(., 255) + relu, two elements per instruction
                     p01 = __viaddmin_s16x2_relu(p01, prmt(aw[w], 0, 0x9180), 0x00FF00FFu);
@@ -350,7 +360,7 @@ __global__ void __launch_bounds__(kThreads) layernorm_fast_kernel(LnFastArgs a) 
                 }
                 ow[w] = prmt(p01, p23, 0x6420) ^ 0x80808080u;  // low bytes of the four lanes, un-biased
             }
-            stg16(a.out + row * a.ldo + (long long)chunk * 16, make_uint4(ow[0], ow[1], ow[2], ow[3]));
+            stg16(orow + j * G * 16, make_uint4(ow[0], ow[1], ow[2], ow[3]));
         }
     }
 }
@@ -364,10 +374,12 @@ struct SmFastArgs {
     uint8_t* out; long long ldo;
     long long rows; int cols;
     int mode, B, S, Dmax, inv_shift, use_clb, exp_kq;
+    int stages;
     RowGeom geom;
     int* status;
 };
 
+// exp_score16, softmax.cpp:252-273
 __device__ __forceinline__ int exp_score16(int d, int kq) {
     const int z = min(d * kq, 32767);
     const int zint = z >> 8, zfrac = z & 255;
@@ -379,33 +391,32 @@ __device__ __forceinline__ int exp_score16(int d, int kq) {
 }
 
 // score(d) * 2^-64 from the per-lane table: byte K of dw selects the table row (128 bytes per row, one float
-// per lane -> no bank conflicts); byte offset = (d << 7) | (lane * 4), added to the (warp-uniform) table base
+// per lane -> no bank conflicts).  lut_lane = table base + lane * 4 (shared address).
 template <int K>
-__device__ __forceinline__ float lut_at(const float* lut, uint32_t lane4, uint32_t dw) {
+__device__ __forceinline__ float lut_at(uint32_t lut_lane, uint32_t dw) {
     uint32_t sh;
     if (K == 0) sh = dw << 7;
     else if (K == 1) sh = dw >> 1;
     else if (K == 2) sh = dw >> 9;
     else sh = dw >> 17;
-    const uint32_t off = (sh & 0x7F80u) | lane4;
-    return *reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(lut) + off);
+    return lds32f((sh & 0x7F80u) + lut_lane);
 }
 
-template <int NCH>
+template <int NCH, bool HAS_ADD>
 __global__ void __launch_bounds__(kThreads) softmax_fast_kernel(SmFastArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
-    float* lut = reinterpret_cast<float*>(smem);  // [256][32] = 32 KB
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 256 * 32 * 4);
-    uint8_t* ring = smem + 256 * 32 * 4 + kWarps * kStages * 8;
-    ring = reinterpret_cast<uint8_t*>(((uintptr_t)ring + 127) & ~(uintptr_t)127);
-
+    // layout: score table [256][32] floats (32 KB) | barriers | ring
+    const uint32_t s_base = smem_u32(smem);
+    const uint32_t s_bar = s_base + 256 * 32 * 4;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int G = a.geom.G, R = a.geom.R, cols = a.cols;
     const int sub = lane / G, gl = lane % G;
+    const uint32_t ring0 = (s_bar + kWarps * a.stages * 8 + 127u) & ~127u;
     {
         // one score per thread (kThreads == 256 == table rows), staged in the ring area, then replicated
         // across the 32 lanes of each table row with conflict-free stores
-        float* stage_sc = reinterpret_cast<float*>(ring);
+        float* lut = reinterpret_cast<float*>(smem);
+        float* stage_sc = reinterpret_cast<float*>(smem + (ring0 - s_base));
         const int d = threadIdx.x;
         int s;
         if (a.mode == 0) s = clampi(a.B - a.S * min(d, a.Dmax), -32768, 32767);
@@ -415,14 +426,18 @@ __global__ void __launch_bounds__(kThreads) softmax_fast_kernel(SmFastArgs a) {
         for (int i = threadIdx.x; i < 256 * 32; i += kThreads) lut[i] = stage_sc[i >> 5];
         __syncthreads();
     }
-    RingCtx rc;
-    rc.slot_bytes = R * cols;
-    rc.slots = ring + (size_t)warp * kStages * rc.slot_bytes;
-    rc.bars = bars + warp * kStages;
-    rc.src = reinterpret_cast<const uint8_t*>(a.x);
-    rc.ld = a.ldx; rc.rows = a.rows; rc.cols = cols; rc.R = R;
+    Ring rc;
+    rc.R = R;
+    rc.row_bytes = (uint32_t)cols; rc.add_row_bytes = (uint32_t)cols;
+    rc.add_off = (uint32_t)(R * cols);
+    rc.slot_bytes = (uint32_t)(R * cols) * (HAS_ADD ? 2u : 1u);
+    rc.bars = s_bar + warp * a.stages * 8;
+    rc.slots = ring0 + warp * a.stages * rc.slot_bytes;
+    rc.x = reinterpret_cast<const uint8_t*>(a.x); rc.ldx = a.ldx;
+    rc.addend = HAS_ADD ? a.addend : nullptr; rc.ldadd = a.ldadd;
+    rc.rows = a.rows;
     if (lane == 0)
-        for (int s = 0; s < kStages; ++s) mbar_init(&rc.bars[s], 1);
+        for (int s = 0; s < a.stages; ++s) mbar_init(rc.bars + s * 8, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
 
@@ -430,44 +445,46 @@ __global__ void __launch_bounds__(kThreads) softmax_fast_kernel(SmFastArgs a) {
     const long long warp_global = (long long)blockIdx.x * kWarps + warp;
     const long long total_warps = (long long)gridDim.x * kWarps;
     if (lane == 0)
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < a.stages; ++s) {
             const long long it = warp_global + (long long)s * total_warps;
             if (it < n_items) ring_issue(rc, it, s);
         }
-    const uint32_t lane4 = (uint32_t)lane * 4u;
+    const uint32_t lut_lane = s_base + (uint32_t)lane * 4u;
     const int numer = 255 << a.inv_shift;  // inv_shift <= 22 on this path
     const float numer_f = (float)numer;     // exact: 255 * 2^k
-    const uint32_t group_mask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (sub * G));
     const float out_mul = __int_as_float((127 - (a.inv_shift + 85)) << 23);  // 2^-(inv_shift + 85)
-    const bool has_add = a.addend != nullptr;
+    const uint32_t group_mask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (sub * G));
+    const uint32_t lane_in_slot = (uint32_t)(sub * cols + gl * 16);
+    const long long step_rows = total_warps * R;
+    long long row = warp_global * R + sub;
 
     int stage = 0;
     uint32_t parity = 0;
-    for (long long item = warp_global; item < n_items; item += total_warps) {
-        if (!__all_sync(0xffffffffu, mbar_wait(&rc.bars[stage], parity, a.status, 202))) break;
-        const long long row = item * R + sub;
+    for (long long item = warp_global; item < n_items; item += total_warps, row += step_rows) {
+        if (!mbar_wait(rc.bars + stage * 8, parity, a.status, 202)) break;
         const bool row_ok = row < a.rows;
-        uint4 xv[NCH];
-        const uint8_t* slot = rc.slots + (size_t)stage * rc.slot_bytes + (size_t)sub * cols;
+        uint4 xv[NCH], av[NCH];
+        const uint32_t slot = rc.slots + stage * rc.slot_bytes + lane_in_slot;
 #pragma unroll
         for (int j = 0; j < NCH; ++j) {
-            const int chunk = j * G + gl;
+            const bool ok = row_ok && (j * G + gl) < a.geom.nchunks;
             // biased bytes (x ^ 0x80): unsigned order == signed order; padding = 0 (the minimum)
             xv[j] = make_uint4(0, 0, 0, 0);
-            if (row_ok && chunk < a.geom.nchunks) {
-                const uint4 v = *reinterpret_cast<const uint4*>(slot + chunk * 16);
+            if (ok) {
+                const uint4 v = lds128(slot + j * G * 16);
                 xv[j] = make_uint4(v.x ^ 0x80808080u, v.y ^ 0x80808080u, v.z ^ 0x80808080u, v.w ^ 0x80808080u);
             }
+            if (HAS_ADD) av[j] = ok ? lds128(slot + rc.add_off + j * G * 16) : make_uint4(0, 0, 0, 0);
         }
         __syncwarp();
         if (lane == 0) {
-            const long long nxt = item + (long long)kStages * total_warps;
+            const long long nxt = item + (long long)a.stages * total_warps;
             if (nxt < n_items) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 ring_issue(rc, nxt, stage);
             }
         }
-        if (++stage == kStages) { stage = 0; parity ^= 1u; }
+        if (++stage == a.stages) { stage = 0; parity ^= 1u; }
 
         // row maximum: even / odd bytes widened to u16x2 lanes, three-input packed maximum
         uint32_t mx = 0;
@@ -482,76 +499,67 @@ __global__ void __launch_bounds__(kThreads) softmax_fast_kernel(SmFastArgs a) {
 
         // scores (kept in registers for the normalisation pass) and their sum
         float e[NCH][16];
-        float fsum = 0.0f;
+        float fs0 = 0.0f, fs1 = 0.0f;
 #pragma unroll
         for (int j = 0; j < NCH; ++j) {
             const uint32_t w4[4] = {xv[j].x, xv[j].y, xv[j].z, xv[j].w};
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
                 const uint32_t dw = m4 - w4[w];  // per byte: max - x, no borrows
-                e[j][w * 4 + 0] = lut_at<0>(lut, lane4, dw);
-                e[j][w * 4 + 1] = lut_at<1>(lut, lane4, dw);
-                e[j][w * 4 + 2] = lut_at<2>(lut, lane4, dw);
-                e[j][w * 4 + 3] = lut_at<3>(lut, lane4, dw);
+                e[j][w * 4 + 0] = lut_at<0>(lut_lane, dw);
+                e[j][w * 4 + 1] = lut_at<1>(lut_lane, dw);
+                e[j][w * 4 + 2] = lut_at<2>(lut_lane, dw);
+                e[j][w * 4 + 3] = lut_at<3>(lut_lane, dw);
             }
-            const int chunk = j * G + gl;
-            if (row_ok && chunk < a.geom.nchunks) {
+            if (row_ok && (j * G + gl) < a.geom.nchunks) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) fsum += e[j][i];
+                for (int i = 0; i < 16; i += 2) { fs0 += e[j][i]; fs1 += e[j][i + 1]; }
             }
         }
-        // exact: a lane adds at most 64 scores <= 32767 (scaled by 2^-64)
-        const int sum = __reduce_add_sync(group_mask, __float2int_rn(fsum * 18446744073709551616.0f));
+        // exact: a lane adds at most 32 scores <= 32767 (scaled by 2^-64)
+        const int sum = __reduce_add_sync(group_mask, __float2int_rn((fs0 + fs1) * TWO_P64));
         const int s = sum > 0 ? sum : 1;
         int inv;
         if (a.use_clb && a.mode == 0) {
             const int k = 31 - __clz(s);
             inv = a.inv_shift - k >= 0 ? (255 << (a.inv_shift - k)) : (255 >> (k - a.inv_shift));
         } else {
-            // exact floor(numer / s): reciprocal estimate, then at most one step either way
-            // (numer < 2^30 and s >= 1, so the estimate is within 1 of the quotient)
-            int q = __float2int_rz(__fmul_rz(numer_f, __frcp_rn((float)s)));
-            int rem = numer - q * s;
-            if (rem < 0) { --q; rem += s; }
-            if (rem < 0) { --q; rem += s; }
-            if (rem >= s) { ++q; rem -= s; }
-            if (rem >= s) { ++q; }
+            // exact floor(numer / s) when it is below 2^15 (larger quotients saturate to 32767 anyway):
+            // reciprocal estimate (relative error < 2^-22), then at most one step either way
+            float rcp;
+            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rcp) : "f"((float)s));
+            int q = __float2int_rz(numer_f * rcp);
+            const int rem = numer - q * s;
+            q += (rem >= s) - (rem < 0);
             inv = q;
         }
         inv = min(max(inv, 0), 32767);
         const float invs = (float)inv * out_mul;  // inv * 2^-(shift + 85), exact
+        uint8_t* orow = a.out + row * a.ldo + gl * 16;
 
 #pragma unroll
         for (int j = 0; j < NCH; ++j) {
-            const int chunk = j * G + gl;
-            if (!(row_ok && chunk < a.geom.nchunks)) continue;
+            if (!(row_ok && (j * G + gl) < a.geom.nchunks)) continue;
             uint32_t aw[4] = {0, 0, 0, 0};
-            if (has_add) {
-                const uint4 av = ldg16(a.addend + row * a.ldadd + (long long)chunk * 16);
-                aw[0] = av.x; aw[1] = av.y; aw[2] = av.z; aw[3] = av.w;
-            }
+            if (HAS_ADD) { aw[0] = av[j].x; aw[1] = av[j].y; aw[2] = av[j].z; aw[3] = av[j].w; }
             uint32_t ow[4];
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
                 // floor(score * inv / 2^shift) lands in the low bits of a subnormal (scores are non-negative)
-                int o0 = __float_as_int(__fmaf_rd(e[j][w * 4 + 0], invs, 0.0f));
-                int o1 = __float_as_int(__fmaf_rd(e[j][w * 4 + 1], invs, 0.0f));
-                int o2 = __float_as_int(__fmaf_rd(e[j][w * 4 + 2], invs, 0.0f));
-                int o3 = __float_as_int(__fmaf_rd(e[j][w * 4 + 3], invs, 0.0f));
-                if (has_add) {
-                    o0 = min(o0, 255); o1 = min(o1, 255); o2 = min(o2, 255); o3 = min(o3, 255);
-                    o0 = __viaddmin_s32(o0, (int)prmt(aw[w], 0, 0x4440), 255);
-                    o1 = __viaddmin_s32(o1, (int)prmt(aw[w], 0, 0x4441), 255);
-                    o2 = __viaddmin_s32(o2, (int)prmt(aw[w], 0, 0x4442), 255);
-                    o3 = __viaddmin_s32(o3, (int)prmt(aw[w], 0, 0x4443), 255);
-                } else {
-                    o0 = min(o0, 255); o1 = min(o1, 255); o2 = min(o2, 255); o3 = min(o3, 255);
+                const int o0 = min(__float_as_int(__fmaf_rd(e[j][w * 4 + 0], invs, 0.0f)), 255);
+                const int o1 = min(__float_as_int(__fmaf_rd(e[j][w * 4 + 1], invs, 0.0f)), 255);
+                const int o2 = min(__float_as_int(__fmaf_rd(e[j][w * 4 + 2], invs, 0.0f)), 255);
+                const int o3 = min(__float_as_int(__fmaf_rd(e[j][w * 4 + 3], invs, 0.0f)), 255);
+                uint32_t p01 = prmt((uint32_t)o0, (uint32_t)o1, 0x5410);
+                uint32_t p23 = prmt((uint32_t)o2, (uint32_t)o3, 0x5410);
+                if (HAS_ADD) {
+                    // fused saturating uint8 Add: zero-extended addend pairs, packed add + min(., 255)
+                    p01 = __viaddmin_u16x2(p01, prmt(aw[w], 0, 0x4140), 0x00FF00FFu);
+                    p23 = __viaddmin_u16x2(p23, prmt(aw[w], 0, 0x4342), 0x00FF00FFu);
                 }
-                const uint32_t lo2 = prmt((uint32_t)o0, (uint32_t)o1, 0x0040);
-                const uint32_t hi2 = prmt((uint32_t)o2, (uint32_t)o3, 0x0040);
-                ow[w] = prmt(lo2, hi2, 0x5410);
+                ow[w] = prmt(p01, p23, 0x6420);
             }
-            stg16(a.out + row * a.ldo + (long long)chunk * 16, make_uint4(ow[0], ow[1], ow[2], ow[3]));
+            stg16(orow + j * G * 16, make_uint4(ow[0], ow[1], ow[2], ow[3]));
         }
     }
 }
@@ -566,29 +574,29 @@ RowGeom make_geom(int cols) {
     return g;
 }
 
-// Fill the reciprocal-std table of one rounding token once per device (stream-ordered, then waited for so
-// that later launches on any stream see it).  Returns false while `stream` is being captured into a graph and
-// the table does not exist yet: the caller then uses the generic kernel for that call.
-bool ensure_inv_std_table(int tok, cudaStream_t stream) {
-    static std::mutex mu;
-    static bool built[64][A4C_RND_COUNT] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
-    std::lock_guard<std::mutex> lock(mu);
-    if (built[dev][tok]) return true;
-    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return false;
-    build_inv_std_table_kernel<<<(kInvStdEntries + 255) / 256, 256, 0, stream>>>(tok);
-    if (cudaGetLastError() != cudaSuccess || cudaStreamSynchronize(stream) != cudaSuccess) return false;
-    built[dev][tok] = true;
-    return true;
-}
-
 int sm_count() {
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     return sms;
+}
+
+// ring depth, shared-memory size and grid size for a kernel with `fixed` bytes of tables and `slot` bytes
+// per ring slot
+void plan_launch(size_t fixed, size_t slot, long long n_items, int* stages, size_t* smem, int* grid) {
+    int st = 4;
+    size_t bytes = fixed + kWarps * st * 8 + 128 + (size_t)kWarps * st * slot;
+    if (bytes > 72 * 1024) {  // keep at least three blocks per SM resident
+        st = 3;
+        bytes = fixed + kWarps * st * 8 + 128 + (size_t)kWarps * st * slot;
+    }
+    int per_sm = (int)((220 * 1024) / bytes);
+    if (per_sm < 1) per_sm = 1;
+    if (per_sm > 4) per_sm = 4;
+    long long blocks = (n_items + kWarps - 1) / kWarps;
+    const long long cap = (long long)sm_count() * per_sm;
+    if (blocks > cap) blocks = cap;
+    *stages = st; *smem = bytes; *grid = (int)blocks;
 }
 
 }  // namespace
@@ -603,8 +611,7 @@ int a4c_launch_layernorm_fast(const int8_t* x, long long ldx, const int16_t* gam
     if (s_out < 2 || gamma_absmax <= 0 || gamma_absmax > 16383) return A4C_ERR_UNSUPPORTED;
     if (rounding == A4C_RND_SYMMETRIC_INF || rounding == A4C_RND_SYMMETRIC_ZERO || rounding == A4C_RND_CONV_ODD)
         return A4C_ERR_UNSUPPORTED;
-    if (cols > 2048 || status == nullptr || eps_q0 > kInvStdMaxEps) return A4C_ERR_UNSUPPORTED;
-    if (!ensure_inv_std_table(rounding, stream)) return A4C_ERR_UNSUPPORTED;
+    if (cols > 2048 || status == nullptr || eps_q0 > (1 << 20)) return A4C_ERR_UNSUPPORTED;
     LnFastArgs a;
     a.x = x; a.ldx = ldx; a.gamma = gamma; a.beta = beta; a.addend = addend; a.ldadd = ldadd; a.out = out; a.ldo = ldo;
     a.rows = rows; a.cols = cols; a.eps_q0 = eps_q0; a.rounding = rounding; a.s_out = s_out;
@@ -621,28 +628,32 @@ int a4c_launch_layernorm_fast(const int8_t* x, long long ldx, const int16_t* gam
     a.c0_out += (float)(128 << s_out);  // outputs are produced biased by +128
     a.geom = make_geom(cols);
     const int nch = (a.geom.nchunks + a.geom.G - 1) / a.geom.G;
-    const size_t smem = (size_t)cols * 8 + kWarps * kStages * 8 + 128 + (size_t)kWarps * kStages * a.geom.R * cols;
+    if (nch != 1 && nch != 2 && nch != 4) return A4C_ERR_UNSUPPORTED;
+    const size_t fixed = (size_t)nch * 4 * 32 * 4 * 4 * 2;
+    const size_t slot = (size_t)a.geom.R * cols * (addend ? 2 : 1);
     const long long n_items = (rows + a.geom.R - 1) / a.geom.R;
-    long long blocks = (n_items + kWarps - 1) / kWarps;
-    const int per_sm = (int)(200 * 1024 / smem) < 1 ? 1 : (int)(200 * 1024 / smem);
-    const long long cap = (long long)sm_count() * (per_sm > 4 ? 4 : per_sm);
-    if (blocks > cap) blocks = cap;
+    size_t smem; int grid;
+    plan_launch(fixed, slot, n_items, &a.stages, &smem, &grid);
     const int fs = rounding == A4C_RND_CONV_EVEN ? 0 : (gamma_absmax <= 511 ? 1 : 2);
-#define LN_LAUNCH(NCH_, FS_)                                                                                  \
-    do {                                                                                                       \
-        cudaFuncSetAttribute(layernorm_fast_kernel<NCH_, FS_>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
-                             (int)smem);                                                                       \
-        layernorm_fast_kernel<NCH_, FS_><<<(int)blocks, kThreads, smem, stream>>>(a);                          \
+#define LN_LAUNCH(NCH_, FS_, ADD_)                                                                                \
+    do {                                                                                                           \
+        cudaFuncSetAttribute(layernorm_fast_kernel<NCH_, FS_, ADD_>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                             (int)smem);                                                                           \
+        layernorm_fast_kernel<NCH_, FS_, ADD_><<<grid, kThreads, smem, stream>>>(a);                               \
     } while (0)
-#define LN_PICK(NCH_)                                                                                          \
-    do {                                                                                                       \
-        if (fs == 0) LN_LAUNCH(NCH_, 0); else if (fs == 1) LN_LAUNCH(NCH_, 1); else LN_LAUNCH(NCH_, 2);        \
+#define LN_PICK_FS(NCH_, ADD_)                                                                                     \
+    do {                                                                                                           \
+        if (fs == 0) LN_LAUNCH(NCH_, 0, ADD_); else if (fs == 1) LN_LAUNCH(NCH_, 1, ADD_); else LN_LAUNCH(NCH_, 2, ADD_); \
+    } while (0)
+#define LN_PICK(NCH_)                                                                                              \
+    do {                                                                                                           \
+        if (addend) LN_PICK_FS(NCH_, true); else LN_PICK_FS(NCH_, false);                                          \
     } while (0)
     if (nch == 1) LN_PICK(1);
     else if (nch == 2) LN_PICK(2);
-    else if (nch == 4) LN_PICK(4);
-    else return A4C_ERR_UNSUPPORTED;
+    else LN_PICK(4);
 #undef LN_PICK
+#undef LN_PICK_FS
 #undef LN_LAUNCH
     return cudaGetLastError() == cudaSuccess ? A4C_OK : A4C_ERR_CUDA;
 }
@@ -658,20 +669,19 @@ int a4c_launch_softmax_fast(const int8_t* x, long long ldx, const void* addend, 
     a.use_clb = use_clb; a.exp_kq = exp_kq; a.status = status;
     a.geom = make_geom(cols);
     const int nch = (a.geom.nchunks + a.geom.G - 1) / a.geom.G;
-    const size_t smem = 256 * 32 * 4 + kWarps * kStages * 8 + 128 + (size_t)kWarps * kStages * a.geom.R * cols;
+    if (nch != 1 && nch != 2) return A4C_ERR_UNSUPPORTED;
+    const size_t slot = (size_t)a.geom.R * cols * (addend ? 2 : 1);
     const long long n_items = (rows + a.geom.R - 1) / a.geom.R;
-    long long blocks = (n_items + kWarps - 1) / kWarps;
-    const int per_sm = (int)(200 * 1024 / smem) < 1 ? 1 : (int)(200 * 1024 / smem);
-    const long long cap = (long long)sm_count() * (per_sm > 4 ? 4 : per_sm);
-    if (blocks > cap) blocks = cap;
-#define SM_LAUNCH(NCH_)                                                                                        \
-    do {                                                                                                       \
-        cudaFuncSetAttribute(softmax_fast_kernel<NCH_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        softmax_fast_kernel<NCH_><<<(int)blocks, kThreads, smem, stream>>>(a);                                 \
+    size_t smem; int grid;
+    plan_launch(256 * 32 * 4, slot, n_items, &a.stages, &smem, &grid);
+#define SM_LAUNCH(NCH_, ADD_)                                                                                      \
+    do {                                                                                                           \
+        cudaFuncSetAttribute(softmax_fast_kernel<NCH_, ADD_>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
+                             (int)smem);                                                                           \
+        softmax_fast_kernel<NCH_, ADD_><<<grid, kThreads, smem, stream>>>(a);                                      \
     } while (0)
-    if (nch == 1) SM_LAUNCH(1);
-    else if (nch == 2) SM_LAUNCH(2);
-    else return A4C_ERR_UNSUPPORTED;
+    if (nch == 1) { if (addend) SM_LAUNCH(1, true); else SM_LAUNCH(1, false); }
+    else { if (addend) SM_LAUNCH(2, true); else SM_LAUNCH(2, false); }
 #undef SM_LAUNCH
     return cudaGetLastError() == cudaSuccess ? A4C_OK : A4C_ERR_CUDA;
 }
