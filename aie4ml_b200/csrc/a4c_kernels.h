@@ -39,3 +39,11 @@ int a4c_launch_layernorm_fast(const int8_t* x, long long ldx, const int16_t* gam
 int a4c_launch_softmax_fast(const int8_t* x, long long ldx, const void* addend, long long ldadd, void* out,
                             long long ldo, long long rows, int cols, int mode, int B, int S, int Dmax, int inv_shift,
                             int use_clb, int exp_kq, int out_dtype, int* status, cudaStream_t stream);
+
+// tcgen05 batched MatMul (bmm_tc.cu).  B stored [N,K] when trans_b (K-major operand) or [K,N] (MN-major operand).
+int a4c_bmm_tc_supported(const void* A, long long lda, long long stride_a, const void* B, long long ldb,
+                         long long stride_b, const void* C, long long ldc, long long stride_c, long long batch, int M,
+                         int K, int N, int trans_a, int trans_b, int out_dtype);
+int a4c_launch_bmm_tc(const void* A, long long lda, long long stride_a, const void* B, long long ldb, long long stride_b,
+                      void* C, long long ldc, long long stride_c, long long batch, int M, int K, int N, int trans_b,
+                      int shift, int rounding, int out_dtype, int a_unsigned, int* status_word, cudaStream_t stream);

@@ -13,6 +13,7 @@ std::mutex g_mutex;
 int* g_status[kMaxDevices] = {nullptr};
 thread_local const char* t_last_cuda_error = "no error";
 int g_rowop_path = 0;  // 0 auto (fast kernels when they apply), 1 generic kernels only
+int g_bmm_path = 0;    // 0 auto (tcgen05 when its rules hold), 1 dp4a kernel only
 
 bool note(cudaError_t e) {
     if (e != cudaSuccess) {
@@ -113,6 +114,15 @@ int a4c_bmm_i8(const void* A, int64_t lda, int64_t stride_a, const int8_t* B, in
     if (batch < 0 || M <= 0 || K <= 0 || N <= 0 || ldc < N) return A4C_ERR_INVALID_ARG;
     if (lda < (trans_a ? M : K) || ldb < (trans_b ? K : N)) return A4C_ERR_INVALID_ARG;
     if (shift < 0 || shift > 31 || !valid_round(rounding) || !valid_dtype(out_dtype)) return A4C_ERR_INVALID_ARG;
+    if (g_bmm_path == 0 && a4c_bmm_tc_supported(A, lda, stride_a, B, ldb, stride_b, C, ldc, stride_c, batch, M, K, N,
+                                                trans_a, trans_b, out_dtype) == A4C_OK) {
+        int* word = status_word();
+        if (word == nullptr) return A4C_ERR_CUDA;
+        const int trc = a4c_launch_bmm_tc(A, lda, stride_a, B, ldb, stride_b, C, ldc, stride_c, batch, M, K, N, trans_b,
+                                          shift, rounding, out_dtype, a_unsigned, word, (cudaStream_t)stream);
+        if (trc != A4C_OK) { if (trc == A4C_ERR_CUDA) note(cudaGetLastError()); return trc; }
+        return finish();
+    }
     // A(m,k): row stride lda / column stride 1, swapped when the stored operand is transposed
     const long long a_rs = trans_a ? 1 : lda, a_cs = trans_a ? lda : 1;
     // B(k,n): stored [K,N] -> k stride ldb, n stride 1; stored [N,K] -> k stride 1, n stride ldb
@@ -127,6 +137,10 @@ int a4c_bmm_i8(const void* A, int64_t lda, int64_t stride_a, const int8_t* B, in
 int a4c_set_option(int option, int value) {
     if (option == A4C_OPT_ROWOP_PATH && (value == 0 || value == 1)) {
         g_rowop_path = value;
+        return A4C_OK;
+    }
+    if (option == A4C_OPT_BMM_PATH && (value == 0 || value == 1)) {
+        g_bmm_path = value;
         return A4C_OK;
     }
     return A4C_ERR_INVALID_ARG;

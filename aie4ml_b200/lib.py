@@ -24,6 +24,7 @@ A4C_ERR_DEVICE_TIMEOUT = -6
 
 ALGO_AUTO, ALGO_SIMT, ALGO_TCGEN05 = 0, 1, 2
 OPT_ROWOP_PATH = 0
+OPT_BMM_PATH = 1
 
 # name -> (restype, argtypes); mirrors the header declaration by declaration
 SIGNATURES = {

@@ -86,12 +86,15 @@ def load_cpu_oracle():
     try:
         subprocess.run(['make', '-C', str(ROOT / 'oracle'), f'OUT={out}', 'ARCH=-march=native'], check=True,
                        capture_output=True, timeout=120)
-        return ctypes.CDLL(str(out)), 'native'
+        lib, arch = ctypes.CDLL(str(out)), 'native'
     except Exception:
         so = ROOT / 'oracle' / 'liboracle.so'
         if not so.exists():
             subprocess.run(['make', '-C', str(ROOT / 'oracle')], check=True, capture_output=True)
-        return ctypes.CDLL(str(so)), 'x86-64-v3'
+        lib, arch = ctypes.CDLL(str(so)), 'x86-64-v3'
+    # all host threads, whatever the launcher exported (torchrun sets OMP_NUM_THREADS=1)
+    lib.orc_set_threads(ctypes.c_int(len(os.sched_getaffinity(0)) if hasattr(os, 'sched_getaffinity') else os.cpu_count()))
+    return lib, arch
 
 
 def cpu_run_plan(lib, plan, inputs, rows: int):

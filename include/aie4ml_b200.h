@@ -51,6 +51,7 @@ extern "C" {
 
 /* Options for a4c_set_option */
 #define A4C_OPT_ROWOP_PATH 0 /* 0 = auto (bandwidth-oriented row kernels when they apply), 1 = generic kernels only */
+#define A4C_OPT_BMM_PATH 1   /* 0 = auto (tcgen05 batched MatMul when its alignment rules hold), 1 = dp4a kernel only */
 
 /* Library version (major*10000 + minor*100 + patch). */
 A4C_API int a4c_version(void);
@@ -97,6 +98,8 @@ A4C_API int a4c_dense_i8(const void* A, int64_t lda, const int8_t* Wt, int64_t l
  *   stored A_b: [M, K] (or [K, M] when trans_a), pitch lda, batch stride stride_a; uint8 when a_unsigned
  *   stored B_b: [K, N] (or [N, K] when trans_b), pitch ldb, batch stride stride_b; always int8
  *   C_b: [M, N] out_dtype, pitch ldc, batch stride stride_c
+ * The tcgen05 kernel is used when the stored A is not transposed, pitches / strides / bases are multiples of
+ * 16 bytes, N is a multiple of 16 and the output is 8-bit; otherwise the dp4a kernel.
  */
 A4C_API int a4c_bmm_i8(const void* A, int64_t lda, int64_t stride_a, const int8_t* B, int64_t ldb, int64_t stride_b,
                void* C, int64_t ldc, int64_t stride_c, int64_t batch, int M, int K, int N, int trans_a,

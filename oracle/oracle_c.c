@@ -252,6 +252,15 @@ ORC_API int orc_softmax_i8(const int8_t* x, int64_t ldx, void* out, int64_t ldo,
     return 0;
 }
 
+/* Override the OpenMP thread count (launchers such as torchrun export OMP_NUM_THREADS=1). */
+ORC_API void orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 ORC_API int orc_num_threads(void) {
     int n = 1;
 #ifdef _OPENMP

@@ -93,7 +93,17 @@ def test_dense_auto_picks_a_working_kernel_and_rejects_bad_arguments():
         G.dense(a, w, bias, shift=40, tok='positive_inf', relu=False)
 
 
-def test_bmm_attention_shapes():
+@pytest.fixture(params=['auto', 'dp4a'])
+def bmm_path(request):
+    from aie4ml_b200 import lib as a4c
+
+    L = a4c.load()
+    assert L.a4c_set_option(a4c.OPT_BMM_PATH, 0 if request.param == 'auto' else 1) == 0
+    yield request.param
+    assert L.a4c_set_option(a4c.OPT_BMM_PATH, 0) == 0
+
+
+def test_bmm_attention_shapes(bmm_path):
     import gpu_util as G
 
     rng = np.random.default_rng(51)
@@ -104,6 +114,21 @@ def test_bmm_attention_shapes():
     np.testing.assert_array_equal(G.bmm(q, k, shift=9, tok='positive_inf', trans_b=True),
                                   oracle.matmul(q, k, shift=9, tok='positive_inf', transpose_b=True))
     np.testing.assert_array_equal(G.bmm(p, v, shift=8, tok='conv_even'), oracle.matmul(p, v, shift=8, tok='conv_even'))
+    for tok in TOKENS:
+        np.testing.assert_array_equal(G.bmm(q, k, shift=9, tok=tok, trans_b=True),
+                                      oracle.matmul(q, k, shift=9, tok=tok, transpose_b=True), err_msg=tok)
+    # ragged: M and K not multiples of the tile, several N tiles, more batches than SMs
+    a2 = rng.integers(-128, 128, (200, 72, 80)).astype(np.int8)
+    b2 = rng.integers(-128, 128, (200, 80, 144)).astype(np.int8)
+    np.testing.assert_array_equal(G.bmm(a2, b2, shift=7, tok='positive_inf', out_dtype='uint8'),
+                                  oracle.matmul(a2, b2, shift=7, tok='positive_inf', out_dtype='uint8'))
+    b2t = np.ascontiguousarray(np.swapaxes(b2, 1, 2))
+    np.testing.assert_array_equal(G.bmm(a2, b2t, shift=7, tok='conv_even', trans_b=True),
+                                  oracle.matmul(a2, b2t, shift=7, tok='conv_even', transpose_b=True))
+    big_k = rng.integers(-128, 128, (5, 130, 400)).astype(np.int8)
+    big_b = rng.integers(-128, 128, (5, 400, 272)).astype(np.int8)
+    np.testing.assert_array_equal(G.bmm(big_k, big_b, shift=0, tok='floor', out_dtype='int8'),
+                                  oracle.matmul(big_k, big_b, shift=0, tok='floor', out_dtype='int8'))
     a = rng.integers(-128, 128, (3, 20, 37)).astype(np.int8)   # stored [K, M]
     b = rng.integers(-128, 128, (3, 20, 11)).astype(np.int8)
     np.testing.assert_array_equal(G.bmm(a, b, shift=4, tok='floor', trans_a=True, out_dtype='int16'),
