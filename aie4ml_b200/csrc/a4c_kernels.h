@@ -47,3 +47,9 @@ int a4c_bmm_tc_supported(const void* A, long long lda, long long stride_a, const
 int a4c_launch_bmm_tc(const void* A, long long lda, long long stride_a, const void* B, long long ldb, long long stride_b,
                       void* C, long long ldc, long long stride_c, long long batch, int M, int K, int N, int trans_b,
                       int shift, int rounding, int out_dtype, int a_unsigned, int* status_word, cudaStream_t stream);
+
+// CTA-pair (cta_group::2) Dense: one 256 x 256 tile per two SMs (dense_tc2.cu); same argument rules as
+// a4c_launch_dense_tc.
+int a4c_launch_dense_tc2(const void* A, long long lda, const void* Wt, long long ldw, const int32_t* bias,
+                         void* Y, long long ldy, long long M, int K, int N, int shift, int rounding, int relu,
+                         int out_dtype, int a_unsigned, int* status_word, cudaStream_t stream);

@@ -97,6 +97,11 @@ int a4c_dense_i8(const void* A, int64_t lda, const int8_t* Wt, int64_t ldw, cons
         if (word == nullptr) return A4C_ERR_CUDA;
         rc = a4c_launch_dense_tc(A, lda, Wt, ldw, bias, Y, ldy, M, K, N, shift, rounding, relu, out_dtype,
                                  a_unsigned, 0, word, s);
+    } else if (use == A4C_ALGO_TCGEN05_PAIR) {
+        int* word = status_word();
+        if (word == nullptr) return A4C_ERR_CUDA;
+        rc = a4c_launch_dense_tc2(A, lda, Wt, ldw, bias, Y, ldy, M, K, N, shift, rounding, relu, out_dtype, a_unsigned,
+                                  word, s);
     } else if (use == A4C_ALGO_SIMT) {
         rc = a4c_launch_gemm_simt(A, lda, 1, 0, Wt, 1, ldw, 0, bias, Y, ldy, 0, 1, M, K, N, shift, rounding, relu,
                                   out_dtype, a_unsigned, s);

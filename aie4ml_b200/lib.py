@@ -22,7 +22,7 @@ A4C_ERR_CUDA = -4
 A4C_ERR_TOO_LARGE = -5
 A4C_ERR_DEVICE_TIMEOUT = -6
 
-ALGO_AUTO, ALGO_SIMT, ALGO_TCGEN05 = 0, 1, 2
+ALGO_AUTO, ALGO_SIMT, ALGO_TCGEN05, ALGO_TCGEN05_PAIR = 0, 1, 2, 3
 OPT_ROWOP_PATH = 0
 OPT_BMM_PATH = 1
 

@@ -48,6 +48,7 @@ extern "C" {
 #define A4C_ALGO_AUTO 0
 #define A4C_ALGO_SIMT 1      /* dp4a tiles, any shape / stride */
 #define A4C_ALGO_TCGEN05 2   /* tcgen05 + TMA + TMEM, one CTA per 128x256 tile */
+#define A4C_ALGO_TCGEN05_PAIR 3 /* tcgen05 cta_group::2, a CTA pair per 256x256 tile */
 
 /* Options for a4c_set_option */
 #define A4C_OPT_ROWOP_PATH 0 /* 0 = auto (bandwidth-oriented row kernels when they apply), 1 = generic kernels only */

@@ -8,7 +8,7 @@ from oracle import oracle
 pytestmark = pytest.mark.gpu
 
 TOKENS = oracle.ROUNDING_TOKENS
-SIMT, TC = 1, 2
+SIMT, TC, TC2 = 1, 2, 3
 
 
 def _rand_dense(seed, M, K, N, unsigned=False, big_bias=True):
@@ -46,26 +46,29 @@ def test_dense_simt_every_rounding_mode_and_dtype(tok):
 
 @pytest.mark.parametrize('shape', [(128, 128, 256), (128, 256, 16), (100, 16, 48), (300, 1024, 272), (1000, 200, 512),
                                    (4096, 512, 1024), (129, 4096, 256)])
-def test_dense_tcgen05_shapes(shape):
+@pytest.mark.parametrize('algo', [TC, TC2])
+def test_dense_tcgen05_shapes(shape, algo):
     import gpu_util as G
 
     M, K, N = shape
     a, w, bias = _rand_dense(sum(shape), M, K, N)
-    got = G.dense(a, w, bias, shift=10, tok='positive_inf', relu=True, algo=TC)
+    got = G.dense(a, w, bias, shift=10, tok='positive_inf', relu=True, algo=algo)
     np.testing.assert_array_equal(got, oracle.dense(a, w, bias, shift=10, tok='positive_inf', relu=True))
 
 
 @pytest.mark.parametrize('tok', TOKENS)
-def test_dense_tcgen05_every_rounding_mode(tok):
+@pytest.mark.parametrize('algo', [TC, TC2])
+def test_dense_tcgen05_every_rounding_mode(tok, algo):
     import gpu_util as G
 
     a, w, bias = _rand_dense(21, 384, 384, 320)
     for shift, relu, od in ((9, False, 'int8'), (3, True, 'int8'), (12, False, 'uint8'), (0, False, 'int8')):
-        got = G.dense(a, w, bias, shift=shift, tok=tok, relu=relu, out_dtype=od, algo=TC)
+        got = G.dense(a, w, bias, shift=shift, tok=tok, relu=relu, out_dtype=od, algo=algo)
         np.testing.assert_array_equal(got, oracle.dense(a, w, bias, shift=shift, tok=tok, relu=relu, out_dtype=od))
 
 
-def test_dense_tcgen05_unsigned_lhs_no_bias_and_many_tiles():
+@pytest.mark.parametrize('TC', [TC, TC2])
+def test_dense_tcgen05_unsigned_lhs_no_bias_and_many_tiles(TC):
     import gpu_util as G
 
     u, w, _ = _rand_dense(31, 640, 256, 768, unsigned=True)
