@@ -144,6 +144,22 @@ A4C_API int a4c_softmax_i8(const int8_t* x, int64_t ldx, const void* addend, int
 A4C_API int a4c_add_sat(const void* a, int64_t lda, const void* b, int64_t ldb, void* out, int64_t ldo, int64_t rows,
                 int64_t cols, int shift, int rounding, int dtype, void* stream);
 
+/*
+ * A chain of Dense layers in one call: X -> Dense_0 -> ... -> Dense_{L-1} -> Y, each with the contract of
+ * a4c_dense_i8 and int8 activations between layers.  Replaces consecutive dense_bias_relu kernels wired buffer to
+ * buffer by the reference's top graph (src/aie4ml/templates/firmware/top_graph.h.jinja; per-layer arithmetic
+ * src/aie4ml/templates/nnet_utils/dense_bias_relu/dense_bias_relu.cpp:67-166).
+ *   dims[L+1]   feature counts: dims[0] = inputs of layer 0, dims[L] = outputs of the last layer
+ *   Wt[l]       [dims[l+1], ldw[l]] int8, K contiguous;  bias[l] int32[dims[l+1]] or NULL (bias itself may be NULL)
+ *   shift[l], relu[l] per layer; one rounding code for the chain; out_dtype applies to the last layer
+ * The activations between layers are written to scratch memory the library allocates on first use, grows on
+ * demand and keeps per device.  Two calls that overlap in time on one device would share that scratch: issue
+ * them on one stream.
+ */
+A4C_API int a4c_mlp_i8(const void* X, int64_t ldx, int x_unsigned, int n_layers, const int* dims,
+                       const int8_t* const* Wt, const int64_t* ldw, const int32_t* const* bias, const int* shift,
+                       const int* relu, int rounding, void* Y, int64_t ldy, int out_dtype, int64_t M, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -109,3 +109,32 @@ def add(a, b, *, shift, tok, dtype):
                        ROUNDING_CODE[tok], DTYPE_CODE[dtype], stream())
     a4c.check(rc, 'a4c_add_sat')
     return o_d.cpu().numpy()
+
+
+def mlp_chain(x, layers, *, tok, out_dtype='int8', fn_name='a4c_mlp_i8'):
+    """layers: list of (w_kn int8, bias int32 or None, shift, relu).  Calls the chain entry point `fn_name`."""
+    L = a4c.load()
+    fn = getattr(L, fn_name)
+    M, K0 = x.shape
+    n = len(layers)
+    dims = (ctypes.c_int * (n + 1))(K0, *[w.shape[1] for w, _, _, _ in layers])
+    wts = [dev(pack_wt(w)) for w, _, _, _ in layers]
+    biases = [dev(b.astype(np.int32)) if b is not None else None for _, b, _, _ in layers]
+    wt_ptrs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in wts])
+    ldw = (ctypes.c_int64 * n)(*[t.shape[1] for t in wts])
+    b_ptrs = (ctypes.c_void_p * n)(*[b.data_ptr() if b is not None else None for b in biases])
+    shifts = (ctypes.c_int * n)(*[s for _, _, s, _ in layers])
+    relus = (ctypes.c_int * n)(*[int(r) for _, _, _, r in layers])
+    lda = (K0 + 15) // 16 * 16
+    x_d = dev(padded(x, lda))
+    N = layers[-1][0].shape[1]
+    esz = np.dtype(NP[out_dtype]).itemsize
+    ldy = (N * esz + 15) // 16 * 16 // esz
+    y_d = torch.zeros((M, ldy), dtype=TD[out_dtype], device='cuda')
+    rc = fn(x_d.data_ptr(), lda, int(x.dtype == np.uint8), n, ctypes.cast(dims, ctypes.c_void_p),
+            ctypes.cast(wt_ptrs, ctypes.c_void_p), ctypes.cast(ldw, ctypes.c_void_p), ctypes.cast(b_ptrs, ctypes.c_void_p),
+            ctypes.cast(shifts, ctypes.c_void_p), ctypes.cast(relus, ctypes.c_void_p), ROUNDING_CODE[tok], y_d.data_ptr(),
+            ldy, DTYPE_CODE[out_dtype], M, stream())
+    a4c.check(rc, fn_name)
+    a4c.device_status(stream())
+    return y_d.cpu().numpy()[:, :N]

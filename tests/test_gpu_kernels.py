@@ -235,6 +235,40 @@ def test_add_saturating(dtype):
                                       oracle.add(a, b, shift=1, tok=tok, out_dtype=dtype), err_msg=tok)
 
 
+def _chain_layers(seed, dims, bias=True):
+    rng = np.random.default_rng(seed)
+    layers = []
+    for i in range(len(dims) - 1):
+        w = rng.integers(-127, 128, (dims[i], dims[i + 1])).astype(np.int8)
+        b = rng.integers(-(1 << 12), 1 << 12, dims[i + 1]).astype(np.int32) if bias else None
+        layers.append((w, b, 7 if dims[i] <= 64 else 9, i < len(dims) - 2))
+    return layers
+
+
+def _chain_oracle(x, layers, tok, out_dtype='int8'):
+    cur = x
+    for i, (w, b, shift, relu) in enumerate(layers):
+        last = i == len(layers) - 1
+        cur = oracle.dense(cur, w, b, shift=shift, tok=tok, relu=relu, out_dtype=out_dtype if last else 'int8')
+    return cur
+
+
+@pytest.mark.parametrize('dims', [(16, 64, 32, 32, 5), (512, 1024, 1024, 10), (64, 48), (100, 72, 40, 24)])
+def test_mlp_chain_matches_layer_by_layer_oracle(dims):
+    import gpu_util as G
+
+    rng = np.random.default_rng(sum(dims))
+    for M in (1, 300, 2048):
+        x = rng.integers(-128, 128, (M, dims[0])).astype(np.int8)
+        layers = _chain_layers(len(dims), dims)
+        for tok in ('positive_inf', 'conv_even'):
+            np.testing.assert_array_equal(G.mlp_chain(x, layers, tok=tok), _chain_oracle(x, layers, tok))
+    layers = _chain_layers(3, dims, bias=False)
+    x = rng.integers(-128, 128, (77, dims[0])).astype(np.int8)
+    np.testing.assert_array_equal(G.mlp_chain(x, layers, tok='floor', out_dtype='int16'),
+                                  _chain_oracle(x, layers, 'floor', out_dtype='int16'))
+
+
 def test_empty_inputs_are_no_ops():
     import gpu_util as G
     import torch
