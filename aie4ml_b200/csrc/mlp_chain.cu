@@ -4,6 +4,7 @@
 
 #include "../../include/aie4ml_b200.h"
 #include "a4c_common.cuh"
+#include "a4c_kernels.h"
 
 namespace {
 
@@ -89,4 +90,98 @@ extern "C" int a4c_mlp_i8(const void* X, int64_t ldx, int x_unsigned, int n_laye
     }
     return run_chain(X, ldx, x_unsigned, n_layers, dims, Wt, ldw, bias, shift, relu, rounding, Y, ldy, out_dtype, M,
                      buf0, buf1, stream);
+}
+
+// ------------------------------------------------------------------------------------------------------
+// The same chain for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they run a model: a plug-in that
+// executes inside another runtime's stream callback or captured region, a process whose device memory is
+// handed out entirely by its own pool, or a latency-critical loop that forbids any call that can take the
+// allocator's lock.  For them the scratch of the chain is a fixed array that is part of the library image:
+// it exists on every GPU that loads the library, from load until exit, and nothing is ever allocated or freed.
+//
+// Layout of the array: bytes [0, 256) hold the status word that the tensor-core kernels report bounded-wait
+// failures into (it must start at zero: it is cleared once at set-up and again whenever it is read back);
+// then two activation buffers of A4C_MLP_STATIC_BYTES each.  The activation buffers need no clearing: every
+// layer overwrites all bytes the next layer reads.
+// ------------------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticBuf = (size_t)A4C_MLP_STATIC_BYTES;
+static __device__ __align__(256) unsigned char g_mlp_static_scratch[256 + 2 * kStaticBuf];
+
+std::mutex g_static_mutex;
+unsigned char* g_static_ptr[kMaxDevices] = {nullptr};
+
+// The array's NAME is only a host-side handle; the device address comes from cudaGetSymbolAddress, asked once
+// per device with that device current.
+int static_scratch(cudaStream_t stream, unsigned char** out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return A4C_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (g_static_ptr[dev] == nullptr) {
+        unsigned char* p = nullptr;
+        if (cudaGetSymbolAddress((void**)&p, g_mlp_static_scratch) != cudaSuccess || p == nullptr) return A4C_ERR_CUDA;
+        if (cudaMemsetAsync(p, 0, 256, stream) != cudaSuccess) return A4C_ERR_CUDA;
+        g_static_ptr[dev] = p;
+    }
+    *out = g_static_ptr[dev];
+    return A4C_OK;
+}
+
+// One Dense layer through the internal launchers (a4c_dense_i8 itself would allocate its status word).
+int dense_no_alloc(const void* A, long long lda, const int8_t* Wt, long long ldw, const int32_t* bias, void* Y,
+                   long long ldy, long long M, int K, int N, int shift, int rounding, int relu, int out_dtype,
+                   int a_unsigned, int* status, cudaStream_t stream) {
+    if (a4c_dense_tc_supported(A, lda, Wt, ldw, Y, ldy, M, K, N, out_dtype) == A4C_OK)
+        return a4c_launch_dense_tc(A, lda, Wt, ldw, bias, Y, ldy, M, K, N, shift, rounding, relu, out_dtype, a_unsigned, 0,
+                                   status, stream);
+    return a4c_launch_gemm_simt(A, lda, 1, 0, Wt, 1, ldw, 0, bias, Y, ldy, 0, 1, M, K, N, shift, rounding, relu, out_dtype,
+                                a_unsigned, stream);
+}
+
+}  // namespace
+
+extern "C" int a4c_mlp_i8_static(const void* X, int64_t ldx, int x_unsigned, int n_layers, const int* dims,
+                                 const int8_t* const* Wt, const int64_t* ldw, const int32_t* const* bias,
+                                 const int* shift, const int* relu, int rounding, void* Y, int64_t ldy, int out_dtype,
+                                 int64_t M, int* status_out, void* stream) {
+    size_t inter = 0;
+    const int chk = check_chain(X, ldx, n_layers, dims, Wt, ldw, shift, relu, rounding, Y, ldy, out_dtype, M, &inter);
+    if (chk != A4C_OK) return chk;
+    if (n_layers > 1 && inter > kStaticBuf) return A4C_ERR_TOO_LARGE;  // M * pitch16(widest hidden layer) > 4 MiB
+    cudaStream_t s = (cudaStream_t)stream;
+    unsigned char* base = nullptr;
+    const int rc0 = static_scratch(s, &base);
+    if (rc0 != A4C_OK) return rc0;
+    int* status = reinterpret_cast<int*>(base);
+    void* buf[2] = {base + 256, base + 256 + kStaticBuf};
+    if (M > 0) {
+        const void* in = X;
+        long long ld_in = ldx;
+        int in_unsigned = x_unsigned;
+        for (int l = 0; l < n_layers; ++l) {
+            const bool last = l == n_layers - 1;
+            void* out = last ? Y : buf[l & 1];
+            const long long ld_out = last ? ldy : pitch16(dims[l + 1]);
+            const int rc = dense_no_alloc(in, ld_in, Wt[l], ldw[l], bias ? bias[l] : nullptr, out, ld_out, M, dims[l],
+                                          dims[l + 1], shift[l], rounding, relu[l], last ? out_dtype : A4C_I8, in_unsigned,
+                                          status, s);
+            if (rc != A4C_OK) return rc;
+            in = out;
+            ld_in = ld_out;
+            in_unsigned = 0;
+        }
+        if (cudaPeekAtLastError() != cudaSuccess) return A4C_ERR_CUDA;
+    }
+    if (status_out != nullptr) {
+        if (cudaMemcpyAsync(status_out, status, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess) return A4C_ERR_CUDA;
+        if (cudaStreamSynchronize(s) != cudaSuccess) return A4C_ERR_CUDA;
+        if (*status_out != 0) {
+            cudaMemsetAsync(status, 0, sizeof(int), s);
+            return A4C_ERR_DEVICE_TIMEOUT;
+        }
+    }
+    return A4C_OK;
 }

@@ -41,6 +41,8 @@ SIGNATURES = {
     'a4c_set_option': (c_int, [c_int, c_int]),
     'a4c_mlp_i8': (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                            c_int, c_void_p, c_int64, c_int, c_int64, c_void_p]),
+    'a4c_mlp_i8_static': (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_int, c_void_p, c_int64, c_int, c_int64, ctypes.POINTER(c_int), c_void_p]),
     'a4c_softmax_i8': (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int, c_int, c_int,
                                c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'a4c_add_sat': (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_int,

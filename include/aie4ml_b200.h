@@ -160,6 +160,35 @@ A4C_API int a4c_mlp_i8(const void* X, int64_t ldx, int x_unsigned, int n_layers,
                        const int8_t* const* Wt, const int64_t* ldw, const int32_t* const* bias, const int* shift,
                        const int* relu, int rounding, void* Y, int64_t ldy, int out_dtype, int64_t M, void* stream);
 
+/*
+ * a4c_mlp_i8 for callers that must not allocate.  (This entry point has no counterpart in the reference: it
+ * exists because of how some hosts embed this library, not because of anything aie4ml does.)
+ *
+ * Who needs it: code that runs a model from a place where cudaMalloc is off limits -- inside another runtime's
+ * stream-ordered callback or captured region, in a process whose device memory is owned by its own pool, or in
+ * a loop that may never take the CUDA allocator's lock.  Same arguments and results as a4c_mlp_i8, but the
+ * activations between layers (and the kernels' status word) live in a fixed array inside the library image
+ * instead of allocated scratch.  The function calls no cudaMalloc, cudaFree or allocating library routine.
+ *
+ * Limit: M * round_up(widest hidden layer, 16) must not exceed A4C_MLP_STATIC_BYTES (4 MiB); beyond that the
+ * call returns A4C_ERR_TOO_LARGE and launches nothing.  The array (two such buffers + 256 bytes) is resident on
+ * every GPU that loads the library until the process exits.
+ *
+ * The first call on a device looks up the array's device address and clears its status word; make that first
+ * call outside any stream capture.  Every call uses the same array and finds the previous call's activations
+ * in it (harmless: each layer overwrites what the next one reads); two calls that overlap in time on one GPU
+ * race on it, so keep calls on one stream or order them yourself.
+ *
+ * status_out (host pointer, or NULL): when given, the call waits for `stream`, stores the kernels' status word
+ * there (0 = every bounded device-side wait completed) and returns A4C_ERR_DEVICE_TIMEOUT if it is not 0;
+ * with NULL the call stays asynchronous.
+ */
+#define A4C_MLP_STATIC_BYTES (4u << 20)
+A4C_API int a4c_mlp_i8_static(const void* X, int64_t ldx, int x_unsigned, int n_layers, const int* dims,
+                              const int8_t* const* Wt, const int64_t* ldw, const int32_t* const* bias,
+                              const int* shift, const int* relu, int rounding, void* Y, int64_t ldy, int out_dtype,
+                              int64_t M, int* status_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
