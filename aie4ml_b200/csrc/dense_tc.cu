@@ -35,11 +35,18 @@ constexpr int B_BYTES = BN * BK;                 // 32 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;   // 48 KB
 constexpr int ACC_STAGES = 2;
 constexpr int TMEM_COLS = ACC_STAGES * BN;       // 512
-constexpr int NUM_THREADS = 192;
-constexpr int EPI_THREADS = 128;
+constexpr int EPI_WARPS = 8;           // two warps per TMEM lane quadrant, each takes half of the tile's columns
+constexpr int EPI_THREADS = EPI_WARPS * 32;
+constexpr int NUM_THREADS = 64 + EPI_THREADS;
+// positive_inf with 1 <= shift <= 22: saturate BEFORE the shift (rounding is monotonic, and lo*2^s / hi*2^s
+// round to lo / hi exactly), which makes the rounding add overflow-free and folds bias add, both clamps
+// and the rounding add into two add-min/max instructions plus the shift.
+constexpr int MODE_HALF_UP_CLAMP = 100;
+
+constexpr int BIAS_CACHE = 2048;   // whole bias vector resident in shared memory when N fits
 
 struct SmemTail {
-    int32_t bias[ACC_STAGES][BN];
+    int32_t bias[BIAS_CACHE];       // N <= BIAS_CACHE: bias[n]; else two per-tile slices of BN at [0] and [BN]
     uint64_t full[STAGES];
     uint64_t empty[STAGES];
     uint64_t tmem_full[ACC_STAGES];
@@ -47,7 +54,11 @@ struct SmemTail {
     uint32_t tmem_base;
     volatile int abort_flag;
 };
-constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + sizeof(SmemTail);
+// Output staging: each epilogue warp owns 32 rows x 64 bytes, so that global stores are coalesced
+// (four lanes per row write 64 contiguous bytes) instead of one 16-byte piece per row per lane.
+constexpr int EPI_STAGE_BYTES = 32 * 64;
+constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES +
+                              ((sizeof(SmemTail) + 127) / 128) * 128 + (size_t)EPI_WARPS * EPI_STAGE_BYTES;
 
 using namespace tc;
 
@@ -60,15 +71,51 @@ struct TcArgs {
     int num_m_tiles, num_n_tiles;
     int shift, lo, hi;
     uint32_t mask, c0;   // rounding constants (see round_shift_i32_t)
+    int half, xhi, xlo;  // MODE_HALF_UP_CLAMP: 2^(s-1), hi * 2^s, lo * 2^s + 2^(s-1)
     uint32_t idesc;
     int* status;
 };
 
 template <int MODE>
-__device__ __forceinline__ int requant(int acc, const TcArgs& g) {
-    int v = acc;
-    if (MODE >= 0) v = round_shift_i32_t<MODE>(acc, g.shift, g.mask, g.c0);
+__device__ __forceinline__ int requant(int acc, int bias, const TcArgs& g) {
+    if (MODE == MODE_HALF_UP_CLAMP) {
+        const int t = __viaddmin_s32(acc, bias, g.xhi);          // min(wrap32(acc + bias), hi * 2^s)
+        return __viaddmax_s32(t, g.half, g.xlo) >> g.shift;      // max(t + 2^(s-1), lo * 2^s + 2^(s-1)) >> s
+    }
+    int v = acc + bias;
+    if (MODE == A4C_RND_FLOOR) v = v >> g.shift;
+    else if (MODE >= 0) v = round_shift_i32_t<MODE>(v, g.shift, g.mask, g.c0);
     return min(max(v, g.lo), g.hi);
+}
+
+// One epilogue warp turns 32 rows x 64 accumulator columns (two TMEM loads, `r`) into int8, stages them
+// in its 32 x 64-byte shared-memory patch and writes them out with four lanes per row.
+template <int MODE>
+__device__ __forceinline__ void epilogue_pair(const uint32_t* r, const int32_t* bias64, uint8_t* my_stage, int lane,
+                                              const TcArgs& g, long long row_base, int col0) {
+    const int sw_w = (lane >> 1) & 3;   // 16-byte-piece swizzle of this lane's staging row
+#pragma unroll
+    for (int piece = 0; piece < 4; ++piece) {
+        uint32_t w[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int4 b = *reinterpret_cast<const int4*>(bias64 + piece * 16 + q * 4);
+            const uint32_t* a = r + piece * 16 + q * 4;
+            w[q] = pack4_i8(requant<MODE>((int)a[0], b.x, g), requant<MODE>((int)a[1], b.y, g),
+                            requant<MODE>((int)a[2], b.z, g), requant<MODE>((int)a[3], b.w, g));
+        }
+        *reinterpret_cast<uint4*>(my_stage + lane * 64 + ((piece ^ sw_w) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int rr = (lane >> 2) + 8 * i, q = lane & 3;
+        const uint4 v = *reinterpret_cast<const uint4*>(my_stage + rr * 64 + ((q ^ ((rr >> 1) & 3)) << 4));
+        const long long row = row_base + rr;
+        const int col = col0 + q * 16;
+        if (row < g.M && col < g.N) *reinterpret_cast<uint4*>(g.Y + row * g.ldy + col) = v;
+    }
+    __syncwarp();
 }
 
 // MODE = rounding token, or -1 when shift == 0 (no rounding step).
@@ -158,50 +205,56 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     } else {
         // ---------------- epilogue (warps 2..5) ----------------
         const int quad = warp & 3;           // TMEM lane quadrant this warp may read
-        const int et = threadIdx.x - 64;     // 0..127
+        const int half = (warp - 2) >> 2;    // which half of the tile's columns this warp handles
+        const int et = threadIdx.x - 64;     // 0..EPI_THREADS-1
+        uint8_t* my_stage = smem + (size_t)STAGES * STAGE_BYTES + ((sizeof(SmemTail) + 127) / 128) * 128 +
+                            (size_t)(warp - 2) * EPI_STAGE_BYTES;
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
+        const bool bias_resident = g.num_n_tiles * BN <= BIAS_CACHE;
+        if (bias_resident) {
+            // the whole (zero-padded) bias vector once: no global load on any tile's critical path
+            for (int i = et; i < g.num_n_tiles * BN; i += EPI_THREADS)
+                tail->bias[i] = (g.bias != nullptr && i < g.N) ? __ldg(g.bias + i) : 0;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+        }
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
             const int m0 = (tile / g.num_n_tiles) * BM;
             const int n0 = (tile % g.num_n_tiles) * BN;
-            // stage this tile's bias slice (zero where there is none)
-            for (int i = et; i < BN; i += EPI_THREADS) {
-                const int n = n0 + i;
-                tail->bias[acc][i] = (g.bias != nullptr && n < g.N) ? __ldg(g.bias + n) : 0;
+            const int32_t* tile_bias = tail->bias + (bias_resident ? n0 : acc * BN);
+            if (!bias_resident) {
+                // stage this tile's bias slice (zero where there is none)
+                for (int i = et; i < BN; i += EPI_THREADS) {
+                    const int n = n0 + i;
+                    tail->bias[acc * BN + i] = (g.bias != nullptr && n < g.N) ? __ldg(g.bias + n) : 0;
+                }
+                asm volatile("bar.sync 1, 256;" ::: "memory");
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
             if (ok) ok = mbar_wait(&tail->tmem_full[acc], acc_phase, abort_flag, g.status, 104);
             if (ok) {
                 tc_fence_after();
-                const long long row = (long long)m0 + quad * 32 + lane;
-                uint8_t* yrow = g.Y + row * g.ldy + n0;
                 const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
-#pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    if (n0 + c * 32 >= g.N) break;   // warp-uniform
-                    uint32_t r[32];
-                    tmem_ld32(taddr + (uint32_t)(c * 32), r);
-                    uint32_t w[8];
-#pragma unroll
-                    for (int q = 0; q < 8; ++q) {
-                        int o[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int col = c * 32 + q * 4 + e;
-                            const int v = (int)(r[q * 4 + e] + (uint32_t)tail->bias[acc][col]);
-                            o[e] = requant<MODE>(v, g);
-                        }
-                        w[q] = (uint32_t)(o[0] & 0xFF) | ((uint32_t)(o[1] & 0xFF) << 8) |
-                               ((uint32_t)(o[2] & 0xFF) << 16) | ((uint32_t)o[3] << 24);
-                    }
-                    if (row < g.M) {
-                        const int col0 = n0 + c * 32;
-                        if (col0 < g.N)
-                            *reinterpret_cast<uint4*>(yrow + c * 32) = make_uint4(w[0], w[1], w[2], w[3]);
-                        if (col0 + 16 < g.N)
-                            *reinterpret_cast<uint4*>(yrow + c * 32 + 16) = make_uint4(w[4], w[5], w[6], w[7]);
-                    }
+                const long long row_base = (long long)m0 + quad * 32;
+                // this warp's two 64-column groups; the second group's TMEM loads fly while the first is converted
+                const int c0 = half * (BN / 2), c1 = c0 + 64;
+                const bool have0 = n0 + c0 < g.N, have1 = n0 + c1 < g.N;   // warp-uniform
+                uint32_t ra[64], rb[64];
+                if (have0) {
+                    tmem_ld32_async(taddr + (uint32_t)c0, ra);
+                    tmem_ld32_async(taddr + (uint32_t)c0 + 32u, ra + 32);
+                    tmem_ld_wait32(ra);
+                    tmem_ld_wait32(ra + 32);
+                }
+                if (have1) {
+                    tmem_ld32_async(taddr + (uint32_t)c1, rb);
+                    tmem_ld32_async(taddr + (uint32_t)c1 + 32u, rb + 32);
+                }
+                if (have0) epilogue_pair<MODE>(ra, tile_bias + c0, my_stage, lane, g, row_base, n0 + c0);
+                if (have1) {
+                    tmem_ld_wait32(rb);
+                    tmem_ld_wait32(rb + 32);
+                    epilogue_pair<MODE>(rb, tile_bias + c1, my_stage, lane, g, row_base, n0 + c1);
                 }
                 tc_fence_before();
                 mbar_arrive(&tail->tmem_empty[acc]);
@@ -302,6 +355,10 @@ int a4c_launch_dense_tc(const void* A, long long lda, const void* Wt, long long 
     if (relu && g.lo < 0) g.lo = 0;
     const RoundParams rp = make_round_params(shift, rounding);
     g.mask = rp.mask; g.c0 = rp.c0;
+    const bool pre_clamp = shift >= 1 && shift <= 22;
+    g.half = pre_clamp ? (1 << (shift - 1)) : 0;
+    g.xhi = pre_clamp ? g.hi * (1 << shift) : 0;
+    g.xlo = pre_clamp ? g.lo * (1 << shift) + g.half : 0;
     g.idesc = make_idesc(BM, BN, a_unsigned != 0);
     g.status = status_word;
     int dev = 0, sms = 148;
@@ -314,7 +371,10 @@ int a4c_launch_dense_tc(const void* A, long long lda, const void* Wt, long long 
     else switch (rounding) {
         case A4C_RND_FLOOR: err = launch_mode<A4C_RND_FLOOR>(ma, mb, g, grid, stream); break;
         case A4C_RND_CEIL: err = launch_mode<A4C_RND_CEIL>(ma, mb, g, grid, stream); break;
-        case A4C_RND_POSITIVE_INF: err = launch_mode<A4C_RND_POSITIVE_INF>(ma, mb, g, grid, stream); break;
+        case A4C_RND_POSITIVE_INF:
+            err = pre_clamp ? launch_mode<MODE_HALF_UP_CLAMP>(ma, mb, g, grid, stream)
+                             : launch_mode<A4C_RND_POSITIVE_INF>(ma, mb, g, grid, stream);
+            break;
         case A4C_RND_NEGATIVE_INF: err = launch_mode<A4C_RND_NEGATIVE_INF>(ma, mb, g, grid, stream); break;
         case A4C_RND_SYMMETRIC_INF: err = launch_mode<A4C_RND_SYMMETRIC_INF>(ma, mb, g, grid, stream); break;
         case A4C_RND_SYMMETRIC_ZERO: err = launch_mode<A4C_RND_SYMMETRIC_ZERO>(ma, mb, g, grid, stream); break;

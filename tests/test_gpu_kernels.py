@@ -67,6 +67,33 @@ def test_dense_tcgen05_every_rounding_mode(tok, algo):
         np.testing.assert_array_equal(got, oracle.dense(a, w, bias, shift=shift, tok=tok, relu=relu, out_dtype=od))
 
 
+@pytest.mark.parametrize('algo', [TC, TC2])
+def test_dense_tcgen05_extreme_bias_wraps_like_the_accumulator(algo):
+    """Biases across the whole int32 range: acc + bias wraps at 32 bits before the rounding shift,
+    on either side of the shift at which the kernel changes its rounding sequence, for both
+    signed and unsigned outputs, with and without ReLU."""
+    import gpu_util as G
+
+    rng = np.random.default_rng(77)
+    a, w, _ = _rand_dense(78, 260, 192, 272)
+    bias = rng.integers(-2 ** 31, 2 ** 31, size=272, dtype=np.int64).astype(np.int32)
+    bias[:8] = [2 ** 31 - 1, -2 ** 31, 2 ** 31 - 2 ** 20, -2 ** 31 + 2 ** 20, 0, 1, -1, 2 ** 30]
+    for shift in (1, 2, 21, 22, 23, 24, 31):
+        for relu, od in ((False, 'int8'), (True, 'int8'), (False, 'uint8')):
+            got = G.dense(a, w, bias, shift=shift, tok='positive_inf', relu=relu, out_dtype=od, algo=algo)
+            np.testing.assert_array_equal(
+                got, oracle.dense(a, w, bias, shift=shift, tok='positive_inf', relu=relu, out_dtype=od))
+
+
+def test_dense_tcgen05_wide_output_streams_the_bias_per_tile():
+    """N above the resident-bias limit: the kernel stages one bias slice per tile instead."""
+    import gpu_util as G
+
+    a, w, bias = _rand_dense(79, 300, 64, 2304)
+    got = G.dense(a, w, bias, shift=7, tok='positive_inf', relu=True, algo=TC)
+    np.testing.assert_array_equal(got, oracle.dense(a, w, bias, shift=7, tok='positive_inf', relu=True))
+
+
 @pytest.mark.parametrize('TC', [TC, TC2])
 def test_dense_tcgen05_unsigned_lhs_no_bias_and_many_tiles(TC):
     import gpu_util as G
