@@ -40,6 +40,9 @@ int a4c_launch_softmax_fast(const int8_t* x, long long ldx, const void* addend, 
                             long long ldo, long long rows, int cols, int mode, int B, int S, int Dmax, int inv_shift,
                             int use_clb, int exp_kq, int out_dtype, int* status, cudaStream_t stream);
 
+// Tuning overrides of rowops_fast.cu (0 = automatic, negative leaves a value unchanged).
+void a4c_rowops_fast_tuning(int chunks_per_lane, int min_stages);
+
 // tcgen05 batched MatMul (bmm_tc.cu).  B stored [N,K] when trans_b (K-major operand) or [K,N] (MN-major operand).
 int a4c_bmm_tc_supported(const void* A, long long lda, long long stride_a, const void* B, long long ldb,
                          long long stride_b, const void* C, long long ldc, long long stride_c, long long batch, int M,

@@ -148,6 +148,14 @@ int a4c_set_option(int option, int value) {
         g_bmm_path = value;
         return A4C_OK;
     }
+    if (option == A4C_OPT_ROWOP_CHUNKS_PER_LANE && (value == 0 || value == 1 || value == 2 || value == 4)) {
+        a4c_rowops_fast_tuning(value, -1);
+        return A4C_OK;
+    }
+    if (option == A4C_OPT_ROWOP_MIN_STAGES && (value == 0 || (value >= 2 && value <= 4))) {
+        a4c_rowops_fast_tuning(-1, value);
+        return A4C_OK;
+    }
     return A4C_ERR_INVALID_ARG;
 }
 

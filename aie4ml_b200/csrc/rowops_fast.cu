@@ -103,8 +103,12 @@ __device__ __forceinline__ float byte_to_f23(uint32_t w) {
     return __uint_as_float(prmt(w, 0x4B000000u, 0x7540 + K));
 }
 
+// A row of `cols` bytes is nchunks 16-byte chunks.  G lanes share a row (lane gl takes chunks gl, gl + G, ...),
+// a warp works on R = 32 / G rows at once.  Rows sit `pitch` bytes apart in a ring slot: when fewer than
+// eight lanes share a row, a quarter-warp's 128-bit loads touch several rows, and the pad of G * 16 bytes
+// puts those rows on different banks.
 struct RowGeom {
-    int nchunks, G, R;
+    int nchunks, G, R, pitch;
 };
 
 // One warp's ring.  A slot holds R input rows and, with a fused Add, R addend rows behind them.
@@ -116,21 +120,24 @@ struct Ring {
     const uint8_t* x; long long ldx;
     const uint8_t* addend; long long ldadd;  // byte pitch
     long long rows;
-    uint32_t row_bytes, add_row_bytes;
+    uint32_t row_bytes;   // bytes copied per row
+    uint32_t pitch;       // distance between rows inside a slot (row_bytes + bank-spreading pad)
     int R;
 };
 
-// lane 0 only
-__device__ __forceinline__ void ring_issue(const Ring& c, long long item, int stage) {
+// Whole warp: lane 0 arms the barrier, lane r (and r + 32, ...) issues the copies of row r, so the R rows of
+// an item are requested in parallel instead of one after another.  A copy may complete before the barrier
+// has been armed: the phase cannot finish until lane 0's arrival.
+__device__ __forceinline__ void ring_issue(const Ring& c, long long item, int stage, int lane) {
     const long long row0 = item * c.R;
     long long nrows = c.rows - row0;
     if (nrows > c.R) nrows = c.R;
     const uint32_t bar = c.bars + stage * 8;
     const uint32_t dst = c.slots + stage * c.slot_bytes;
-    mbar_expect_tx(bar, (uint32_t)nrows * (c.row_bytes + (c.addend ? c.add_row_bytes : 0u)));
-    for (int r = 0; r < (int)nrows; ++r) {
-        bulk_load(dst + r * c.row_bytes, c.x + (row0 + r) * c.ldx, c.row_bytes, bar);
-        if (c.addend) bulk_load(dst + c.add_off + r * c.add_row_bytes, c.addend + (row0 + r) * c.ldadd, c.add_row_bytes, bar);
+    if (lane == 0) mbar_expect_tx(bar, (uint32_t)nrows * c.row_bytes * (c.addend ? 2u : 1u));
+    if (lane < (int)nrows) {
+        bulk_load(dst + lane * c.pitch, c.x + (row0 + lane) * c.ldx, c.row_bytes, bar);
+        if (c.addend) bulk_load(dst + c.add_off + lane * c.pitch, c.addend + (row0 + lane) * c.ldadd, c.row_bytes, bar);
     }
 }
 
@@ -223,9 +230,9 @@ __global__ void __launch_bounds__(kThreads) layernorm_fast_kernel(LnFastArgs a) 
     }
     Ring rc;
     rc.R = R;
-    rc.row_bytes = (uint32_t)cols; rc.add_row_bytes = (uint32_t)cols;
-    rc.add_off = (uint32_t)(R * cols);
-    rc.slot_bytes = (uint32_t)(R * cols) * (HAS_ADD ? 2u : 1u);
+    rc.row_bytes = (uint32_t)cols; rc.pitch = (uint32_t)a.geom.pitch;
+    rc.add_off = (uint32_t)(R * a.geom.pitch);
+    rc.slot_bytes = (uint32_t)(R * a.geom.pitch) * (HAS_ADD ? 2u : 1u);
     rc.bars = s_bar + warp * a.stages * 8;
     const uint32_t ring0 = (s_bar + kWarps * a.stages * 8 + 127u) & ~127u;
     rc.slots = ring0 + warp * a.stages * rc.slot_bytes;
@@ -240,11 +247,10 @@ __global__ void __launch_bounds__(kThreads) layernorm_fast_kernel(LnFastArgs a) 
     const long long n_items = (a.rows + R - 1) / R;
     const long long warp_global = (long long)blockIdx.x * kWarps + warp;
     const long long total_warps = (long long)gridDim.x * kWarps;
-    if (lane == 0)
-        for (int s = 0; s < a.stages; ++s) {
-            const long long it = warp_global + (long long)s * total_warps;
-            if (it < n_items) ring_issue(rc, it, s);
-        }
+    for (int s = 0; s < a.stages; ++s) {
+        const long long it = warp_global + (long long)s * total_warps;
+        if (it < n_items) ring_issue(rc, it, s, lane);
+    }
 
     const float out_mul = __int_as_float((127 - (a.s_out + 85)) << 23);  // 2^-(s_out + 85)
     const float c0g = (float)a.c0_gamma;
@@ -252,7 +258,7 @@ __global__ void __launch_bounds__(kThreads) layernorm_fast_kernel(LnFastArgs a) 
     const int clamp_threshold = (32767 * 128) / a.gamma_absmax;  // inv_std above this may overflow int16
     const bool nearest = a.rounding == A4C_RND_CONV_EVEN || a.rounding == A4C_RND_POSITIVE_INF ||
                          a.rounding == A4C_RND_NEGATIVE_INF;
-    const uint32_t lane_in_slot = (uint32_t)(sub * cols + gl * 16);
+    const uint32_t lane_in_slot = (uint32_t)(sub * a.geom.pitch + gl * 16);
     const uint32_t lane_param = (uint32_t)gl * 16u;
     const long long step_rows = total_warps * R;
     long long row = warp_global * R + sub;
@@ -270,11 +276,11 @@ __global__ void __launch_bounds__(kThreads) layernorm_fast_kernel(LnFastArgs a) 
             if (HAS_ADD) av[j] = ok ? lds128(slot + rc.add_off + j * G * 16) : make_uint4(0, 0, 0, 0);
         }
         __syncwarp();
-        if (lane == 0) {
+        {
             const long long nxt = item + (long long)a.stages * total_warps;
-            if (nxt < n_items) {
+            if (nxt < n_items && lane < R) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                ring_issue(rc, nxt, stage);
+                ring_issue(rc, nxt, stage, lane);
             }
         }
         if (++stage == a.stages) { stage = 0; parity ^= 1u; }
@@ -428,9 +434,9 @@ __global__ void __launch_bounds__(kThreads) softmax_fast_kernel(SmFastArgs a) {
     }
     Ring rc;
     rc.R = R;
-    rc.row_bytes = (uint32_t)cols; rc.add_row_bytes = (uint32_t)cols;
-    rc.add_off = (uint32_t)(R * cols);
-    rc.slot_bytes = (uint32_t)(R * cols) * (HAS_ADD ? 2u : 1u);
+    rc.row_bytes = (uint32_t)cols; rc.pitch = (uint32_t)a.geom.pitch;
+    rc.add_off = (uint32_t)(R * a.geom.pitch);
+    rc.slot_bytes = (uint32_t)(R * a.geom.pitch) * (HAS_ADD ? 2u : 1u);
     rc.bars = s_bar + warp * a.stages * 8;
     rc.slots = ring0 + warp * a.stages * rc.slot_bytes;
     rc.x = reinterpret_cast<const uint8_t*>(a.x); rc.ldx = a.ldx;
@@ -444,17 +450,16 @@ __global__ void __launch_bounds__(kThreads) softmax_fast_kernel(SmFastArgs a) {
     const long long n_items = (a.rows + R - 1) / R;
     const long long warp_global = (long long)blockIdx.x * kWarps + warp;
     const long long total_warps = (long long)gridDim.x * kWarps;
-    if (lane == 0)
-        for (int s = 0; s < a.stages; ++s) {
-            const long long it = warp_global + (long long)s * total_warps;
-            if (it < n_items) ring_issue(rc, it, s);
-        }
+    for (int s = 0; s < a.stages; ++s) {
+        const long long it = warp_global + (long long)s * total_warps;
+        if (it < n_items) ring_issue(rc, it, s, lane);
+    }
     const uint32_t lut_lane = s_base + (uint32_t)lane * 4u;
     const int numer = 255 << a.inv_shift;  // inv_shift <= 22 on this path
     const float numer_f = (float)numer;     // exact: 255 * 2^k
     const float out_mul = __int_as_float((127 - (a.inv_shift + 85)) << 23);  // 2^-(inv_shift + 85)
     const uint32_t group_mask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (sub * G));
-    const uint32_t lane_in_slot = (uint32_t)(sub * cols + gl * 16);
+    const uint32_t lane_in_slot = (uint32_t)(sub * a.geom.pitch + gl * 16);
     const long long step_rows = total_warps * R;
     long long row = warp_global * R + sub;
 
@@ -477,11 +482,11 @@ __global__ void __launch_bounds__(kThreads) softmax_fast_kernel(SmFastArgs a) {
             if (HAS_ADD) av[j] = ok ? lds128(slot + rc.add_off + j * G * 16) : make_uint4(0, 0, 0, 0);
         }
         __syncwarp();
-        if (lane == 0) {
+        {
             const long long nxt = item + (long long)a.stages * total_warps;
-            if (nxt < n_items) {
+            if (nxt < n_items && lane < R) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                ring_issue(rc, nxt, stage);
+                ring_issue(rc, nxt, stage, lane);
             }
         }
         if (++stage == a.stages) { stage = 0; parity ^= 1u; }
@@ -564,13 +569,20 @@ __global__ void __launch_bounds__(kThreads) softmax_fast_kernel(SmFastArgs a) {
     }
 }
 
-RowGeom make_geom(int cols) {
+// Tuning overrides (0 = the launcher's own choice).  Chunks per lane: how many 16-element chunks of a row one
+// lane works on; the per-row scalar work is amortised over them, at the price of registers and ring bytes.
+int g_min_stages = 0;
+int g_chunks_per_lane = 0;
+
+RowGeom make_geom(int cols, int preferred_nch) {
     RowGeom g;
     g.nchunks = cols / 16;
+    const int target = g_chunks_per_lane > 0 ? g_chunks_per_lane : preferred_nch;
     int G = 1;
-    while (G < g.nchunks && G < 32) G <<= 1;
+    while (G * target < g.nchunks && G < 32) G <<= 1;
     g.G = G;
     g.R = 32 / G;
+    g.pitch = cols + ((G < 8 && cols % 128 == 0) ? G * 16 : 0);
     return g;
 }
 
@@ -586,8 +598,9 @@ int sm_count() {
 void plan_launch(size_t fixed, size_t slot, long long n_items, int* stages, size_t* smem, int* grid) {
     int st = 4;
     size_t bytes = fixed + kWarps * st * 8 + 128 + (size_t)kWarps * st * slot;
-    if (bytes > 72 * 1024) {  // keep at least three blocks per SM resident
-        st = 3;
+    const int min_st = g_min_stages > 0 ? g_min_stages : 2;
+    while (bytes > 72 * 1024 && st > min_st) {  // prefer three blocks per SM over a deeper ring
+        --st;
         bytes = fixed + kWarps * st * 8 + 128 + (size_t)kWarps * st * slot;
     }
     int per_sm = (int)((220 * 1024) / bytes);
@@ -600,6 +613,11 @@ void plan_launch(size_t fixed, size_t slot, long long n_items, int* stages, size
 }
 
 }  // namespace
+
+void a4c_rowops_fast_tuning(int chunks_per_lane, int min_stages) {
+    if (chunks_per_lane >= 0) g_chunks_per_lane = chunks_per_lane;
+    if (min_stages >= 0) g_min_stages = min_stages;
+}
 
 // Returns A4C_ERR_UNSUPPORTED when the request is outside the fast path's proofs (caller falls back
 // to the generic kernel).
@@ -626,11 +644,11 @@ int a4c_launch_layernorm_fast(const int8_t* x, long long ldx, const int16_t* gam
         default: break;
     }
     a.c0_out += (float)(128 << s_out);  // outputs are produced biased by +128
-    a.geom = make_geom(cols);
+    a.geom = make_geom(cols, 4);   // measured best at every row length from 128 to 2048
     const int nch = (a.geom.nchunks + a.geom.G - 1) / a.geom.G;
     if (nch != 1 && nch != 2 && nch != 4) return A4C_ERR_UNSUPPORTED;
     const size_t fixed = (size_t)nch * 4 * 32 * 4 * 4 * 2;
-    const size_t slot = (size_t)a.geom.R * cols * (addend ? 2 : 1);
+    const size_t slot = (size_t)a.geom.R * a.geom.pitch * (addend ? 2 : 1);
     const long long n_items = (rows + a.geom.R - 1) / a.geom.R;
     size_t smem; int grid;
     plan_launch(fixed, slot, n_items, &a.stages, &smem, &grid);
@@ -667,10 +685,11 @@ int a4c_launch_softmax_fast(const int8_t* x, long long ldx, const void* addend, 
     a.x = x; a.ldx = ldx; a.addend = (const uint8_t*)addend; a.ldadd = ldadd; a.out = (uint8_t*)out; a.ldo = ldo;
     a.rows = rows; a.cols = cols; a.mode = mode; a.B = B; a.S = S; a.Dmax = Dmax; a.inv_shift = inv_shift;
     a.use_clb = use_clb; a.exp_kq = exp_kq; a.status = status;
-    a.geom = make_geom(cols);
+    // four chunks per lane keep 64 scores in registers: worth it only with the fused Add on long rows
+    a.geom = make_geom(cols, (addend && cols >= 512) ? 4 : 2);
     const int nch = (a.geom.nchunks + a.geom.G - 1) / a.geom.G;
-    if (nch != 1 && nch != 2) return A4C_ERR_UNSUPPORTED;
-    const size_t slot = (size_t)a.geom.R * cols * (addend ? 2 : 1);
+    if (nch != 1 && nch != 2 && nch != 4) return A4C_ERR_UNSUPPORTED;
+    const size_t slot = (size_t)a.geom.R * a.geom.pitch * (addend ? 2 : 1);
     const long long n_items = (rows + a.geom.R - 1) / a.geom.R;
     size_t smem; int grid;
     plan_launch(256 * 32 * 4, slot, n_items, &a.stages, &smem, &grid);
@@ -681,7 +700,8 @@ int a4c_launch_softmax_fast(const int8_t* x, long long ldx, const void* addend, 
         softmax_fast_kernel<NCH_, ADD_><<<grid, kThreads, smem, stream>>>(a);                                      \
     } while (0)
     if (nch == 1) { if (addend) SM_LAUNCH(1, true); else SM_LAUNCH(1, false); }
-    else { if (addend) SM_LAUNCH(2, true); else SM_LAUNCH(2, false); }
+    else if (nch == 2) { if (addend) SM_LAUNCH(2, true); else SM_LAUNCH(2, false); }
+    else { if (addend) SM_LAUNCH(4, true); else SM_LAUNCH(4, false); }
 #undef SM_LAUNCH
     return cudaGetLastError() == cudaSuccess ? A4C_OK : A4C_ERR_CUDA;
 }

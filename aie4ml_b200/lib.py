@@ -25,6 +25,8 @@ A4C_ERR_DEVICE_TIMEOUT = -6
 ALGO_AUTO, ALGO_SIMT, ALGO_TCGEN05, ALGO_TCGEN05_PAIR = 0, 1, 2, 3
 OPT_ROWOP_PATH = 0
 OPT_BMM_PATH = 1
+OPT_ROWOP_CHUNKS_PER_LANE = 2
+OPT_ROWOP_MIN_STAGES = 3
 
 # name -> (restype, argtypes); mirrors the header declaration by declaration
 SIGNATURES = {

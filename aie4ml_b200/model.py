@@ -31,6 +31,7 @@ class CudaModel:
         self.source_model = source_model
         self._lowered = False
         self.plan = None
+        self._pipeline = None
 
     # -- reference-compatible surface -------------------------------------------------------------
     @classmethod
@@ -81,14 +82,29 @@ class CudaModel:
         iterations = int(self._ctx.aie_config.get('Iterations', 1))
         prepared = self.prepare_inputs(X, iterations=iterations, quantize=quantize_in)
         outs: Dict[str, list] = {name: [] for name in graph.output_tensor_names}
-        for it in range(iterations):
-            for name, arr in prepared.items():
-                host = torch.from_numpy(np.ascontiguousarray(arr[it]))
-                plan.tensor_of(name).copy_(host.to(plan.device, non_blocking=False))
-            plan.run()
-            plan.check_status()
-            for name in outs:
-                outs[name].append(plan.tensor_of(name).cpu().numpy().astype(np.int64))
+        if iterations > 1 and all(int(graph.tensors[n].shape[0]) == int(graph.tensors[graph.input_tensor_names[0]].shape[0])
+                                  for n in list(graph.input_tensor_names) + list(graph.output_tensor_names)):
+            # iterations are chunks of one long batch: copy-in, launches and copy-out overlap across them
+            pipe = self.pipeline()
+            host_in = {n: torch.from_numpy(np.ascontiguousarray(a.reshape(-1, *a.shape[2:]))).pin_memory()
+                       for n, a in prepared.items()}
+            host_out = {}
+            for n in outs:
+                t = plan.tensor_of(n)
+                host_out[n] = torch.empty((iterations * t.shape[0], *t.shape[1:]), dtype=t.dtype).pin_memory()
+            pipe.run_and_wait(host_in, host_out)
+            for n in outs:
+                arr = host_out[n].numpy().astype(np.int64)
+                outs[n] = list(arr.reshape(iterations, -1, *arr.shape[1:]))
+        else:
+            for it in range(iterations):
+                for name, arr in prepared.items():
+                    host = torch.from_numpy(np.ascontiguousarray(arr[it]))
+                    plan.tensor_of(name).copy_(host.to(plan.device, non_blocking=False))
+                plan.run()
+                plan.check_status()
+                for name in outs:
+                    outs[name].append(plan.tensor_of(name).cpu().numpy().astype(np.int64))
         result: Dict[str, np.ndarray] = {}
         for name, chunks in outs.items():
             arr = np.stack(chunks, axis=0)
@@ -98,6 +114,16 @@ class CudaModel:
         if len(result) == 1:
             return next(iter(result.values()))
         return result
+
+    def pipeline(self, depth: int = 3):
+        """The streaming executor for host batches longer than the model's own batch: ``depth`` buffer
+        sets, copy-in / launches / copy-out on three streams (see ``streaming.HostPipeline``)."""
+        from .streaming import HostPipeline
+
+        self.build()
+        if self._pipeline is None or len(self._pipeline.plans) != depth:
+            self._pipeline = HostPipeline(self._ctx, depth, first_plan=self.plan)
+        return self._pipeline
 
     # -- helpers ----------------------------------------------------------------------------------
     def tensor_dtype(self, name: str):

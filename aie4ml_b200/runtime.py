@@ -109,7 +109,7 @@ class Plan:
     """Buffers, views, device constants and the launch list of one lowered model."""
 
     def __init__(self, ctx: BackendContext, device: Optional[str] = None, fuse_rowop_add: bool = True,
-                 dense_algo: int = _lib.ALGO_AUTO):
+                 dense_algo: int = _lib.ALGO_AUTO, share_params: Optional['Plan'] = None):
         torch = _torch()
         self.ctx = ctx
         self.lib = _lib.load()
@@ -118,6 +118,7 @@ class Plan:
                                'CPU execution path.')
         self.device = torch.device(device or f'cuda:{torch.cuda.current_device()}')
         self.dense_algo = int(dense_algo)
+        self.fuse_rowop_add = bool(fuse_rowop_add)
         graph = ctx.ir.logical
         self.graph = graph
 
@@ -183,9 +184,15 @@ class Plan:
             self._view(name)
 
         # 4. device constants
+        #    (a second plan of the same model on the same device reuses the first one's constants)
         self.params: Dict[str, Any] = {}
-        for key, arr in self.params_np.items():
-            self.params[key] = torch.from_numpy(np.ascontiguousarray(arr)).to(self.device)
+        if share_params is not None:
+            if share_params.device != self.device or set(share_params.params) != set(self.params_np):
+                raise ValueError('share_params: the other plan holds different constants or lives on another device.')
+            self.params = share_params.params
+        else:
+            for key, arr in self.params_np.items():
+                self.params[key] = torch.from_numpy(np.ascontiguousarray(arr)).to(self.device)
 
         # 5. launches
         self.launches: List[Tuple[Callable, tuple]] = []

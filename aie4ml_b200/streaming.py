@@ -1,0 +1,121 @@
+"""Host-to-host execution of a lowered model as a three-stage stream pipeline.
+
+A lowered graph is independent along its leading (batch) axis, so a host batch of any length is
+cut into chunks of the plan's own batch size and the chunks flow through
+
+    copy-in stream   : pinned host rows  -> device input buffers of slot s
+    compute stream   : the plan's launches (or its captured CUDA graph) on slot s
+    copy-out stream  : device output buffers of slot s -> pinned host rows
+
+with ``depth`` slots in flight, ordered by CUDA events only (no host synchronisation inside the
+loop).  Copy-in of chunk i+1, compute of chunk i and copy-out of chunk i-1 overlap, so the step
+costs max(H2D, compute, D2H) instead of their sum; on a PCIe-attached GPU the two copy directions
+run concurrently.  This is the executor behind ``CudaModel.predict`` when ``Iterations`` > 1
+(the reference runs its simulator once per iteration, ``src/aie4ml/simulation.py:199-245``).
+
+Slots share one set of device constants; each slot owns its activation buffers.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+from . import lib as _lib
+from .runtime import Plan
+
+
+class HostPipeline:
+    def __init__(self, ctx, depth: int = 3, *, first_plan: Optional[Plan] = None, fuse_rowop_add: bool = True,
+                 dense_algo: int = _lib.ALGO_AUTO, use_graph: bool = True):
+        """``first_plan``: an existing plan of ``ctx`` to use as slot 0 (its fusion and algorithm
+        settings apply to every slot); otherwise ``fuse_rowop_add`` / ``dense_algo`` configure a new one."""
+        import torch
+
+        if depth < 1:
+            raise ValueError('depth must be at least 1')
+        self.torch = torch
+        first = first_plan or Plan(ctx, fuse_rowop_add=fuse_rowop_add, dense_algo=dense_algo)
+        self.plans: List[Plan] = [first]
+        for _ in range(depth - 1):
+            self.plans.append(Plan(ctx, device=str(first.device), fuse_rowop_add=first.fuse_rowop_add,
+                                   dense_algo=first.dense_algo, share_params=first))
+        self.device = first.device
+        graph = first.graph
+        self.in_names = list(graph.input_tensor_names)
+        self.out_names = list(graph.output_tensor_names)
+        self.chunk_rows = int(graph.tensors[self.in_names[0]].shape[0])
+        for n in self.in_names + self.out_names:
+            if int(graph.tensors[n].shape[0]) != self.chunk_rows:
+                raise ValueError(f'{n}: leading extent differs from the batch size {self.chunk_rows}; '
+                                 'the graph cannot be streamed along its first axis.')
+        if use_graph:
+            for p in self.plans:
+                if p.graph_exec is None and len(p.launches) > 1:
+                    p.capture()
+        self.s_in = torch.cuda.Stream(self.device)
+        self.s_run = torch.cuda.Stream(self.device)
+        self.s_out = torch.cuda.Stream(self.device)
+        mk = lambda: [torch.cuda.Event() for _ in self.plans]
+        self.ev_in, self.ev_run, self.ev_out = mk(), mk(), mk()
+        self.launches_per_chunk = len(first.launches)
+
+    def chunks_for(self, rows: int) -> int:
+        return (int(rows) + self.chunk_rows - 1) // self.chunk_rows
+
+    def run(self, host_in: Dict[str, 'object'], host_out: Dict[str, 'object']) -> int:
+        """Stream ``host_in[name][r]`` for every row r through the model into ``host_out``.
+
+        Host tensors are torch CPU tensors (pinned for asynchronous copies) shaped ``[rows, ...]``
+        with the graph tensor's trailing extents; ``rows`` need not be a multiple of the chunk.  A
+        short last chunk runs at full chunk size over whatever the slot's buffers hold beyond the
+        copied rows (operators never mix rows), and only its valid rows are copied back.
+        Returns the number of chunks.  The call only enqueues: the caller's current stream is made to
+        wait for all three pipeline streams, so synchronise it (or use ``run_and_wait``) before
+        reading ``host_out``.
+        """
+        torch = self.torch
+        rows = int(host_in[self.in_names[0]].shape[0])
+        for n in self.in_names:
+            if int(host_in[n].shape[0]) != rows:
+                raise ValueError(f'{n}: every input needs the same number of rows ({rows}).')
+        for n in self.out_names:
+            if int(host_out[n].shape[0]) != rows:
+                raise ValueError(f'{n}: output buffer needs {rows} rows.')
+        n_chunks = self.chunks_for(rows)
+        depth = len(self.plans)
+        origin = torch.cuda.current_stream(self.device)
+        start = torch.cuda.Event()
+        start.record(origin)
+        for s in (self.s_in, self.s_run, self.s_out):
+            s.wait_event(start)
+        for c in range(n_chunks):
+            slot = c % depth
+            plan = self.plans[slot]
+            r0 = c * self.chunk_rows
+            r1 = min(rows, r0 + self.chunk_rows)
+            with torch.cuda.stream(self.s_in):
+                if c >= depth:
+                    self.s_in.wait_event(self.ev_run[slot])     # the slot's inputs have been consumed
+                for n in self.in_names:
+                    plan.tensor_of(n)[: r1 - r0].copy_(host_in[n][r0:r1], non_blocking=True)
+                self.ev_in[slot].record(self.s_in)
+            with torch.cuda.stream(self.s_run):
+                self.s_run.wait_event(self.ev_in[slot])
+                if c >= depth:
+                    self.s_run.wait_event(self.ev_out[slot])    # the slot's outputs have been read back
+                plan.run()
+                self.ev_run[slot].record(self.s_run)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(self.ev_run[slot])
+                for n in self.out_names:
+                    host_out[n][r0:r1].copy_(plan.tensor_of(n)[: r1 - r0], non_blocking=True)
+                self.ev_out[slot].record(self.s_out)
+        for s in (self.s_in, self.s_run, self.s_out):
+            origin.wait_stream(s)
+        return n_chunks
+
+    def run_and_wait(self, host_in, host_out) -> int:
+        n = self.run(host_in, host_out)
+        self.torch.cuda.synchronize(self.device)
+        self.plans[0].check_status()
+        return n

@@ -53,6 +53,9 @@ extern "C" {
 /* Options for a4c_set_option */
 #define A4C_OPT_ROWOP_PATH 0 /* 0 = auto (bandwidth-oriented row kernels when they apply), 1 = generic kernels only */
 #define A4C_OPT_BMM_PATH 1   /* 0 = auto (tcgen05 batched MatMul when its alignment rules hold), 1 = dp4a kernel only */
+/* Tuning of the bandwidth-oriented row kernels (results do not depend on either): */
+#define A4C_OPT_ROWOP_CHUNKS_PER_LANE 2 /* 0 = automatic (default), else 1, 2 or 4: 16-element chunks of one row per lane */
+#define A4C_OPT_ROWOP_MIN_STAGES 3      /* 0 = automatic (default), else 2..4: least depth of the per-warp copy ring */
 
 /* Library version (major*10000 + minor*100 + patch). */
 A4C_API int a4c_version(void);

@@ -165,16 +165,22 @@ def test_bmm_attention_shapes(bmm_path):
                                   oracle.matmul(a, b, shift=4, tok='floor', transpose_a=True, out_dtype='int16'))
 
 
-@pytest.fixture(params=['auto', 'generic'])
+@pytest.fixture(params=['auto', 'generic', 'chunks1', 'chunks2', 'chunks4'])
 def rowop_path(request):
-    """Runs a row-op test once with automatic kernel selection (bandwidth-oriented kernels where they
-    apply) and once with the generic integer kernels forced."""
+    """Runs a row-op test with automatic kernel selection (bandwidth-oriented kernels where they
+    apply), with the generic integer kernels forced, and with every work split of the
+    bandwidth-oriented kernels forced (16-element chunks per lane; shortest copy ring)."""
     from aie4ml_b200 import lib as a4c
 
     L = a4c.load()
-    assert L.a4c_set_option(a4c.OPT_ROWOP_PATH, 0 if request.param == 'auto' else 1) == 0
+    assert L.a4c_set_option(a4c.OPT_ROWOP_PATH, 1 if request.param == 'generic' else 0) == 0
+    if request.param.startswith('chunks'):
+        assert L.a4c_set_option(a4c.OPT_ROWOP_CHUNKS_PER_LANE, int(request.param[-1])) == 0
+        assert L.a4c_set_option(a4c.OPT_ROWOP_MIN_STAGES, 2) == 0
     yield request.param
     assert L.a4c_set_option(a4c.OPT_ROWOP_PATH, 0) == 0
+    assert L.a4c_set_option(a4c.OPT_ROWOP_CHUNKS_PER_LANE, 0) == 0
+    assert L.a4c_set_option(a4c.OPT_ROWOP_MIN_STAGES, 0) == 0
 
 
 def _ln_inputs(seed, rows, cols):
