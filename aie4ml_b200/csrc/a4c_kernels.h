@@ -51,6 +51,17 @@ int a4c_launch_bmm_tc(const void* A, long long lda, long long stride_a, const vo
                       void* C, long long ldc, long long stride_c, long long batch, int M, int K, int N, int trans_b,
                       int shift, int rounding, int out_dtype, int a_unsigned, int* status_word, cudaStream_t stream);
 
+// Fused attention head (attention_tc.cu): scores, softmax and the value product in one kernel.
+int a4c_attention_tc_supported(const void* q, long long ldq, long long stride_q, const void* k, long long ldk,
+                               long long stride_k, const void* v, long long ldv, long long stride_v, const void* out,
+                               long long ldo, long long stride_o, long long batch, int sq, int sk, int dh, int qk_shift,
+                               int pv_shift, int sm_mode, int B, int S, int Dmax, int inv_shift);
+int a4c_launch_attention_tc(const void* q, long long ldq, long long stride_q, const void* k, long long ldk,
+                            long long stride_k, const void* v, long long ldv, long long stride_v, void* out,
+                            long long ldo, long long stride_o, long long batch, int sq, int sk, int dh, int qk_shift,
+                            int pv_shift, int rounding, int sm_mode, int B, int S, int Dmax, int inv_shift, int use_clb,
+                            int exp_kq, int* status_word, cudaStream_t stream);
+
 // CTA-pair (cta_group::2) Dense: one 256 x 256 tile per two SMs (dense_tc2.cu); same argument rules as
 // a4c_launch_dense_tc.
 int a4c_launch_dense_tc2(const void* A, long long lda, const void* Wt, long long ldw, const int32_t* bias,

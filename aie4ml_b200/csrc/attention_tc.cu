@@ -1,0 +1,511 @@
+// One attention head per launch, fused:  O_b = srs( softmax_u8( srs(Q_b . K_b^T) ) . V_b )  for every batch
+// entry b, with the scores and probabilities never leaving the SM.
+//
+// This is the chain  matmul_single::run (matmul.cpp:32-118, TRANSPOSE_B) -> softmax (softmax.cpp:20-88 HCCS,
+// :252-384 exp) -> matmul_single::run  of aie4ml, with every intermediate rounding and saturation kept:
+//   scores  s[m,n] = sat_i8(round_shift(sum_d Q[m,d] K[n,d], qk_shift))
+//   probs   p[m,n] = min((score(max_n s - s[m,n]) * inv) >> inv_shift, 255),  inv from the row's score sum
+//   out     o[m,d] = sat_i8(round_shift(sum_n p[m,n] V[n,d], pv_shift))
+// The three kernels it replaces move the [rows, keys] score and probability matrices through HBM four times;
+// here HBM sees Q, K, V once and O once.
+//
+// Shape of the kernel (one CTA per SM, persistent over (batch entry, 128-query tile) items):
+//   warp 0      TMA producer: Q tile [128 x 64], K [128 keys x 64], V [128 keys x 64] per item, 64-byte swizzle,
+//               4-stage ring
+//   warp 1      MMA issuer: S = Q K^T (M128 N128 K64, both operands K-major) into one of two TMEM score
+//               buffers; later O = P V (M128 N64 K128, P K-major from shared memory, V MN-major) into one of
+//               two TMEM output buffers.  The next item's S is issued before this item's O, so the tensor
+//               pipe works on scores while the softmax warps are busy.
+//   warps 2-5   softmax group 0 (even items), warps 6-9 group 1 (odd items).  A thread owns one query row
+//               (its TMEM lane): tcgen05.ld of 128 accumulators, requantise, row maximum, score table lookup
+//               (per-lane replicated table in shared memory: no bank conflicts), sum, reciprocal, normalise,
+//               and the uint8 probabilities go to shared memory in the 128-byte-swizzled K-major layout the
+//               second MMA reads.  Then the same thread converts its O row and stores it.
+// Every wait is bounded (tc::mbar_wait): on a timeout the CTA sets the status word and drains.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "a4c_common.cuh"
+#include "a4c_kernels.h"
+#include "tc_common.cuh"
+
+using namespace tc;
+
+namespace {
+
+constexpr int BM = 128;        // query rows per item
+constexpr int SK = 128;        // keys per batch entry (exactly)
+constexpr int DH = 64;         // head width
+constexpr int UMMA_K = 32;
+constexpr int STAGES = 4;
+constexpr int TILE_BYTES = 128 * DH;              // 8 KB: Q, K and V tiles alike
+constexpr int STAGE_BYTES = 3 * TILE_BYTES;
+constexpr int P_BYTES = BM * SK;                  // 16 KB per softmax group
+constexpr int LUT_BYTES = 256 * 32 * 4;
+constexpr int GROUPS = 2;
+constexpr int GROUP_THREADS = 128;
+constexpr int NUM_THREADS = 64 + GROUPS * GROUP_THREADS;
+constexpr int TMEM_COLS = 512;                    // scores at columns g*128, outputs at 256 + g*64
+constexpr int MODE_HALF_UP_CLAMP = 100;           // positive_inf, both shifts in [1, 22]: saturate before the shift
+
+constexpr float TWO_M64 = 5.421010862427522e-20f;  // 2^-64
+constexpr float TWO_P64 = 18446744073709551616.0f; // 2^64
+
+struct Tail {
+    uint64_t qkv_full[STAGES];
+    uint64_t qkv_empty[STAGES];
+    uint64_t s_full[GROUPS];
+    uint64_t p_full[GROUPS];
+    uint64_t o_full[GROUPS];
+    uint32_t tmem_base;
+    volatile int abort_flag;
+};
+
+constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (size_t)GROUPS * P_BYTES + LUT_BYTES + sizeof(Tail);
+
+struct AttnArgs {
+    uint8_t* out; long long ldo, stride_o;
+    long long batch; int sq, m_tiles;
+    // requantisation of the scores (1) and of the outputs (2)
+    int shift1, shift2;
+    uint32_t mask1, c01, mask2, c02;          // generic rounding constants
+    int xhi1, addb1, xlob1;                   // MODE_HALF_UP_CLAMP, biased by +128: see requant_biased
+    int xhi2, half2, xlo2;
+    // softmax
+    int mode, B, S, Dmax, inv_shift, use_clb, exp_kq;
+    int* status;
+};
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        :: "r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+// K-major operand whose K extent is one 64-byte swizzle row: rows of 64 bytes, 8-row groups 512 bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc_k64(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(512 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)4 << 61;              // SWIZZLE_64B
+    return d;
+}
+// MN-major operand, 64-byte swizzle: k-rows of 64 bytes, 8-row groups 512 bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc_mn64(uint32_t saddr) { return make_smem_desc_k64(saddr); }
+
+__device__ __forceinline__ float lds32f(uint32_t a) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" :: "r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
+// exp_score16, softmax.cpp:252-273
+__device__ __forceinline__ int exp_score16(int d, int kq) {
+    const int z = min(d * kq, 32767);
+    const int zint = z >> 8, zfrac = z & 255;
+    const int t = (zfrac * 2811) >> 8;
+    const int inner = t - 11004;
+    const int t2 = (inner * zfrac) >> 8;
+    const int e = t2 + 16384;
+    return zint >= 16 ? 0 : (e >> (zint & 15));
+}
+
+// Score accumulator -> int8 score + 128 (an unsigned byte whose order is the signed order).
+template <int MODE>
+__device__ __forceinline__ int requant_biased(int acc, const AttnArgs& g) {
+    if (MODE == MODE_HALF_UP_CLAMP) {
+        // min(acc, 127 * 2^s), then + 2^(s-1) + 128 * 2^s with the lower clamp folded in, then the shift
+        return __viaddmax_s32(min(acc, g.xhi1), g.addb1, g.xlob1) >> g.shift1;
+    }
+    int v = acc;
+    if (MODE == A4C_RND_FLOOR) v = acc >> g.shift1;
+    else if (MODE >= 0) v = round_shift_i32_t<MODE>(acc, g.shift1, g.mask1, g.c01);
+    return min(max(v, -128), 127) + 128;
+}
+
+template <int MODE>
+__device__ __forceinline__ int requant_out(int acc, const AttnArgs& g) {
+    if (MODE == MODE_HALF_UP_CLAMP) return __viaddmax_s32(min(acc, g.xhi2), g.half2, g.xlo2) >> g.shift2;
+    int v = acc;
+    if (MODE == A4C_RND_FLOOR) v = acc >> g.shift2;
+    else if (MODE >= 0) v = round_shift_i32_t<MODE>(acc, g.shift2, g.mask2, g.c02);
+    return min(max(v, -128), 127);
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                    const __grid_constant__ CUtensorMap tmap_v, AttnArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* p_smem = smem + (size_t)STAGES * STAGE_BYTES;
+    float* lut = reinterpret_cast<float*>(p_smem + (size_t)GROUPS * P_BYTES);
+    Tail* tail = reinterpret_cast<Tail*>(reinterpret_cast<uint8_t*>(lut) + LUT_BYTES);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const long long num_items = g.batch * g.m_tiles;
+    // items of this CTA: blockIdx.x, + gridDim.x, ...; n is the CTA-local index
+    const long long first = blockIdx.x;
+    const int n_local = first < num_items ? (int)((num_items - first + gridDim.x - 1) / gridDim.x) : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&tail->qkv_full[s], 1); mbar_init(&tail->qkv_empty[s], 1); }
+        for (int s = 0; s < GROUPS; ++s) {
+            mbar_init(&tail->s_full[s], 1);
+            mbar_init(&tail->p_full[s], GROUP_THREADS);
+            mbar_init(&tail->o_full[s], 1);
+        }
+        tail->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(smem_u32(&tail->tmem_base)), "r"((uint32_t)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    {
+        // score table: entry d (= row maximum - score, 0..255) replicated across 32 lanes, scaled by 2^-64 so
+        // that the normalising multiply lands in a subnormal whose bit pattern is the integer result
+        float* stage_sc = reinterpret_cast<float*>(p_smem);
+        if (threadIdx.x < 256) {
+            const int d = threadIdx.x;
+            int s;
+            if (g.mode == 0) s = clampi(g.B - g.S * min(d, g.Dmax), -32768, 32767);
+            else s = exp_score16(d, g.exp_kq);
+            stage_sc[d] = (float)s * TWO_M64;
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < 256 * 32; i += NUM_THREADS) lut[i] = stage_sc[i >> 5];
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tail->tmem_base;
+    volatile int* abort_flag = &tail->abort_flag;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            bool ok = true;
+            for (int n = 0; ok && n < n_local; ++n) {
+                const long long item = first + (long long)n * gridDim.x;
+                const int b = (int)(item / g.m_tiles);
+                const int m0 = (int)(item % g.m_tiles) * BM;
+                const int stage = n % STAGES;
+                const uint32_t ph = (uint32_t)(n / STAGES) & 1u;
+                ok = mbar_wait(&tail->qkv_empty[stage], ph ^ 1u, abort_flag, g.status, 121);
+                if (!ok) break;
+                uint8_t* st = smem + (size_t)stage * STAGE_BYTES;
+                mbar_arrive_expect_tx(&tail->qkv_full[stage], STAGE_BYTES);
+                tma_load_3d(st, &tmap_q, &tail->qkv_full[stage], 0, m0, b);
+                tma_load_3d(st + TILE_BYTES, &tmap_k, &tail->qkv_full[stage], 0, 0, b);
+                tma_load_3d(st + 2 * TILE_BYTES, &tmap_v, &tail->qkv_full[stage], 0, 0, b);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc_s = make_idesc(BM, SK, false);
+            const uint32_t idesc_o = make_idesc(BM, DH, true) | (1u << 16);   // P is uint8, V is MN-major
+            bool ok = true;
+            auto issue_scores = [&](int n) -> bool {
+                const int stage = n % STAGES;
+                if (!mbar_wait(&tail->qkv_full[stage], (uint32_t)(n / STAGES) & 1u, abort_flag, g.status, 122)) return false;
+                tc_fence_after();
+                const uint32_t st = smem_u32(smem + (size_t)stage * STAGE_BYTES);
+                const uint64_t qd = make_smem_desc_k64(st), kd = make_smem_desc_k64(st + TILE_BYTES);
+                const uint32_t d_tmem = tmem_base + (uint32_t)((n & 1) * SK);
+#pragma unroll
+                for (int k = 0; k < DH / UMMA_K; ++k)
+                    umma_i8(d_tmem, qd + (uint64_t)(k * (UMMA_K >> 4)), kd + (uint64_t)(k * (UMMA_K >> 4)), idesc_s,
+                            (uint32_t)(k != 0));
+                umma_commit(&tail->s_full[n & 1]);
+                return true;
+            };
+            if (n_local > 0) ok = issue_scores(0);
+            for (int n = 0; ok && n < n_local; ++n) {
+                // the score buffer of item n+1 was last read for item n-1, whose probabilities this thread has
+                // already waited for
+                if (n + 1 < n_local) { ok = issue_scores(n + 1); if (!ok) break; }
+                const int grp = n & 1, stage = n % STAGES;
+                ok = mbar_wait(&tail->p_full[grp], (uint32_t)(n >> 1) & 1u, abort_flag, g.status, 123);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t pd = make_smem_desc(smem_u32(p_smem + (size_t)grp * P_BYTES));
+                const uint64_t vd = make_smem_desc_mn64(smem_u32(smem + (size_t)stage * STAGE_BYTES + 2 * TILE_BYTES));
+                const uint32_t d_tmem = tmem_base + (uint32_t)(2 * SK + grp * DH);
+#pragma unroll
+                for (int k = 0; k < SK / UMMA_K; ++k)
+                    umma_i8(d_tmem, pd + (uint64_t)(k * (UMMA_K >> 4)), vd + (uint64_t)(k * ((UMMA_K * DH) >> 4)), idesc_o,
+                            (uint32_t)(k != 0));
+                umma_commit(&tail->o_full[grp]);
+                umma_commit(&tail->qkv_empty[stage]);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- softmax + output (two groups of four warps) ----------------
+        const int grp = (warp - 2) >> 2;
+        const int quad = warp & 3;                   // TMEM lane quadrant of this warp
+        const int r = quad * 32 + lane;              // query row inside the tile
+        const uint32_t lut_lane = smem_u32(lut) + (uint32_t)lane * 4u;
+        const uint32_t p_row = smem_u32(p_smem + (size_t)grp * P_BYTES) + (uint32_t)r * 128u;
+        const uint32_t sw = (uint32_t)(r & 7);
+        const uint32_t taddr_s = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(grp * SK);
+        const uint32_t taddr_o = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(2 * SK + grp * DH);
+        const int numer = 255 << g.inv_shift;
+        const float numer_f = (float)numer;
+        const float out_mul = __int_as_float((127 - (g.inv_shift + 85)) << 23);  // 2^-(inv_shift + 85)
+        bool ok = true;
+        for (int n = grp; ok && n < n_local; n += GROUPS) {
+            const long long item = first + (long long)n * gridDim.x;
+            const long long b = item / g.m_tiles;
+            const int row = (int)(item % g.m_tiles) * BM + r;
+            const uint32_t par = (uint32_t)(n >> 1) & 1u;
+            ok = mbar_wait(&tail->s_full[grp], par, abort_flag, g.status, 124);
+            if (!ok) break;
+            tc_fence_after();
+
+            // scores: 128 accumulators -> biased bytes, and the row maximum
+            uint32_t pw[SK / 4];
+            int m = 0;
+            {
+                uint32_t acc[SK];
+#pragma unroll
+                for (int c = 0; c < SK / 32; ++c) tmem_ld32_async(taddr_s + (uint32_t)(c * 32), acc + c * 32);
+#pragma unroll
+                for (int c = 0; c < SK / 32; ++c) tmem_ld_wait32(acc + c * 32);
+#pragma unroll
+                for (int i = 0; i < SK / 4; ++i) {
+                    const int u0 = requant_biased<MODE>((int)acc[4 * i + 0], g), u1 = requant_biased<MODE>((int)acc[4 * i + 1], g);
+                    const int u2 = requant_biased<MODE>((int)acc[4 * i + 2], g), u3 = requant_biased<MODE>((int)acc[4 * i + 3], g);
+                    m = __vimax3_s32(m, u0, u1);
+                    m = __vimax3_s32(m, u2, u3);
+                    pw[i] = pack4_i8(u0, u1, u2, u3);
+                }
+            }
+            const uint32_t m4 = (uint32_t)m * 0x01010101u;
+            float e[SK];
+            float fs0 = 0.0f, fs1 = 0.0f;
+#pragma unroll
+            for (int i = 0; i < SK / 4; ++i) {
+                const uint32_t dw = m4 - pw[i];   // per byte: maximum - score, no borrows
+                e[4 * i + 0] = lds32f(prmt(dw, 0, 0x4440) * 128u + lut_lane);
+                e[4 * i + 1] = lds32f(prmt(dw, 0, 0x4441) * 128u + lut_lane);
+                e[4 * i + 2] = lds32f(prmt(dw, 0, 0x4442) * 128u + lut_lane);
+                e[4 * i + 3] = lds32f(prmt(dw, 0, 0x4443) * 128u + lut_lane);
+                fs0 += e[4 * i + 0] + e[4 * i + 2];
+                fs1 += e[4 * i + 1] + e[4 * i + 3];
+            }
+            // exact: at most 128 scores <= 32767 (scaled by 2^-64)
+            const int sum = __float2int_rn((fs0 + fs1) * TWO_P64);
+            const int s = sum > 0 ? sum : 1;
+            int inv;
+            if (g.use_clb && g.mode == 0) {
+                const int k = 31 - __clz(s);
+                inv = g.inv_shift - k >= 0 ? (255 << (g.inv_shift - k)) : (255 >> (k - g.inv_shift));
+            } else {
+                // exact floor(numer / s) wherever it is below 2^15 (larger quotients saturate to 32767 anyway)
+                float rcp;
+                asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rcp) : "f"((float)s));
+                int q = __float2int_rz(numer_f * rcp);
+                const int rem = numer - q * s;
+                q += (rem >= s) - (rem < 0);
+                inv = q;
+            }
+            inv = min(max(inv, 0), 32767);
+            const float invs = (float)inv * out_mul;
+#pragma unroll
+            for (int c = 0; c < SK / 16; ++c) {
+                uint32_t w[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int i = c * 16 + q * 4;
+                    // floor(score * inv / 2^shift) in the low bits of a subnormal (scores are non-negative)
+                    const int o0 = min(__float_as_int(__fmaf_rd(e[i + 0], invs, 0.0f)), 255);
+                    const int o1 = min(__float_as_int(__fmaf_rd(e[i + 1], invs, 0.0f)), 255);
+                    const int o2 = min(__float_as_int(__fmaf_rd(e[i + 2], invs, 0.0f)), 255);
+                    const int o3 = min(__float_as_int(__fmaf_rd(e[i + 3], invs, 0.0f)), 255);
+                    w[q] = pack4_i8(o0, o1, o2, o3);
+                }
+                // K-major, 128-byte swizzle: 16-byte piece c of row r sits at piece c ^ (r & 7)
+                sts128(p_row + (((uint32_t)c ^ sw) << 4), w[0], w[1], w[2], w[3]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> tensor-core reads
+            tc_fence_before();
+            mbar_arrive(&tail->p_full[grp]);
+
+            // output row
+            ok = mbar_wait(&tail->o_full[grp], par, abort_flag, g.status, 125);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t oa[DH];
+            tmem_ld32_async(taddr_o, oa);
+            tmem_ld32_async(taddr_o + 32u, oa + 32);
+            tmem_ld_wait32(oa);
+            tmem_ld_wait32(oa + 32);
+            tc_fence_before();
+            if (row < g.sq) {
+                uint8_t* orow = g.out + b * g.stride_o + (long long)row * g.ldo;
+#pragma unroll
+                for (int c = 0; c < DH / 16; ++c) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int i = c * 16 + q * 4;
+                        w[q] = pack4_i8(requant_out<MODE>((int)oa[i + 0], g), requant_out<MODE>((int)oa[i + 1], g),
+                                        requant_out<MODE>((int)oa[i + 2], g), requant_out<MODE>((int)oa[i + 3], g));
+                    }
+                    *reinterpret_cast<uint4*>(orow + c * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    __syncthreads();
+    if (*abort_flag) {
+        // let TMA copies and MMAs that were already issued land before the CTA gives up its shared memory and TMEM
+        const uint64_t t0 = a4c_globaltimer();
+        while (a4c_globaltimer() - t0 < 2000000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// 3-D uint8 map {64 bytes of head, rows, batch}; box {64, 128, 1}; 64-byte swizzle; rows past the end read as zero
+bool make_head_map(CUtensorMap* map, const void* base, long long rows, long long batch, long long ld, long long stride) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return false;
+    if (batch <= 1) stride = (rows > 0 ? rows : 1) * ld;
+    cuuint64_t dims[3] = {(cuuint64_t)DH, (cuuint64_t)rows, (cuuint64_t)(batch > 0 ? batch : 1)};
+    cuuint64_t strides[2] = {(cuuint64_t)ld, (cuuint64_t)stride};
+    cuuint32_t box[3] = {(cuuint32_t)DH, 128u, 1u};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int MODE>
+cudaError_t launch_mode(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& g, int grid,
+                        cudaStream_t s) {
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(attention_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)SMEM_BYTES);
+    });
+    if (attr_err != cudaSuccess) return attr_err;
+    attention_tc_kernel<MODE><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(mq, mk, mv, g);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+int a4c_attention_tc_supported(const void* q, long long ldq, long long stride_q, const void* k, long long ldk,
+                               long long stride_k, const void* v, long long ldv, long long stride_v, const void* out,
+                               long long ldo, long long stride_o, long long batch, int sq, int sk, int dh, int qk_shift,
+                               int pv_shift, int sm_mode, int B, int S, int Dmax, int inv_shift) {
+    if (sk != SK || dh != DH || sq < 1 || batch < 0) return A4C_ERR_UNSUPPORTED;
+    if ((qk_shift == 0) != (pv_shift == 0)) return A4C_ERR_UNSUPPORTED;   // one rounding template serves both steps
+    if (qk_shift < 0 || qk_shift > 31 || pv_shift < 0 || pv_shift > 31) return A4C_ERR_INVALID_ARG;
+    if (sm_mode != 0 && sm_mode != 1) return A4C_ERR_INVALID_ARG;
+    if (inv_shift < 0 || inv_shift > 22) return A4C_ERR_UNSUPPORTED;
+    if (sm_mode == 0 && B - S * (Dmax < 255 ? Dmax : 255) < 0) return A4C_ERR_UNSUPPORTED;   // negative scores
+    if (ldq % 16 || ldk % 16 || ldv % 16 || ldo % 16) return A4C_ERR_ALIGNMENT;
+    if (batch > 1 && (stride_q % 16 || stride_k % 16 || stride_v % 16 || stride_o % 16)) return A4C_ERR_ALIGNMENT;
+    if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15u) return A4C_ERR_ALIGNMENT;
+    if (ldq < DH || ldk < DH || ldv < DH || ldo < DH) return A4C_ERR_INVALID_ARG;
+    const long long items = batch * ((sq + BM - 1) / BM);
+    if (batch > 2147483647LL || items > 2147483647LL) return A4C_ERR_TOO_LARGE;
+    return A4C_OK;
+}
+
+int a4c_launch_attention_tc(const void* q, long long ldq, long long stride_q, const void* k, long long ldk,
+                            long long stride_k, const void* v, long long ldv, long long stride_v, void* out,
+                            long long ldo, long long stride_o, long long batch, int sq, int sk, int dh, int qk_shift,
+                            int pv_shift, int rounding, int sm_mode, int B, int S, int Dmax, int inv_shift, int use_clb,
+                            int exp_kq, int* status_word, cudaStream_t stream) {
+    const int sup = a4c_attention_tc_supported(q, ldq, stride_q, k, ldk, stride_k, v, ldv, stride_v, out, ldo, stride_o,
+                                               batch, sq, sk, dh, qk_shift, pv_shift, sm_mode, B, S, Dmax, inv_shift);
+    if (sup != A4C_OK) return sup;
+    if (rounding < 0 || rounding >= A4C_RND_COUNT) return A4C_ERR_INVALID_ARG;
+    if (batch == 0) return A4C_OK;
+    CUtensorMap mq, mk, mv;
+    if (!make_head_map(&mq, q, sq, batch, ldq, stride_q) || !make_head_map(&mk, k, sk, batch, ldk, stride_k) ||
+        !make_head_map(&mv, v, sk, batch, ldv, stride_v))
+        return A4C_ERR_CUDA;
+    AttnArgs g;
+    g.out = (uint8_t*)out; g.ldo = ldo; g.stride_o = stride_o; g.batch = batch; g.sq = sq;
+    g.m_tiles = (sq + BM - 1) / BM;
+    g.shift1 = qk_shift; g.shift2 = pv_shift;
+    const RoundParams r1 = make_round_params(qk_shift, rounding), r2 = make_round_params(pv_shift, rounding);
+    g.mask1 = r1.mask; g.c01 = r1.c0; g.mask2 = r2.mask; g.c02 = r2.c0;
+    const bool pre_clamp = rounding == A4C_RND_POSITIVE_INF && qk_shift >= 1 && qk_shift <= 22 && pv_shift >= 1 &&
+                           pv_shift <= 22;
+    g.xhi1 = g.addb1 = g.xlob1 = g.xhi2 = g.half2 = g.xlo2 = 0;
+    if (pre_clamp) {
+        g.xhi1 = 127 * (1 << qk_shift);
+        g.addb1 = (1 << (qk_shift - 1)) + 128 * (1 << qk_shift);
+        g.xlob1 = -128 * (1 << qk_shift) + g.addb1;
+        g.xhi2 = 127 * (1 << pv_shift);
+        g.half2 = 1 << (pv_shift - 1);
+        g.xlo2 = -128 * (1 << pv_shift) + g.half2;
+    }
+    g.mode = sm_mode; g.B = B; g.S = S; g.Dmax = Dmax; g.inv_shift = inv_shift; g.use_clb = use_clb; g.exp_kq = exp_kq;
+    g.status = status_word;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long items = batch * g.m_tiles;
+    const int grid = (int)(items < sms ? items : sms);
+    cudaError_t err;
+    if (qk_shift == 0) err = launch_mode<-1>(mq, mk, mv, g, grid, stream);
+    else if (pre_clamp) err = launch_mode<MODE_HALF_UP_CLAMP>(mq, mk, mv, g, grid, stream);
+    else switch (rounding) {
+        case A4C_RND_FLOOR: err = launch_mode<A4C_RND_FLOOR>(mq, mk, mv, g, grid, stream); break;
+        case A4C_RND_CEIL: err = launch_mode<A4C_RND_CEIL>(mq, mk, mv, g, grid, stream); break;
+        case A4C_RND_POSITIVE_INF: err = launch_mode<A4C_RND_POSITIVE_INF>(mq, mk, mv, g, grid, stream); break;
+        case A4C_RND_NEGATIVE_INF: err = launch_mode<A4C_RND_NEGATIVE_INF>(mq, mk, mv, g, grid, stream); break;
+        case A4C_RND_SYMMETRIC_INF: err = launch_mode<A4C_RND_SYMMETRIC_INF>(mq, mk, mv, g, grid, stream); break;
+        case A4C_RND_SYMMETRIC_ZERO: err = launch_mode<A4C_RND_SYMMETRIC_ZERO>(mq, mk, mv, g, grid, stream); break;
+        case A4C_RND_CONV_EVEN: err = launch_mode<A4C_RND_CONV_EVEN>(mq, mk, mv, g, grid, stream); break;
+        default: err = launch_mode<A4C_RND_CONV_ODD>(mq, mk, mv, g, grid, stream); break;
+    }
+    return err == cudaSuccess ? A4C_OK : A4C_ERR_CUDA;
+}

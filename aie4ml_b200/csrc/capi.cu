@@ -139,6 +139,30 @@ int a4c_bmm_i8(const void* A, int64_t lda, int64_t stride_a, const int8_t* B, in
     return finish();
 }
 
+int a4c_attention_i8_supported(const int8_t* q, int64_t ldq, int64_t stride_q, const int8_t* k, int64_t ldk,
+                               int64_t stride_k, const int8_t* v, int64_t ldv, int64_t stride_v, const int8_t* out,
+                               int64_t ldo, int64_t stride_o, int64_t batch, int sq, int sk, int dh, int qk_shift,
+                               int pv_shift, int sm_mode, int B, int S, int Dmax, int inv_shift) {
+    if (q == nullptr || k == nullptr || v == nullptr || out == nullptr) return A4C_ERR_INVALID_ARG;
+    return a4c_attention_tc_supported(q, ldq, stride_q, k, ldk, stride_k, v, ldv, stride_v, out, ldo, stride_o, batch,
+                                      sq, sk, dh, qk_shift, pv_shift, sm_mode, B, S, Dmax, inv_shift);
+}
+
+int a4c_attention_i8(const int8_t* q, int64_t ldq, int64_t stride_q, const int8_t* k, int64_t ldk, int64_t stride_k,
+                     const int8_t* v, int64_t ldv, int64_t stride_v, int8_t* out, int64_t ldo, int64_t stride_o,
+                     int64_t batch, int sq, int sk, int dh, int qk_shift, int pv_shift, int rounding, int sm_mode, int B,
+                     int S, int Dmax, int inv_shift, int use_clb, int exp_kq, void* stream) {
+    if (q == nullptr || k == nullptr || v == nullptr || out == nullptr) return A4C_ERR_INVALID_ARG;
+    if (!valid_round(rounding)) return A4C_ERR_INVALID_ARG;
+    int* word = status_word();
+    if (word == nullptr) return A4C_ERR_CUDA;
+    const int rc = a4c_launch_attention_tc(q, ldq, stride_q, k, ldk, stride_k, v, ldv, stride_v, out, ldo, stride_o,
+                                           batch, sq, sk, dh, qk_shift, pv_shift, rounding, sm_mode, B, S, Dmax,
+                                           inv_shift, use_clb, exp_kq, word, (cudaStream_t)stream);
+    if (rc != A4C_OK) { if (rc == A4C_ERR_CUDA) note(cudaGetLastError()); return rc; }
+    return finish();
+}
+
 int a4c_set_option(int option, int value) {
     if (option == A4C_OPT_ROWOP_PATH && (value == 0 || value == 1)) {
         g_rowop_path = value;

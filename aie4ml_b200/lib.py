@@ -47,6 +47,12 @@ SIGNATURES = {
                                   c_void_p, c_int, c_void_p, c_int64, c_int, c_int64, ctypes.POINTER(c_int), c_void_p]),
     'a4c_softmax_i8': (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int, c_int, c_int,
                                c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    'a4c_attention_i8_supported': (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64,
+                                           c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int,
+                                           c_int, c_int, c_int, c_int, c_int, c_int]),
+    'a4c_attention_i8': (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64,
+                                 c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                 c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'a4c_add_sat': (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_int,
                             c_int, c_void_p]),
 }

@@ -109,7 +109,7 @@ class Plan:
     """Buffers, views, device constants and the launch list of one lowered model."""
 
     def __init__(self, ctx: BackendContext, device: Optional[str] = None, fuse_rowop_add: bool = True,
-                 dense_algo: int = _lib.ALGO_AUTO, share_params: Optional['Plan'] = None):
+                 dense_algo: int = _lib.ALGO_AUTO, share_params: Optional['Plan'] = None, fuse_attention: bool = True):
         torch = _torch()
         self.ctx = ctx
         self.lib = _lib.load()
@@ -119,6 +119,7 @@ class Plan:
         self.device = torch.device(device or f'cuda:{torch.cuda.current_device()}')
         self.dense_algo = int(dense_algo)
         self.fuse_rowop_add = bool(fuse_rowop_add)
+        self.fuse_attention = bool(fuse_attention)
         graph = ctx.ir.logical
         self.graph = graph
 
@@ -170,14 +171,16 @@ class Plan:
                                               'express it as dense.')
             self.ops.append(op)
         self.fused: List[str] = []
+        self.views: Dict[str, View] = {}
+        self.buffers: Dict[str, Any] = {}
+        if fuse_attention:
+            self._fuse_attention()
         if fuse_rowop_add:
             self._fuse_rowop_add()
 
-        self.views: Dict[str, View] = {}
-        self.buffers: Dict[str, Any] = {}
         live = set(graph.input_tensor_names) | set(graph.output_tensor_names)
         for op in self.ops:
-            for key in ('lhs', 'rhs', 'out', 'addend'):
+            for key in ('lhs', 'rhs', 'out', 'addend', 'q', 'k', 'v'):
                 if op.get(key):
                     live.add(op[key])
         for name in sorted(live):
@@ -278,6 +281,67 @@ class Plan:
                     op['out'] = op.pop('fused_out')
             self.ops = [op for i, op in enumerate(self.ops) if i not in drop]
 
+    def _attention_args(self, op: Dict[str, Any]) -> tuple:
+        """Positional arguments of a4c_attention_i8 up to (not including) `rounding`, from the four views."""
+        name = op['name']
+        q, k, v, o = (self._view(op[key]) for key in ('q', 'k', 'v', 'out'))
+        q_off, bq, sq, dq, ldq, stq = collapse_batched(q, f'{name}: q')
+        k_off, bk, sk, dk, ldk, stk = collapse_batched(k, f'{name}: k')
+        v_off, bv, sv, dv, ldv, stv = collapse_batched(v, f'{name}: v')
+        o_off, bo, so, do, ldo, sto = collapse_batched(o, f'{name}: output')
+        if not (bq == bk == bv == bo and sk == sv and sq == so and dq == dk == dv == do):
+            raise ValueError(f'{name}: q/k/v/output shapes do not form an attention head.')
+        return (self.ptr(q, q_off), ldq, stq, self.ptr(k, k_off), ldk, stk, self.ptr(v, v_off), ldv, stv,
+                self.ptr(o, o_off), ldo, sto, bq, sq, sk, dq, op['qk_shift'], op['pv_shift'])
+
+    def _fuse_attention(self) -> None:
+        """matmul(q, k^T) -> softmax (uint8) -> matmul(p, v) becomes one launch per head when the library has a
+        fused kernel for the shapes (a4c_attention_i8_supported): scores and probabilities then have no
+        buffer at all.  Both intermediates must feed nothing else and be neither graph outputs nor views."""
+        graph = self.graph
+        produced_at = {op['out']: i for i, op in enumerate(self.ops)}
+        aliased = set(self.alias) | {p for p, _, _ in self.alias.values()}
+
+        def private(t: str) -> bool:
+            return len(graph.tensors[t].consumers) == 1 and t not in graph.output_tensor_names and t not in aliased
+
+        drop, replace = set(), {}
+        for i, av in enumerate(self.ops):
+            if av['kind'] != 'matmul' or av['transpose_lhs'] or av['transpose_rhs'] or av['out_dtype'] != 'int8':
+                continue
+            j = produced_at.get(av['lhs'])
+            if j is None or self.ops[j]['kind'] != 'softmax':
+                continue
+            sm = self.ops[j]
+            if sm.get('addend') or sm['out_dtype'] != 'uint8' or not private(sm['out']) or not private(sm['lhs']):
+                continue
+            h = produced_at.get(sm['lhs'])
+            if h is None or self.ops[h]['kind'] != 'matmul':
+                continue
+            qk = self.ops[h]
+            if (qk['transpose_lhs'] or not qk['transpose_rhs'] or qk['out_dtype'] != 'int8' or qk['lhs_dtype'] != 'int8'
+                    or qk['rounding'] != av['rounding']):
+                continue
+            op = {'kind': 'attention', 'name': f"{qk['name']}+{sm['name']}+{av['name']}", 'q': qk['lhs'], 'k': qk['rhs'],
+                  'v': av['rhs'], 'out': av['out'], 'qk_shift': qk['shift'], 'pv_shift': av['shift'],
+                  'rounding': av['rounding'], 'sm_mode': 0 if sm['approximation'] == 'hccs' else 1, 'B': sm['B'],
+                  'S': sm['S'], 'Dmax': sm['Dmax'], 'inv_shift': sm['inv_shift'], 'use_clb': int(sm['use_clb']),
+                  'exp_kq': sm['exp_kq']}
+            if any(self.fmt[op[key]] != 'int8' for key in ('q', 'k', 'v', 'out')):
+                continue
+            try:
+                args = self._attention_args(op)
+            except (NotImplementedError, ValueError):
+                continue
+            if self.lib.a4c_attention_i8_supported(*args, op['sm_mode'], op['B'], op['S'], op['Dmax'],
+                                                   op['inv_shift']) != 0:
+                continue
+            replace[i] = op
+            drop.update((h, j))
+            self.fused.append(op['name'])
+        if replace:
+            self.ops = [replace.get(i, op) for i, op in enumerate(self.ops) if i not in drop]
+
     # ---- launch compilation --------------------------------------------------------------------
     def _compile(self, op: Dict[str, Any]) -> Tuple[Callable, tuple]:
         kind, name = op['kind'], op['name']
@@ -315,6 +379,10 @@ class Plan:
                     int(op['transpose_lhs']), int(op['transpose_rhs']), op['shift'], ROUNDING_CODE[op['rounding']],
                     DTYPE_CODE[op['out_dtype']], int(op['lhs_dtype'] == 'uint8'))
             return L.a4c_bmm_i8, args
+        if kind == 'attention':
+            args = self._attention_args(op) + (ROUNDING_CODE[op['rounding']], op['sm_mode'], op['B'], op['S'],
+                                               op['Dmax'], op['inv_shift'], op['use_clb'], op['exp_kq'])
+            return L.a4c_attention_i8, args
         if kind in ('layer_norm', 'softmax', 'add'):
             x, y = self._view(op['lhs']), self._view(op['out'])
             x_off, rows, cols, ldx = collapse_2d(x, f'{name}: input')

@@ -38,7 +38,8 @@ class HostPipeline:
         self.plans: List[Plan] = [first]
         for _ in range(depth - 1):
             self.plans.append(Plan(ctx, device=str(first.device), fuse_rowop_add=first.fuse_rowop_add,
-                                   dense_algo=first.dense_algo, share_params=first))
+                                   fuse_attention=first.fuse_attention, dense_algo=first.dense_algo,
+                                   share_params=first))
         self.device = first.device
         graph = first.graph
         self.in_names = list(graph.input_tensor_names)

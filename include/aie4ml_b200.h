@@ -139,6 +139,33 @@ A4C_API int a4c_softmax_i8(const int8_t* x, int64_t ldx, const void* addend, int
                    int exp_kq, int out_dtype, void* stream);
 
 /*
+ * One attention head, fused:  out_b = srs( softmax_u8( srs(Q_b . K_b^T, qk_shift) ) . V_b, pv_shift )  for every
+ * batch entry b.  The reference has no single kernel for this: it is the chain of its three kernels
+ *   matmul_single::run with TRANSPOSE_B (src/aie4ml/templates/nnet_utils/matmul/matmul.cpp:32-118)
+ *   -> softmax (softmax.cpp:20-88 HCCS / :252-384 exp, uint8 output)
+ *   -> matmul_single::run (uint8 x int8),
+ * with the int8 scores and uint8 probabilities kept on chip, and it produces exactly the bytes the three
+ * calls a4c_bmm_i8 / a4c_softmax_i8 / a4c_bmm_i8 produce.
+ *   q [batch][sq][dh], k [batch][sk][dh], v [batch][sk][dh], out [batch][sq][dh], all int8, row pitches ld*
+ *   and batch strides stride_* in bytes (a head is a column slice of a wider tensor: pitch > dh).
+ *   qk_shift / pv_shift / rounding: the SRS parameters of the two MatMuls (one rounding token for both).
+ *   sm_mode, B, S, Dmax, inv_shift, use_clb, exp_kq: as a4c_softmax_i8.
+ * Supported: sk == 128, dh == 64, 16-byte aligned pointers / pitches / strides, inv_shift <= 22, non-negative
+ * HCCS scores, shifts both zero or both non-zero.  a4c_attention_i8_supported answers A4C_OK or the error
+ * code a4c_attention_i8 would return for the same arguments, without launching anything; callers fall back to
+ * the three separate calls.
+ */
+A4C_API int a4c_attention_i8_supported(const int8_t* q, int64_t ldq, int64_t stride_q, const int8_t* k, int64_t ldk,
+                               int64_t stride_k, const int8_t* v, int64_t ldv, int64_t stride_v, const int8_t* out,
+                               int64_t ldo, int64_t stride_o, int64_t batch, int sq, int sk, int dh, int qk_shift,
+                               int pv_shift, int sm_mode, int B, int S, int Dmax, int inv_shift);
+A4C_API int a4c_attention_i8(const int8_t* q, int64_t ldq, int64_t stride_q, const int8_t* k, int64_t ldk,
+                     int64_t stride_k, const int8_t* v, int64_t ldv, int64_t stride_v, int8_t* out, int64_t ldo,
+                     int64_t stride_o, int64_t batch, int sq, int sk, int dh, int qk_shift, int pv_shift,
+                     int rounding, int sm_mode, int B, int S, int Dmax, int inv_shift, int use_clb, int exp_kq,
+                     void* stream);
+
+/*
  * Elementwise out = saturate( round_shift( a + b, shift ) ) over [rows, cols] tensors of one dtype.
  * Replaces elementwise_add_kernel::run
  * (src/aie4ml/templates/nnet_utils/elementwise_add/elementwise_add.cpp:12-37; SHIFT, ROUNDING from

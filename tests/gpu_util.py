@@ -138,3 +138,25 @@ def mlp_chain(x, layers, *, tok, out_dtype='int8', fn_name='a4c_mlp_i8'):
     a4c.check(rc, fn_name)
     a4c.device_status(stream())
     return y_d.cpu().numpy()[:, :N]
+
+
+def attention(qkv, heads_at, *, qk_shift, pv_shift, tok, mode, B=0, S=0, Dmax=0, inv_shift=15, use_clb=False, exp_kq=0,
+              out_width=None):
+    """One fused attention head over a packed [batch, seq, width] int8 tensor: q, k, v are the 64-column
+    slices starting at heads_at = (q0, k0, v0); the result lands in columns [o0, o0 + 64) of a
+    [batch, seq_q, out_width] tensor pre-filled with 0x5A (o0 = q0).  Returns that whole tensor."""
+    L = a4c.load()
+    batch, seq, width = qkv.shape
+    q0, k0, v0 = heads_at
+    d = dev(qkv)
+    ow = out_width or width
+    out = torch.full((batch, seq, ow), 0x5A, dtype=torch.int8, device='cuda')
+    base = d.data_ptr()
+    args = (base + q0, width, seq * width, base + k0, width, seq * width, base + v0, width, seq * width,
+            out.data_ptr() + q0, ow, seq * ow, batch, seq, seq, 64, qk_shift, pv_shift)
+    sm = (0 if mode == 'hccs' else 1, B, S, Dmax, inv_shift)
+    a4c.check(L.a4c_attention_i8_supported(*args, *sm), 'a4c_attention_i8_supported')
+    rc = L.a4c_attention_i8(*args, ROUNDING_CODE[tok], *sm, int(use_clb), exp_kq, stream())
+    a4c.check(rc, 'a4c_attention_i8')
+    a4c.device_status(stream())
+    return out.cpu().numpy()

@@ -314,3 +314,62 @@ def test_empty_inputs_are_no_ops():
     assert L.a4c_add_sat(p, 64, p, 64, p, 64, 0, 64, 0, 6, 0, G.stream()) == 0
     assert L.a4c_layernorm_i8(p, 64, p, p, None, 0, p, 64, 0, 64, 1, 4, 6, 0, G.stream()) == 0
     assert L.a4c_softmax_i8(p, 64, None, 0, p, 64, 0, 64, 1, 0, 0, 0, 15, 0, 23, 1, G.stream()) == 0
+
+
+def _attention_oracle(q, k, v, *, qk_shift, pv_shift, tok, mode, **sm):
+    s = oracle.matmul(q, k, shift=qk_shift, tok=tok, transpose_b=True, out_dtype='int8')
+    if mode == 'exp':
+        p = oracle.softmax_exp(s, exp_kq=sm['exp_kq'], inv_shift=sm.get('inv_shift', 15), out_dtype='uint8')
+    else:
+        p = oracle.softmax_hccs(s, B=sm['B'], S=sm['S'], Dmax=sm['Dmax'], inv_shift=sm.get('inv_shift', 15),
+                                use_clb=sm.get('use_clb', False), out_dtype='uint8')
+    return oracle.matmul(p, v, shift=pv_shift, tok=tok, out_dtype='int8')
+
+
+@pytest.mark.parametrize('tok', ['positive_inf', 'conv_even', 'floor', 'symmetric_inf'])
+@pytest.mark.parametrize('mode', ['exp', 'hccs'])
+def test_fused_attention_head_equals_matmul_softmax_matmul(tok, mode):
+    """The fused kernel against the oracle's three-step chain, on head slices of a packed tensor (pitch 256,
+    head offsets 64 / 128 / 192), more items than SMs so every ring stage and both softmax groups wrap."""
+    import gpu_util as G
+
+    rng = np.random.default_rng(11)
+    batch, seq, width = 333, 128, 256
+    qkv = np.clip(np.rint(rng.normal(0, 40, (batch, seq, width))), -128, 127).astype(np.int8)
+    qkv[0, :, :64] = 127          # saturating scores
+    qkv[1, :, 64:128] = -128
+    qkv[2] = 0                    # all scores equal
+    sm = dict(exp_kq=23) if mode == 'exp' else dict(B=200, S=3, Dmax=66)
+    q0, k0, v0 = 64, 128, 192
+    got = G.attention(qkv, (q0, k0, v0), qk_shift=9, pv_shift=8, tok=tok, mode=mode, **sm)
+    want = _attention_oracle(qkv[..., q0:q0 + 64], qkv[..., k0:k0 + 64], qkv[..., v0:v0 + 64], qk_shift=9, pv_shift=8,
+                             tok=tok, mode=mode, **sm)
+    np.testing.assert_array_equal(got[..., q0:q0 + 64], want)
+    untouched = np.delete(got, np.s_[q0:q0 + 64], axis=2)
+    assert (untouched == 0x5A).all()
+
+
+def test_fused_attention_other_softmax_parameters_and_rejections():
+    import gpu_util as G
+    from aie4ml_b200 import lib as a4c
+
+    rng = np.random.default_rng(12)
+    qkv = rng.integers(-128, 128, (5, 128, 192)).astype(np.int8)
+    for sm in (dict(mode='hccs', B=255, S=1, Dmax=200, inv_shift=14, use_clb=True),
+               dict(mode='exp', exp_kq=128, inv_shift=12), dict(mode='exp', exp_kq=1, inv_shift=22)):
+        got = G.attention(qkv, (0, 64, 128), qk_shift=11, pv_shift=7, tok='positive_inf', **sm)
+        mode = sm.pop('mode')
+        want = _attention_oracle(qkv[..., :64], qkv[..., 64:128], qkv[..., 128:], qk_shift=11, pv_shift=7,
+                                 tok='positive_inf', mode=mode, **sm)
+        np.testing.assert_array_equal(got[..., :64], want)
+    L = a4c.load()
+    p = G.dev(qkv).data_ptr()
+    ok = (p, 192, 128 * 192, p + 64, 192, 128 * 192, p + 128, 192, 128 * 192, p, 192, 128 * 192, 5, 128, 128, 64, 9, 8,
+          1, 0, 0, 0, 15)
+    assert L.a4c_attention_i8_supported(*ok) == 0
+    bad_keys = list(ok); bad_keys[14] = 64
+    assert L.a4c_attention_i8_supported(*bad_keys) == a4c.A4C_ERR_UNSUPPORTED
+    misaligned = list(ok); misaligned[0] = p + 8
+    assert L.a4c_attention_i8_supported(*misaligned) == a4c.A4C_ERR_ALIGNMENT
+    one_zero_shift = list(ok); one_zero_shift[16] = 0
+    assert L.a4c_attention_i8_supported(*one_zero_shift) == a4c.A4C_ERR_UNSUPPORTED

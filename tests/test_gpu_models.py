@@ -37,7 +37,12 @@ def test_cfg2_dense(shape):
 def test_cfg3_encoder_block(softmax, rounding):
     model = _check(*W.encoder_cfg3(3, softmax=softmax, rounding=rounding))
     kinds = [op['kind'] for op in model.plan.ops]
-    assert kinds.count('matmul') == 8 and kinds.count('softmax') == 4 and kinds.count('layer_norm') == 2
+    # every head's QK^T -> softmax -> AV chain runs as one fused launch; scores and probabilities have no buffer
+    assert kinds.count('attention') == 4 and kinds.count('matmul') == 0 and kinds.count('softmax') == 0
+    assert kinds.count('layer_norm') == 2 and not any(n.startswith(('qk', 'sm')) for n in model.plan.buffers)
+    unfused = _check(*W.encoder_cfg3(3, softmax=softmax, rounding=rounding), FusionPolicy={'attention': False})
+    kinds = [op['kind'] for op in unfused.plan.ops]
+    assert kinds.count('matmul') == 8 and kinds.count('softmax') == 4 and kinds.count('attention') == 0
 
 
 @pytest.mark.parametrize('op', ['layer_norm', 'softmax_exp', 'softmax_hccs'])
