@@ -19,8 +19,9 @@ int a4c_launch_dense_tc(const void* A, long long lda, const void* Wt, long long 
 int a4c_dense_tc_supported(const void* A, long long lda, const void* Wt, long long ldw, const void* Y,
                            long long ldy, long long M, int K, int N, int out_dtype);
 
+// pre_add != 0: the addend is added (saturating) to the input before the statistics; otherwise to the result.
 int a4c_launch_layernorm(const int8_t* x, long long ldx, const int16_t* gamma, const int16_t* beta,
-                         const int8_t* addend, long long ldadd, int8_t* out, long long ldo, long long rows,
+                         const int8_t* addend, long long ldadd, int pre_add, int8_t* out, long long ldo, long long rows,
                          int cols, int eps_q0, int out_shift, int rounding, cudaStream_t stream);
 
 int a4c_launch_softmax(const int8_t* x, long long ldx, const void* addend, long long ldadd, void* out,
@@ -33,9 +34,9 @@ int a4c_launch_add(const void* a, long long lda, const void* b, long long ldb, v
 // Bandwidth-oriented variants of the two row ops (rowops_fast.cu).  They return A4C_ERR_UNSUPPORTED when a
 // request lies outside what they prove exact; the caller then uses the generic kernels above.
 int a4c_launch_layernorm_fast(const int8_t* x, long long ldx, const int16_t* gamma, const int16_t* beta,
-                              const int8_t* addend, long long ldadd, int8_t* out, long long ldo, long long rows,
-                              int cols, int eps_q0, int out_shift, int rounding, int gamma_absmax, int* status,
-                              cudaStream_t stream);
+                              const int8_t* addend, long long ldadd, int pre_add, int8_t* out, long long ldo,
+                              long long rows, int cols, int eps_q0, int out_shift, int rounding, int gamma_absmax,
+                              int* status, cudaStream_t stream);
 int a4c_launch_softmax_fast(const int8_t* x, long long ldx, const void* addend, long long ldadd, void* out,
                             long long ldo, long long rows, int cols, int mode, int B, int S, int Dmax, int inv_shift,
                             int use_clb, int exp_kq, int out_dtype, int* status, cudaStream_t stream);

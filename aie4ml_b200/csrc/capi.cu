@@ -183,24 +183,40 @@ int a4c_set_option(int option, int value) {
     return A4C_ERR_INVALID_ARG;
 }
 
-int a4c_layernorm_i8(const int8_t* x, int64_t ldx, const int16_t* gamma, const int16_t* beta,
-                     const int8_t* addend, int64_t ldadd, int8_t* out, int64_t ldo, int64_t rows, int cols,
-                     int eps_q0, int out_shift, int rounding, int gamma_absmax, void* stream) {
+static int layernorm_any(const int8_t* x, int64_t ldx, const int16_t* gamma, const int16_t* beta,
+                         const int8_t* addend, int64_t ldadd, int pre_add, int8_t* out, int64_t ldo, int64_t rows,
+                         int cols, int eps_q0, int out_shift, int rounding, int gamma_absmax, void* stream) {
     if (x == nullptr || gamma == nullptr || beta == nullptr || out == nullptr) return A4C_ERR_INVALID_ARG;
     if (ldx < cols || ldo < cols || (addend && ldadd < cols)) return A4C_ERR_INVALID_ARG;
     if (g_rowop_path == 0 && rows > 0 && cols >= 16 && (cols & (cols - 1)) == 0 && out_shift >= 0 && out_shift <= 15 &&
         eps_q0 >= 1 && valid_round(rounding) && cols % 16 == 0 && ldx % 16 == 0 && ldo % 16 == 0 &&
         (((uintptr_t)x | (uintptr_t)out | (uintptr_t)gamma | (uintptr_t)beta) & 15u) == 0 &&
         (!addend || (ldadd % 16 == 0 && ((uintptr_t)addend & 15u) == 0))) {
-        const int frc = a4c_launch_layernorm_fast(x, ldx, gamma, beta, addend, ldadd, out, ldo, rows, cols, eps_q0,
-                                                  out_shift, rounding, gamma_absmax, status_word(), (cudaStream_t)stream);
+        const int frc = a4c_launch_layernorm_fast(x, ldx, gamma, beta, addend, ldadd, pre_add, out, ldo, rows, cols,
+                                                  eps_q0, out_shift, rounding, gamma_absmax, status_word(),
+                                                  (cudaStream_t)stream);
         if (frc == A4C_OK) return finish();
         if (frc != A4C_ERR_UNSUPPORTED) return frc;
     }
-    const int rc = a4c_launch_layernorm(x, ldx, gamma, beta, addend, ldadd, out, ldo, rows, cols, eps_q0, out_shift,
-                                        rounding, (cudaStream_t)stream);
+    const int rc = a4c_launch_layernorm(x, ldx, gamma, beta, addend, ldadd, pre_add, out, ldo, rows, cols, eps_q0,
+                                        out_shift, rounding, (cudaStream_t)stream);
     if (rc != A4C_OK) return rc;
     return finish();
+}
+
+int a4c_layernorm_i8(const int8_t* x, int64_t ldx, const int16_t* gamma, const int16_t* beta,
+                     const int8_t* addend, int64_t ldadd, int8_t* out, int64_t ldo, int64_t rows, int cols,
+                     int eps_q0, int out_shift, int rounding, int gamma_absmax, void* stream) {
+    return layernorm_any(x, ldx, gamma, beta, addend, ldadd, 0, out, ldo, rows, cols, eps_q0, out_shift, rounding,
+                         gamma_absmax, stream);
+}
+
+int a4c_add_layernorm_i8(const int8_t* x, int64_t ldx, const int8_t* residual, int64_t ldr, const int16_t* gamma,
+                         const int16_t* beta, int8_t* out, int64_t ldo, int64_t rows, int cols, int eps_q0,
+                         int out_shift, int rounding, int gamma_absmax, void* stream) {
+    if (residual == nullptr) return A4C_ERR_INVALID_ARG;
+    return layernorm_any(x, ldx, gamma, beta, residual, ldr, 1, out, ldo, rows, cols, eps_q0, out_shift, rounding,
+                         gamma_absmax, stream);
 }
 
 int a4c_softmax_i8(const int8_t* x, int64_t ldx, const void* addend, int64_t ldadd, void* out, int64_t ldo,

@@ -38,10 +38,17 @@ constexpr int TMEM_COLS = ACC_STAGES * BN;       // 512
 constexpr int EPI_WARPS = 8;           // two warps per TMEM lane quadrant, each takes half of the tile's columns
 constexpr int EPI_THREADS = EPI_WARPS * 32;
 constexpr int NUM_THREADS = 64 + EPI_THREADS;
-// positive_inf with 1 <= shift <= 22: saturate BEFORE the shift (rounding is monotonic, and lo*2^s / hi*2^s
-// round to lo / hi exactly), which makes the rounding add overflow-free and folds bias add, both clamps
-// and the rounding add into two add-min/max instructions plus the shift.
+// positive_inf with 2 <= shift <= 22: saturate BEFORE the shift (rounding is monotonic, and lo*2^s / hi*2^s
+// round to lo / hi exactly), which makes the rounding add overflow-free.  The integer ALU of an SM
+// sub-partition retires half a warp per clock and is what bounds this epilogue, so the sequence is split
+// between it and the multiply-add pipe:
+//   x = acc * 1 + bias                         multiply-add pipe (the 1 is a kernel argument, so it stays a multiply)
+//   MODE_HALF_UP_RELU  (lo == 0):  t = max(min(x, hi*2^s), 0)                  one ALU instruction
+//                                  y = hi32(t * 2^(32-s) + 2^31)               multiply-add pipe: (t + 2^(s-1)) >> s
+//   MODE_HALF_UP_CLAMP:            t = min(x, hi*2^s); u = max(t + 2^(s-1), lo*2^s + 2^(s-1))     two ALU instructions
+//                                  y = hi32(u * 2^(32-s))                      multiply-add pipe: u >> s
 constexpr int MODE_HALF_UP_CLAMP = 100;
+constexpr int MODE_HALF_UP_RELU = 101;
 
 constexpr int BIAS_CACHE = 2048;   // whole bias vector resident in shared memory when N fits
 
@@ -54,11 +61,11 @@ struct SmemTail {
     uint32_t tmem_base;
     volatile int abort_flag;
 };
-// Output staging: each epilogue warp owns 32 rows x 64 bytes, so that global stores are coalesced
-// (four lanes per row write 64 contiguous bytes) instead of one 16-byte piece per row per lane.
+// Output staging: each epilogue warp owns a 32-row x 64-byte patch (64-byte swizzle) that a TMA store
+// moves to global memory, so the warps that convert accumulators never wait on the store path.
 constexpr int EPI_STAGE_BYTES = 32 * 64;
 constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES +
-                              ((sizeof(SmemTail) + 127) / 128) * 128 + (size_t)EPI_WARPS * EPI_STAGE_BYTES;
+                              (size_t)EPI_WARPS * EPI_STAGE_BYTES + sizeof(SmemTail);
 
 using namespace tc;
 
@@ -71,16 +78,27 @@ struct TcArgs {
     int num_m_tiles, num_n_tiles;
     int shift, lo, hi;
     uint32_t mask, c0;   // rounding constants (see round_shift_i32_t)
-    int half, xhi, xlo;  // MODE_HALF_UP_CLAMP: 2^(s-1), hi * 2^s, lo * 2^s + 2^(s-1)
+    int half, xhi, xlo;  // MODE_HALF_UP_*: 2^(s-1), hi * 2^s, lo * 2^s + 2^(s-1)
+    int one, mulm;       // MODE_HALF_UP_*: 1 and 2^(32-s)
+    long long half_mul;  // MODE_HALF_UP_RELU: 2^(s-1) * 2^(32-s) = 2^31
     uint32_t idesc;
     int* status;
 };
 
 template <int MODE>
 __device__ __forceinline__ int requant(int acc, int bias, const TcArgs& g) {
-    if (MODE == MODE_HALF_UP_CLAMP) {
-        const int t = __viaddmin_s32(acc, bias, g.xhi);          // min(wrap32(acc + bias), hi * 2^s)
-        return __viaddmax_s32(t, g.half, g.xlo) >> g.shift;      // max(t + 2^(s-1), lo * 2^s + 2^(s-1)) >> s
+    if (MODE == MODE_HALF_UP_CLAMP || MODE == MODE_HALF_UP_RELU) {
+        int x, y;
+        asm("mad.lo.s32 %0, %1, %2, %3;" : "=r"(x) : "r"(acc), "r"(g.one), "r"(bias));   // wrap32(acc + bias)
+        if (MODE == MODE_HALF_UP_RELU) {
+            const int t = __vimin_s32_relu(x, g.xhi);
+            asm("{\n\t.reg .s64 w;\n\tmad.wide.s32 w, %1, %2, %3;\n\tmov.b64 {_, %0}, w;\n\t}"
+                : "=r"(y) : "r"(t), "r"(g.mulm), "l"(g.half_mul));
+        } else {
+            const int u = __viaddmax_s32(min(x, g.xhi), g.half, g.xlo);
+            asm("mul.hi.s32 %0, %1, %2;" : "=r"(y) : "r"(u), "r"(g.mulm));
+        }
+        return y;
     }
     int v = acc + bias;
     if (MODE == A4C_RND_FLOOR) v = v >> g.shift;
@@ -88,12 +106,21 @@ __device__ __forceinline__ int requant(int acc, int bias, const TcArgs& g) {
     return min(max(v, g.lo), g.hi);
 }
 
-// One epilogue warp turns 32 rows x 64 accumulator columns (two TMEM loads, `r`) into int8, stages them
-// in its 32 x 64-byte shared-memory patch and writes them out with four lanes per row.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, const void* src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 :: "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(src)) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+// One epilogue warp turns 32 rows x 64 accumulator columns (two TMEM loads, `r`) into int8 in its shared-memory
+// patch and hands the patch to a TMA store (which clips rows >= M and columns >= N).
 template <int MODE>
 __device__ __forceinline__ void epilogue_pair(const uint32_t* r, const int32_t* bias64, uint8_t* my_stage, int lane,
-                                              const TcArgs& g, long long row_base, int col0) {
-    const int sw_w = (lane >> 1) & 3;   // 16-byte-piece swizzle of this lane's staging row
+                                              const TcArgs& g, const CUtensorMap* tmap_y, int row0, int col0) {
+    // the previous store out of this patch must have read it before it is overwritten
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    __syncwarp();
+    const int sw_w = (lane >> 1) & 3;   // 64-byte swizzle: 16-byte piece p of row l sits at piece p ^ ((l >> 1) & 3)
 #pragma unroll
     for (int piece = 0; piece < 4; ++piece) {
         uint32_t w[4];
@@ -106,25 +133,20 @@ __device__ __forceinline__ void epilogue_pair(const uint32_t* r, const int32_t* 
         }
         *reinterpret_cast<uint4*>(my_stage + lane * 64 + ((piece ^ sw_w) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
     }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> TMA read
     __syncwarp();
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int rr = (lane >> 2) + 8 * i, q = lane & 3;
-        const uint4 v = *reinterpret_cast<const uint4*>(my_stage + rr * 64 + ((q ^ ((rr >> 1) & 3)) << 4));
-        const long long row = row_base + rr;
-        const int col = col0 + q * 16;
-        if (row < g.M && col < g.N) *reinterpret_cast<uint4*>(g.Y + row * g.ldy + col) = v;
-    }
-    __syncwarp();
+    if (lane == 0) tma_store_2d(tmap_y, col0, row0, my_stage);
 }
 
 // MODE = rounding token, or -1 when shift == 0 (no rounding step).
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-dense_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, TcArgs g) {
+dense_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                const __grid_constant__ CUtensorMap tmap_y, TcArgs g) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    SmemTail* tail = reinterpret_cast<SmemTail*>(smem + (size_t)STAGES * STAGE_BYTES);
+    uint8_t* epi_stage = smem + (size_t)STAGES * STAGE_BYTES;   // 1024-byte aligned: whole swizzle atoms
+    SmemTail* tail = reinterpret_cast<SmemTail*>(epi_stage + (size_t)EPI_WARPS * EPI_STAGE_BYTES);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -207,8 +229,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         const int quad = warp & 3;           // TMEM lane quadrant this warp may read
         const int half = (warp - 2) >> 2;    // which half of the tile's columns this warp handles
         const int et = threadIdx.x - 64;     // 0..EPI_THREADS-1
-        uint8_t* my_stage = smem + (size_t)STAGES * STAGE_BYTES + ((sizeof(SmemTail) + 127) / 128) * 128 +
-                            (size_t)(warp - 2) * EPI_STAGE_BYTES;
+        uint8_t* my_stage = epi_stage + (size_t)(warp - 2) * EPI_STAGE_BYTES;
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -235,7 +256,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             if (ok) {
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
-                const long long row_base = (long long)m0 + quad * 32;
+                const int row_base = m0 + quad * 32;
                 // this warp's two 64-column groups; the second group's TMEM loads fly while the first is converted
                 const int c0 = half * (BN / 2), c1 = c0 + 64;
                 const bool have0 = n0 + c0 < g.N, have1 = n0 + c1 < g.N;   // warp-uniform
@@ -250,17 +271,20 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     tmem_ld32_async(taddr + (uint32_t)c1, rb);
                     tmem_ld32_async(taddr + (uint32_t)c1 + 32u, rb + 32);
                 }
-                if (have0) epilogue_pair<MODE>(ra, tile_bias + c0, my_stage, lane, g, row_base, n0 + c0);
+                if (have0) epilogue_pair<MODE>(ra, tile_bias + c0, my_stage, lane, g, &tmap_y, row_base, n0 + c0);
                 if (have1) {
                     tmem_ld_wait32(rb);
                     tmem_ld_wait32(rb + 32);
-                    epilogue_pair<MODE>(rb, tile_bias + c1, my_stage, lane, g, row_base, n0 + c1);
+                    epilogue_pair<MODE>(rb, tile_bias + c1, my_stage, lane, g, &tmap_y, row_base, n0 + c1);
                 }
                 tc_fence_before();
                 mbar_arrive(&tail->tmem_empty[acc]);
             }
             if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1u; }
         }
+        // the stores this warp issued must be complete (not merely read) before the CTA retires
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        __syncwarp();
     }
 
     // ---------------- teardown ----------------
@@ -310,8 +334,23 @@ bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// 2-D uint8 map over the row-major [rows, cols] output, box = [32 rows, 64 bytes], 64-byte swizzle: the
+// shape of one epilogue warp's staging patch.
+bool make_out_map(CUtensorMap* map, void* base, long long rows, long long cols, long long ld) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld};
+    cuuint32_t box[2] = {64u, 32u};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
+           CUDA_SUCCESS;
+}
+
 template <int MODE>
-cudaError_t launch_mode(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& g, int grid, cudaStream_t s) {
+cudaError_t launch_mode(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& my, const TcArgs& g, int grid,
+                        cudaStream_t s) {
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
@@ -319,7 +358,7 @@ cudaError_t launch_mode(const CUtensorMap& ma, const CUtensorMap& mb, const TcAr
                                         (int)SMEM_BYTES);
     });
     if (attr_err != cudaSuccess) return attr_err;
-    dense_tc_kernel<MODE><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(ma, mb, g);
+    dense_tc_kernel<MODE><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(ma, mb, my, g);
     return cudaGetLastError();
 }
 
@@ -344,8 +383,9 @@ int a4c_launch_dense_tc(const void* A, long long lda, const void* Wt, long long 
     const int sup = a4c_dense_tc_supported(A, lda, Wt, ldw, Y, ldy, M, K, N, out_dtype);
     if (sup != A4C_OK) return sup;
     if (M == 0) return A4C_OK;
-    CUtensorMap ma, mb;
-    if (!make_map(&ma, A, M, K, lda, BM) || !make_map(&mb, Wt, N, K, ldw, BN)) return A4C_ERR_CUDA;
+    CUtensorMap ma, mb, my;
+    if (!make_map(&ma, A, M, K, lda, BM) || !make_map(&mb, Wt, N, K, ldw, BN) || !make_out_map(&my, Y, M, N, ldy))
+        return A4C_ERR_CUDA;
     TcArgs g;
     g.bias = bias; g.Y = (uint8_t*)Y; g.ldy = ldy; g.M = M; g.K = K; g.N = N;
     g.num_m_tiles = (int)((M + BM - 1) / BM);
@@ -355,10 +395,13 @@ int a4c_launch_dense_tc(const void* A, long long lda, const void* Wt, long long 
     if (relu && g.lo < 0) g.lo = 0;
     const RoundParams rp = make_round_params(shift, rounding);
     g.mask = rp.mask; g.c0 = rp.c0;
-    const bool pre_clamp = shift >= 1 && shift <= 22;
+    const bool pre_clamp = shift >= 2 && shift <= 22;
     g.half = pre_clamp ? (1 << (shift - 1)) : 0;
     g.xhi = pre_clamp ? g.hi * (1 << shift) : 0;
     g.xlo = pre_clamp ? g.lo * (1 << shift) + g.half : 0;
+    g.one = 1;
+    g.mulm = pre_clamp ? (1 << (32 - shift)) : 0;
+    g.half_mul = 1LL << 31;
     g.idesc = make_idesc(BM, BN, a_unsigned != 0);
     g.status = status_word;
     int dev = 0, sms = 148;
@@ -367,19 +410,20 @@ int a4c_launch_dense_tc(const void* A, long long lda, const void* Wt, long long 
     const long long tiles = (long long)g.num_m_tiles * g.num_n_tiles;
     const int grid = (int)(tiles < sms ? tiles : sms);
     cudaError_t err;
-    if (shift == 0) err = launch_mode<-1>(ma, mb, g, grid, stream);
+    if (shift == 0) err = launch_mode<-1>(ma, mb, my, g, grid, stream);
     else switch (rounding) {
-        case A4C_RND_FLOOR: err = launch_mode<A4C_RND_FLOOR>(ma, mb, g, grid, stream); break;
-        case A4C_RND_CEIL: err = launch_mode<A4C_RND_CEIL>(ma, mb, g, grid, stream); break;
+        case A4C_RND_FLOOR: err = launch_mode<A4C_RND_FLOOR>(ma, mb, my, g, grid, stream); break;
+        case A4C_RND_CEIL: err = launch_mode<A4C_RND_CEIL>(ma, mb, my, g, grid, stream); break;
         case A4C_RND_POSITIVE_INF:
-            err = pre_clamp ? launch_mode<MODE_HALF_UP_CLAMP>(ma, mb, g, grid, stream)
-                             : launch_mode<A4C_RND_POSITIVE_INF>(ma, mb, g, grid, stream);
+            err = !pre_clamp ? launch_mode<A4C_RND_POSITIVE_INF>(ma, mb, my, g, grid, stream)
+                  : g.lo == 0 ? launch_mode<MODE_HALF_UP_RELU>(ma, mb, my, g, grid, stream)
+                              : launch_mode<MODE_HALF_UP_CLAMP>(ma, mb, my, g, grid, stream);
             break;
-        case A4C_RND_NEGATIVE_INF: err = launch_mode<A4C_RND_NEGATIVE_INF>(ma, mb, g, grid, stream); break;
-        case A4C_RND_SYMMETRIC_INF: err = launch_mode<A4C_RND_SYMMETRIC_INF>(ma, mb, g, grid, stream); break;
-        case A4C_RND_SYMMETRIC_ZERO: err = launch_mode<A4C_RND_SYMMETRIC_ZERO>(ma, mb, g, grid, stream); break;
-        case A4C_RND_CONV_EVEN: err = launch_mode<A4C_RND_CONV_EVEN>(ma, mb, g, grid, stream); break;
-        case A4C_RND_CONV_ODD: err = launch_mode<A4C_RND_CONV_ODD>(ma, mb, g, grid, stream); break;
+        case A4C_RND_NEGATIVE_INF: err = launch_mode<A4C_RND_NEGATIVE_INF>(ma, mb, my, g, grid, stream); break;
+        case A4C_RND_SYMMETRIC_INF: err = launch_mode<A4C_RND_SYMMETRIC_INF>(ma, mb, my, g, grid, stream); break;
+        case A4C_RND_SYMMETRIC_ZERO: err = launch_mode<A4C_RND_SYMMETRIC_ZERO>(ma, mb, my, g, grid, stream); break;
+        case A4C_RND_CONV_EVEN: err = launch_mode<A4C_RND_CONV_EVEN>(ma, mb, my, g, grid, stream); break;
+        case A4C_RND_CONV_ODD: err = launch_mode<A4C_RND_CONV_ODD>(ma, mb, my, g, grid, stream); break;
         default: return A4C_ERR_INVALID_ARG;
     }
     return err == cudaSuccess ? A4C_OK : A4C_ERR_CUDA;

@@ -77,6 +77,7 @@ struct LnArgs {
     const int8_t* x; long long ldx;
     const int16_t* gamma; const int16_t* beta;
     const int8_t* addend; long long ldadd;
+    int pre_add;  // the addend joins the INPUT (saturating, before the statistics) instead of the result
     int8_t* out; long long ldo;
     long long rows; int cols, log2c, eps_q0, rounding;
     RoundParams rp_gamma;  // shift 7
@@ -102,7 +103,21 @@ __global__ void __launch_bounds__(kThreads) layernorm_kernel(LnArgs a) {
         for (int j = 0; j < NCH; ++j) {
             const int chunk = j * G + gl;
             xv[j] = make_uint4(0, 0, 0, 0);
-            if (row_ok && chunk < a.geom.nchunks) xv[j] = ldg16(a.x + row * a.ldx + (long long)chunk * 16);
+            if (row_ok && chunk < a.geom.nchunks) {
+                xv[j] = ldg16(a.x + row * a.ldx + (long long)chunk * 16);
+                if (a.pre_add) {  // x <- saturate(x + addend) (elementwise_add.cpp:30-33 with SHIFT = 0)
+                    const uint4 av = ldg16(a.addend + row * a.ldadd + (long long)chunk * 16);
+                    uint32_t xw[4] = {xv[j].x, xv[j].y, xv[j].z, xv[j].w};
+                    const uint32_t aw[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+                    for (int w = 0; w < 4; ++w)
+                        xw[w] = pack4(clampi(sbyte(xw[w], 0) + sbyte(aw[w], 0), -128, 127),
+                                      clampi(sbyte(xw[w], 1) + sbyte(aw[w], 1), -128, 127),
+                                      clampi(sbyte(xw[w], 2) + sbyte(aw[w], 2), -128, 127),
+                                      clampi(sbyte(xw[w], 3) + sbyte(aw[w], 3), -128, 127));
+                    xv[j] = make_uint4(xw[0], xw[1], xw[2], xw[3]);
+                }
+            }
             sum_x = dp4a_ss(xv[j].x, 0x01010101u, sum_x); sum_sq = dp4a_ss(xv[j].x, xv[j].x, sum_sq);
             sum_x = dp4a_ss(xv[j].y, 0x01010101u, sum_x); sum_sq = dp4a_ss(xv[j].y, xv[j].y, sum_sq);
             sum_x = dp4a_ss(xv[j].z, 0x01010101u, sum_x); sum_sq = dp4a_ss(xv[j].z, xv[j].z, sum_sq);
@@ -148,7 +163,7 @@ __global__ void __launch_bounds__(kThreads) layernorm_kernel(LnArgs a) {
                 }
                 ow[w] = pack4(o[0], o[1], o[2], o[3]);
             }
-            if (a.addend) {  // fused saturating Add (elementwise_add.cpp:30-33 with SHIFT = 0)
+            if (a.addend && !a.pre_add) {  // fused saturating Add (elementwise_add.cpp:30-33 with SHIFT = 0)
                 const uint4 av = ldg16(a.addend + row * a.ldadd + (long long)chunk * 16);
                 const uint32_t aw[4] = {av.x, av.y, av.z, av.w};
 #pragma unroll
@@ -359,7 +374,7 @@ int grid_for(long long work_items, int per_block) {
 }  // namespace
 
 int a4c_launch_layernorm(const int8_t* x, long long ldx, const int16_t* gamma, const int16_t* beta,
-                         const int8_t* addend, long long ldadd, int8_t* out, long long ldo, long long rows,
+                         const int8_t* addend, long long ldadd, int pre_add, int8_t* out, long long ldo, long long rows,
                          int cols, int eps_q0, int out_shift, int rounding, cudaStream_t stream) {
     if (rows < 0 || cols <= 0 || (cols & (cols - 1)) != 0 || out_shift < 0 || out_shift > 15 || eps_q0 < 1 ||
         rounding < 0 || rounding >= A4C_RND_COUNT)
@@ -371,6 +386,7 @@ int a4c_launch_layernorm(const int8_t* x, long long ldx, const int16_t* gamma, c
         return A4C_ERR_ALIGNMENT;
     LnArgs a;
     a.x = x; a.ldx = ldx; a.gamma = gamma; a.beta = beta; a.addend = addend; a.ldadd = ldadd;
+    a.pre_add = (addend && pre_add) ? 1 : 0;
     a.out = out; a.ldo = ldo; a.rows = rows; a.cols = cols; a.eps_q0 = eps_q0; a.rounding = rounding;
     a.log2c = 0;
     while ((1 << a.log2c) < cols) ++a.log2c;

@@ -204,8 +204,11 @@ __device__ __forceinline__ int inv_std_q15(int var, int tok, bool nearest) {
 // FS = 0: conv_even, fscale = rne(inv_std * gamma / 128) in one nearest-even FMA
 // FS = 1: floor-type modes with |gamma| <= 511: inv_std * gamma + c0 is exact in FP32, then one round-down FMA
 // FS = 2: floor-type modes with larger gamma: integer multiply-add and shift
-template <int NCH, int FS, bool HAS_ADD>
+template <int NCH, int FS, int ADD>
 __global__ void __launch_bounds__(kThreads) layernorm_fast_kernel(LnFastArgs a) {
+    constexpr bool HAS_ADD = ADD == 1;   // saturating Add of the result (after the normalisation)
+    constexpr bool PRE_ADD = ADD == 2;   // saturating Add of the input (before the statistics)
+    constexpr bool RING_ADD = ADD != 0;  // a second row travels through the ring
     extern __shared__ __align__(128) uint8_t smem[];
     // layout: gamma[NCH*4*32*4] | beta[same] | barriers | ring.  Parameters are stored lane-major: position
     // ((j*4 + w)*32 + lane)*4 + k holds column (j*G + lane)*16 + w*4 + k, so for fixed (j, w) a row group reads
@@ -232,12 +235,12 @@ __global__ void __launch_bounds__(kThreads) layernorm_fast_kernel(LnFastArgs a) 
     rc.R = R;
     rc.row_bytes = (uint32_t)cols; rc.pitch = (uint32_t)a.geom.pitch;
     rc.add_off = (uint32_t)(R * a.geom.pitch);
-    rc.slot_bytes = (uint32_t)(R * a.geom.pitch) * (HAS_ADD ? 2u : 1u);
+    rc.slot_bytes = (uint32_t)(R * a.geom.pitch) * (RING_ADD ? 2u : 1u);
     rc.bars = s_bar + warp * a.stages * 8;
     const uint32_t ring0 = (s_bar + kWarps * a.stages * 8 + 127u) & ~127u;
     rc.slots = ring0 + warp * a.stages * rc.slot_bytes;
     rc.x = reinterpret_cast<const uint8_t*>(a.x); rc.ldx = a.ldx;
-    rc.addend = HAS_ADD ? reinterpret_cast<const uint8_t*>(a.addend) : nullptr; rc.ldadd = a.ldadd;
+    rc.addend = RING_ADD ? reinterpret_cast<const uint8_t*>(a.addend) : nullptr; rc.ldadd = a.ldadd;
     rc.rows = a.rows;
     if (lane == 0)
         for (int s = 0; s < a.stages; ++s) mbar_init(rc.bars + s * 8, 1);
@@ -273,7 +276,22 @@ __global__ void __launch_bounds__(kThreads) layernorm_fast_kernel(LnFastArgs a) 
         for (int j = 0; j < NCH; ++j) {
             const bool ok = row_ok && (j * G + gl) < a.geom.nchunks;
             xv[j] = ok ? lds128(slot + j * G * 16) : make_uint4(0, 0, 0, 0);
-            if (HAS_ADD) av[j] = ok ? lds128(slot + rc.add_off + j * G * 16) : make_uint4(0, 0, 0, 0);
+            if (RING_ADD) av[j] = ok ? lds128(slot + rc.add_off + j * G * 16) : make_uint4(0, 0, 0, 0);
+            if (PRE_ADD) {
+                // x <- saturate_i8(x + addend) (elementwise_add.cpp:30-33, SHIFT = 0): sign-extended byte pairs,
+                // packed add + min(., 127), packed max(., -128), low bytes back into one word
+                uint32_t xs[4] = {xv[j].x, xv[j].y, xv[j].z, xv[j].w};
+                const uint32_t as[4] = {av[j].x, av[j].y, av[j].z, av[j].w};
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    uint32_t lo = __viaddmin_s16x2(prmt(xs[w], 0, 0x9180), prmt(as[w], 0, 0x9180), 0x007F007Fu);
+                    uint32_t hi = __viaddmin_s16x2(prmt(xs[w], 0, 0xB3A2), prmt(as[w], 0, 0xB3A2), 0x007F007Fu);
+                    lo = __vimax3_s16x2(lo, 0xFF80FF80u, 0xFF80FF80u);
+                    hi = __vimax3_s16x2(hi, 0xFF80FF80u, 0xFF80FF80u);
+                    xs[w] = prmt(lo, hi, 0x6420);
+                }
+                xv[j] = make_uint4(xs[0], xs[1], xs[2], xs[3]);
+            }
         }
         __syncwarp();
         {
@@ -622,9 +640,9 @@ void a4c_rowops_fast_tuning(int chunks_per_lane, int min_stages) {
 // Returns A4C_ERR_UNSUPPORTED when the request is outside the fast path's proofs (caller falls back
 // to the generic kernel).
 int a4c_launch_layernorm_fast(const int8_t* x, long long ldx, const int16_t* gamma, const int16_t* beta,
-                              const int8_t* addend, long long ldadd, int8_t* out, long long ldo, long long rows,
-                              int cols, int eps_q0, int out_shift, int rounding, int gamma_absmax, int* status,
-                              cudaStream_t stream) {
+                              const int8_t* addend, long long ldadd, int pre_add, int8_t* out, long long ldo,
+                              long long rows, int cols, int eps_q0, int out_shift, int rounding, int gamma_absmax,
+                              int* status, cudaStream_t stream) {
     const int s_out = 15 - out_shift;
     if (s_out < 2 || gamma_absmax <= 0 || gamma_absmax > 16383) return A4C_ERR_UNSUPPORTED;
     if (rounding == A4C_RND_SYMMETRIC_INF || rounding == A4C_RND_SYMMETRIC_ZERO || rounding == A4C_RND_CONV_ODD)
@@ -665,7 +683,7 @@ int a4c_launch_layernorm_fast(const int8_t* x, long long ldx, const int16_t* gam
     } while (0)
 #define LN_PICK(NCH_)                                                                                              \
     do {                                                                                                           \
-        if (addend) LN_PICK_FS(NCH_, true); else LN_PICK_FS(NCH_, false);                                          \
+        if (!addend) LN_PICK_FS(NCH_, 0); else if (pre_add) LN_PICK_FS(NCH_, 2); else LN_PICK_FS(NCH_, 1);         \
     } while (0)
     if (nch == 1) LN_PICK(1);
     else if (nch == 2) LN_PICK(2);

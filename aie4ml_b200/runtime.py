@@ -176,11 +176,12 @@ class Plan:
         if fuse_attention:
             self._fuse_attention()
         if fuse_rowop_add:
+            self._fuse_add_layernorm()
             self._fuse_rowop_add()
 
         live = set(graph.input_tensor_names) | set(graph.output_tensor_names)
         for op in self.ops:
-            for key in ('lhs', 'rhs', 'out', 'addend', 'q', 'k', 'v'):
+            for key in ('lhs', 'rhs', 'out', 'addend', 'pre_addend', 'q', 'k', 'v'):
                 if op.get(key):
                     live.add(op[key])
         for name in sorted(live):
@@ -261,7 +262,7 @@ class Plan:
                 if j is None or j in drop:
                     continue
                 prod = self.ops[j]
-                if prod['kind'] not in ('layer_norm', 'softmax') or prod.get('addend'):
+                if prod['kind'] not in ('layer_norm', 'softmax') or prod.get('addend') or prod.get('pre_addend'):
                     continue
                 t = graph.tensors[mid]
                 if len(t.consumers) != 1 or mid in graph.output_tensor_names or mid in aliased:
@@ -279,6 +280,33 @@ class Plan:
             for op in self.ops:
                 if op.get('fused_out'):
                     op['out'] = op.pop('fused_out')
+            self.ops = [op for i, op in enumerate(self.ops) if i not in drop]
+
+    def _fuse_add_layernorm(self) -> None:
+        """add (same int8 type, shift 0) -> layer_norm becomes one launch that adds while it loads: the sum is
+        never stored.  The sum must feed only the LayerNorm and be neither a graph output nor a view."""
+        graph = self.graph
+        produced_at = {op['out']: i for i, op in enumerate(self.ops)}
+        aliased = set(self.alias) | {p for p, _, _ in self.alias.values()}
+        drop = set()
+        for ln in self.ops:
+            if ln['kind'] != 'layer_norm' or ln.get('addend'):
+                continue
+            mid = ln['lhs']
+            j = produced_at.get(mid)
+            if j is None or j in drop:
+                continue
+            add = self.ops[j]
+            if add['kind'] != 'add' or add['shift'] != 0:
+                continue
+            if len(graph.tensors[mid].consumers) != 1 or mid in graph.output_tensor_names or mid in aliased:
+                continue
+            if any(self.fmt[t] != 'int8' for t in (add['lhs'], add['rhs'], mid)):
+                continue
+            ln['lhs'], ln['pre_addend'] = add['lhs'], add['rhs']
+            self.fused.append(f"{add['name']}+{ln['name']}")
+            drop.add(j)
+        if drop:
             self.ops = [op for i, op in enumerate(self.ops) if i not in drop]
 
     def _attention_args(self, op: Dict[str, Any]) -> tuple:
@@ -390,13 +418,19 @@ class Plan:
             if (rows, cols) != (rows_y, cols_y):
                 raise ValueError(f'{name}: input and output views differ in shape.')
             add_ptr, ldadd = None, 0
-            other = op.get('addend') if kind != 'add' else op['rhs']
+            other = (op.get('addend') or op.get('pre_addend')) if kind != 'add' else op['rhs']
             if other:
                 o = self._view(other)
                 o_off, ro, co, ldadd = collapse_2d(o, f'{name}: addend')
                 if (ro, co) != (rows, cols):
                     raise ValueError(f'{name}: addend shape differs from the output.')
                 add_ptr = self.ptr(o, o_off)
+            if kind == 'layer_norm' and op.get('pre_addend'):
+                args = (self.ptr(x, x_off), ldx, add_ptr, ldadd, self.params[op['gamma']].data_ptr(),
+                        self.params[op['beta']].data_ptr(), self.ptr(y, y_off), ldy, rows, cols, op['eps_q0'],
+                        op['out_shift'], ROUNDING_CODE[op['rounding']],
+                        int(np.abs(self.params_np[op['gamma']].astype(np.int64)).max()))
+                return L.a4c_add_layernorm_i8, args
             if kind == 'layer_norm':
                 args = (self.ptr(x, x_off), ldx, self.params[op['gamma']].data_ptr(), self.params[op['beta']].data_ptr(),
                         add_ptr, ldadd, self.ptr(y, y_off), ldy, rows, cols, op['eps_q0'], op['out_shift'],

@@ -126,6 +126,15 @@ A4C_API int a4c_layernorm_i8(const int8_t* x, int64_t ldx, const int16_t* gamma,
                      int eps_q0, int out_shift, int rounding, int gamma_absmax, void* stream);
 
 /*
+ * out = layernorm( saturate_i8(x + residual) ): the exact-type residual Add of elementwise_add.cpp:12-37
+ * (SHIFT = 0) followed by the LayerNorm above, in one pass over the rows -- the sum is never written.
+ * The reference runs these as two kernels; the result is the same bytes as a4c_add_sat then a4c_layernorm_i8.
+ */
+A4C_API int a4c_add_layernorm_i8(const int8_t* x, int64_t ldx, const int8_t* residual, int64_t ldr,
+                         const int16_t* gamma, const int16_t* beta, int8_t* out, int64_t ldo, int64_t rows,
+                         int cols, int eps_q0, int out_shift, int rounding, int gamma_absmax, void* stream);
+
+/*
  * Quantized Softmax over rows of int8, output uint8 (dtype 1) or int16 (dtype 2).
  * mode 0 = HCCS clipped-linear surrogate: replaces softmax_i8::softmax_row / softmax_i8_tiled::run
  *          (src/aie4ml/templates/nnet_utils/softmax/softmax.cpp:20-88, 159-239); B, S, Dmax, inv_shift,

@@ -74,6 +74,20 @@ def bmm(a, b, *, shift, tok, trans_a=False, trans_b=False, out_dtype='int8'):
     return c_d.cpu().numpy()
 
 
+def add_layer_norm(x, residual, gamma, beta, *, eps_q0, out_shift, tok):
+    L = a4c.load()
+    rows, cols = x.shape
+    x_d, r_d = dev(x), dev(residual)
+    g_d, b_d = dev(gamma.astype(np.int16)), dev(beta.astype(np.int16))
+    o_d = torch.zeros((rows, cols), dtype=torch.int8, device='cuda')
+    rc = L.a4c_add_layernorm_i8(x_d.data_ptr(), cols, r_d.data_ptr(), cols, g_d.data_ptr(), b_d.data_ptr(),
+                                o_d.data_ptr(), cols, rows, cols, eps_q0, out_shift, ROUNDING_CODE[tok],
+                                int(np.abs(gamma).max()), stream())
+    a4c.check(rc, 'a4c_add_layernorm_i8')
+    a4c.device_status(stream())
+    return o_d.cpu().numpy()
+
+
 def layer_norm(x, gamma, beta, *, eps_q0, out_shift, tok, addend=None):
     L = a4c.load()
     rows, cols = x.shape

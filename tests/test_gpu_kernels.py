@@ -218,6 +218,25 @@ def test_layer_norm(cols, tok, rowop_path):
     np.testing.assert_array_equal(fused, want)
 
 
+@pytest.mark.parametrize('cols', [64, 256, 1024, 4096])
+@pytest.mark.parametrize('tok', ['positive_inf', 'conv_even', 'symmetric_inf'])
+def test_add_then_layer_norm_in_one_pass(cols, tok, rowop_path):
+    """layernorm(saturate(x + residual)) against the oracle's two steps; the sums saturate on both sides."""
+    import gpu_util as G
+
+    x, rng = _ln_inputs(cols + 3, 77, cols)
+    residual = rng.integers(-128, 128, x.shape).astype(np.int8)
+    residual[0] = 127
+    residual[1] = -128
+    gamma = rng.integers(-256, 257, cols)
+    beta = rng.integers(-256, 257, cols)
+    for out_shift in (4, 13):
+        got = G.add_layer_norm(x, residual, gamma, beta, eps_q0=1, out_shift=out_shift, tok=tok)
+        want = oracle.layer_norm(oracle.add(x, residual, out_dtype='int8'), gamma, beta, eps_q0=1, out_shift=out_shift,
+                                 tok=tok)
+        np.testing.assert_array_equal(got, want)
+
+
 def test_layer_norm_every_rounding_mode(rowop_path):
     import gpu_util as G
 

@@ -40,6 +40,8 @@ def test_cfg3_encoder_block(softmax, rounding):
     # every head's QK^T -> softmax -> AV chain runs as one fused launch; scores and probabilities have no buffer
     assert kinds.count('attention') == 4 and kinds.count('matmul') == 0 and kinds.count('softmax') == 0
     assert kinds.count('layer_norm') == 2 and not any(n.startswith(('qk', 'sm')) for n in model.plan.buffers)
+    # both residual Adds ride inside their LayerNorm launches
+    assert kinds.count('add') == 0 and sum(1 for op in model.plan.ops if op.get('pre_addend')) == 2
     unfused = _check(*W.encoder_cfg3(3, softmax=softmax, rounding=rounding), FusionPolicy={'attention': False})
     kinds = [op['kind'] for op in unfused.plan.ops]
     assert kinds.count('matmul') == 8 and kinds.count('softmax') == 4 and kinds.count('attention') == 0
