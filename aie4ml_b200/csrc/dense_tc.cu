@@ -37,18 +37,17 @@ constexpr int ACC_STAGES = 2;
 constexpr int TMEM_COLS = ACC_STAGES * BN;       // 512
 constexpr int EPI_WARPS = 8;           // two warps per TMEM lane quadrant, each takes half of the tile's columns
 constexpr int EPI_THREADS = EPI_WARPS * 32;
+constexpr int EPI_GROUP_THREADS = EPI_THREADS / 2;   // one group per accumulator
 constexpr int NUM_THREADS = 64 + EPI_THREADS;
-// positive_inf with 2 <= shift <= 22: saturate BEFORE the shift (rounding is monotonic, and lo*2^s / hi*2^s
-// round to lo / hi exactly), which makes the rounding add overflow-free.  The integer ALU of an SM
-// sub-partition retires half a warp per clock and is what bounds this epilogue, so the sequence is split
-// between it and the multiply-add pipe:
-//   x = acc * 1 + bias                         multiply-add pipe (the 1 is a kernel argument, so it stays a multiply)
-//   MODE_HALF_UP_RELU  (lo == 0):  t = max(min(x, hi*2^s), 0)                  one ALU instruction
-//                                  y = hi32(t * 2^(32-s) + 2^31)               multiply-add pipe: (t + 2^(s-1)) >> s
-//   MODE_HALF_UP_CLAMP:            t = min(x, hi*2^s); u = max(t + 2^(s-1), lo*2^s + 2^(s-1))     two ALU instructions
-//                                  y = hi32(u * 2^(32-s))                      multiply-add pipe: u >> s
+// positive_inf with 1 <= shift <= 22: saturate BEFORE the shift (rounding is monotonic, and lo*2^s / hi*2^s
+// round to lo / hi exactly), which makes the rounding add overflow-free and folds bias add, both clamps
+// and the rounding add into two add-min/max instructions plus the shift.
 constexpr int MODE_HALF_UP_CLAMP = 100;
-constexpr int MODE_HALF_UP_RELU = 101;
+// The same for shift <= 13, with the shift moved off the integer pipe (which bounds this epilogue: it retires
+// half a warp per clock): the clamped value n = x + 2^(s-1), |n| < 2^22, is produced directly as the bit pattern
+// of the float 1.5*2^23 + n, and one round-down FMA by 2^-s leaves floor(n / 2^s) in the low mantissa bits.
+constexpr int MODE_HALF_UP_FLOAT = 102;
+constexpr int MAGIC_BITS = 0x4B400000;   // 1.5 * 2^23
 
 constexpr int BIAS_CACHE = 2048;   // whole bias vector resident in shared memory when N fits
 
@@ -78,27 +77,22 @@ struct TcArgs {
     int num_m_tiles, num_n_tiles;
     int shift, lo, hi;
     uint32_t mask, c0;   // rounding constants (see round_shift_i32_t)
-    int half, xhi, xlo;  // MODE_HALF_UP_*: 2^(s-1), hi * 2^s, lo * 2^s + 2^(s-1)
-    int one, mulm;       // MODE_HALF_UP_*: 1 and 2^(32-s)
-    long long half_mul;  // MODE_HALF_UP_RELU: 2^(s-1) * 2^(32-s) = 2^31
+    int half, xhi, xlo;  // MODE_HALF_UP_CLAMP / _FLOAT: 2^(s-1), hi * 2^s, lo * 2^s + 2^(s-1)
+    float fmul, fadd;    // MODE_HALF_UP_FLOAT: 2^-s and 1.5*2^23 * (1 - 2^-s)
     uint32_t idesc;
     int* status;
 };
 
 template <int MODE>
 __device__ __forceinline__ int requant(int acc, int bias, const TcArgs& g) {
-    if (MODE == MODE_HALF_UP_CLAMP || MODE == MODE_HALF_UP_RELU) {
-        int x, y;
-        asm("mad.lo.s32 %0, %1, %2, %3;" : "=r"(x) : "r"(acc), "r"(g.one), "r"(bias));   // wrap32(acc + bias)
-        if (MODE == MODE_HALF_UP_RELU) {
-            const int t = __vimin_s32_relu(x, g.xhi);
-            asm("{\n\t.reg .s64 w;\n\tmad.wide.s32 w, %1, %2, %3;\n\tmov.b64 {_, %0}, w;\n\t}"
-                : "=r"(y) : "r"(t), "r"(g.mulm), "l"(g.half_mul));
-        } else {
-            const int u = __viaddmax_s32(min(x, g.xhi), g.half, g.xlo);
-            asm("mul.hi.s32 %0, %1, %2;" : "=r"(y) : "r"(u), "r"(g.mulm));
-        }
-        return y;
+    if (MODE == MODE_HALF_UP_FLOAT) {
+        const int t = __viaddmin_s32(acc, bias, g.xhi);
+        const int u = __viaddmax_s32(t, g.half + MAGIC_BITS, g.xlo + MAGIC_BITS);   // bits of 1.5*2^23 + x + 2^(s-1)
+        return __float_as_int(__fmaf_rd(__int_as_float(u), g.fmul, g.fadd));        // only the low byte is used
+    }
+    if (MODE == MODE_HALF_UP_CLAMP) {
+        const int t = __viaddmin_s32(acc, bias, g.xhi);          // min(wrap32(acc + bias), hi * 2^s)
+        return __viaddmax_s32(t, g.half, g.xlo) >> g.shift;      // max(t + 2^(s-1), lo * 2^s + 2^(s-1)) >> s
     }
     int v = acc + bias;
     if (MODE == A4C_RND_FLOOR) v = v >> g.shift;
@@ -121,15 +115,26 @@ __device__ __forceinline__ void epilogue_pair(const uint32_t* r, const int32_t* 
     if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     __syncwarp();
     const int sw_w = (lane >> 1) & 3;   // 64-byte swizzle: 16-byte piece p of row l sits at piece p ^ ((l >> 1) & 3)
+    // the 64 bias values are the same for every lane (a lane is a row): broadcast loads, issued one 16-column
+    // piece ahead of their use so that their latency hides under the previous piece's arithmetic
+    int4 bnext[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) bnext[q] = *reinterpret_cast<const int4*>(bias64 + q * 4);
 #pragma unroll
     for (int piece = 0; piece < 4; ++piece) {
+        int4 b[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) b[q] = bnext[q];
+        if (piece < 3) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) bnext[q] = *reinterpret_cast<const int4*>(bias64 + (piece + 1) * 16 + q * 4);
+        }
         uint32_t w[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-            const int4 b = *reinterpret_cast<const int4*>(bias64 + piece * 16 + q * 4);
             const uint32_t* a = r + piece * 16 + q * 4;
-            w[q] = pack4_i8(requant<MODE>((int)a[0], b.x, g), requant<MODE>((int)a[1], b.y, g),
-                            requant<MODE>((int)a[2], b.z, g), requant<MODE>((int)a[3], b.w, g));
+            w[q] = pack4_i8(requant<MODE>((int)a[0], b[q].x, g), requant<MODE>((int)a[1], b[q].y, g),
+                            requant<MODE>((int)a[2], b[q].z, g), requant<MODE>((int)a[3], b[q].w, g));
         }
         *reinterpret_cast<uint4*>(my_stage + lane * 64 + ((piece ^ sw_w) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
     }
@@ -155,7 +160,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&tail->full[s], 1); mbar_init(&tail->empty[s], 1); }
-        for (int s = 0; s < ACC_STAGES; ++s) { mbar_init(&tail->tmem_full[s], 1); mbar_init(&tail->tmem_empty[s], EPI_THREADS); }
+        for (int s = 0; s < ACC_STAGES; ++s) { mbar_init(&tail->tmem_full[s], 1); mbar_init(&tail->tmem_empty[s], EPI_GROUP_THREADS); }
         tail->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -198,7 +203,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-                ok = mbar_wait(&tail->tmem_empty[acc], acc_phase ^ 1u, abort_flag, g.status, 102);
+                ok = mbar_wait_spin(&tail->tmem_empty[acc], acc_phase ^ 1u, abort_flag, g.status, 102);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
@@ -225,62 +230,75 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         }
         __syncwarp();
     } else {
-        // ---------------- epilogue (warps 2..5) ----------------
+        // ---------------- epilogue: two groups of four warps on alternate tiles ----------------
+        // Group 0 (warps 2-5) converts even tiles out of accumulator 0, group 1 (warps 6-9) odd tiles out of
+        // accumulator 1.  The two warps that share an SM sub-partition are therefore in different phases:
+        // one waits for its accumulator or for a TMEM load while the other keeps the integer pipe busy.
         const int quad = warp & 3;           // TMEM lane quadrant this warp may read
-        const int half = (warp - 2) >> 2;    // which half of the tile's columns this warp handles
-        const int et = threadIdx.x - 64;     // 0..EPI_THREADS-1
+        const int grp = (warp - 2) >> 2;     // which accumulator / which tiles
+        const int gt = threadIdx.x - 64 - grp * EPI_GROUP_THREADS;   // 0..127 inside the group
         uint8_t* my_stage = epi_stage + (size_t)(warp - 2) * EPI_STAGE_BYTES;
-        int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
         const bool bias_resident = g.num_n_tiles * BN <= BIAS_CACHE;
         if (bias_resident) {
             // the whole (zero-padded) bias vector once: no global load on any tile's critical path
-            for (int i = et; i < g.num_n_tiles * BN; i += EPI_THREADS)
+            for (int i = threadIdx.x - 64; i < g.num_n_tiles * BN; i += EPI_THREADS)
                 tail->bias[i] = (g.bias != nullptr && i < g.N) ? __ldg(g.bias + i) : 0;
             asm volatile("bar.sync 1, 256;" ::: "memory");
         }
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-            const int m0 = (tile / g.num_n_tiles) * BM;
-            const int n0 = (tile % g.num_n_tiles) * BN;
-            const int32_t* tile_bias = tail->bias + (bias_resident ? n0 : acc * BN);
+        // tile = blockIdx.x + n * gridDim.x for this group's n = grp, grp + 2, ...; (mt, nt) follow without division
+        const int step = 2 * (int)gridDim.x;
+        const int step_m = step / g.num_n_tiles, step_n = step % g.num_n_tiles;
+        const int first = (int)blockIdx.x + grp * (int)gridDim.x;
+        int mt = first / g.num_n_tiles, nt = first % g.num_n_tiles;
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(grp * BN);
+        for (int tile = first; tile < num_tiles; tile += step) {
+            const int m0 = mt * BM, n0 = nt * BN;
+            mt += step_m; nt += step_n;
+            if (nt >= g.num_n_tiles) { nt -= g.num_n_tiles; ++mt; }
+            const int32_t* tile_bias = tail->bias + (bias_resident ? n0 : grp * BN);
             if (!bias_resident) {
-                // stage this tile's bias slice (zero where there is none)
-                for (int i = et; i < BN; i += EPI_THREADS) {
+                // stage this tile's bias slice (zero where there is none); the group's previous tile is done with it
+                asm volatile("bar.sync %0, 128;" :: "r"(2 + grp) : "memory");
+                for (int i = gt; i < BN; i += EPI_GROUP_THREADS) {
                     const int n = n0 + i;
-                    tail->bias[acc * BN + i] = (g.bias != nullptr && n < g.N) ? __ldg(g.bias + n) : 0;
+                    tail->bias[grp * BN + i] = (g.bias != nullptr && n < g.N) ? __ldg(g.bias + n) : 0;
                 }
-                asm volatile("bar.sync 1, 256;" ::: "memory");
+                asm volatile("bar.sync %0, 128;" :: "r"(2 + grp) : "memory");
             }
-            if (ok) ok = mbar_wait(&tail->tmem_full[acc], acc_phase, abort_flag, g.status, 104);
-            if (ok) {
-                tc_fence_after();
-                const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
-                const int row_base = m0 + quad * 32;
-                // this warp's two 64-column groups; the second group's TMEM loads fly while the first is converted
-                const int c0 = half * (BN / 2), c1 = c0 + 64;
-                const bool have0 = n0 + c0 < g.N, have1 = n0 + c1 < g.N;   // warp-uniform
-                uint32_t ra[64], rb[64];
-                if (have0) {
-                    tmem_ld32_async(taddr + (uint32_t)c0, ra);
-                    tmem_ld32_async(taddr + (uint32_t)c0 + 32u, ra + 32);
-                    tmem_ld_wait32(ra);
-                    tmem_ld_wait32(ra + 32);
-                }
-                if (have1) {
-                    tmem_ld32_async(taddr + (uint32_t)c1, rb);
-                    tmem_ld32_async(taddr + (uint32_t)c1 + 32u, rb + 32);
-                }
-                if (have0) epilogue_pair<MODE>(ra, tile_bias + c0, my_stage, lane, g, &tmap_y, row_base, n0 + c0);
-                if (have1) {
-                    tmem_ld_wait32(rb);
-                    tmem_ld_wait32(rb + 32);
-                    epilogue_pair<MODE>(rb, tile_bias + c1, my_stage, lane, g, &tmap_y, row_base, n0 + c1);
-                }
-                tc_fence_before();
-                mbar_arrive(&tail->tmem_empty[acc]);
+            if (ok) ok = mbar_wait(&tail->tmem_full[grp], acc_phase, abort_flag, g.status, 104);
+            acc_phase ^= 1u;
+            if (!ok) continue;
+            tc_fence_after();
+            const int row_base = m0 + quad * 32;
+            // four 64-column groups per warp; the next group's TMEM loads fly while this one is converted
+            uint32_t ra[64], rb[64];
+            const bool have[4] = {n0 < g.N, n0 + 64 < g.N, n0 + 128 < g.N, n0 + 192 < g.N};   // warp-uniform
+            if (have[0]) {
+                tmem_ld32_async(taddr, ra);
+                tmem_ld32_async(taddr + 32u, ra + 32);
+                tmem_ld_wait32(ra);
+                tmem_ld_wait32(ra + 32);
             }
-            if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1u; }
+            if (have[1]) { tmem_ld32_async(taddr + 64u, rb); tmem_ld32_async(taddr + 96u, rb + 32); }
+            if (have[0]) epilogue_pair<MODE>(ra, tile_bias, my_stage, lane, g, &tmap_y, row_base, n0);
+            if (have[1]) { tmem_ld_wait32(rb); tmem_ld_wait32(rb + 32); }
+            if (have[2]) { tmem_ld32_async(taddr + 128u, ra); tmem_ld32_async(taddr + 160u, ra + 32); }
+            if (have[1]) epilogue_pair<MODE>(rb, tile_bias + 64, my_stage, lane, g, &tmap_y, row_base, n0 + 64);
+            if (have[2]) { tmem_ld_wait32(ra); tmem_ld_wait32(ra + 32); }
+            if (have[3]) {
+                tmem_ld32_async(taddr + 192u, rb);
+                tmem_ld32_async(taddr + 224u, rb + 32);
+                tmem_ld_wait32(rb);
+                tmem_ld_wait32(rb + 32);
+            }
+            // Half-way through the tile every accumulator column is in registers or already converted: hand the
+            // buffer back now, so the MMAs of this group's next tile run under the remaining two conversions.
+            tc_fence_before();
+            mbar_arrive(&tail->tmem_empty[grp]);
+            if (have[2]) epilogue_pair<MODE>(ra, tile_bias + 128, my_stage, lane, g, &tmap_y, row_base, n0 + 128);
+            if (have[3]) epilogue_pair<MODE>(rb, tile_bias + 192, my_stage, lane, g, &tmap_y, row_base, n0 + 192);
         }
         // the stores this warp issued must be complete (not merely read) before the CTA retires
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -395,13 +413,12 @@ int a4c_launch_dense_tc(const void* A, long long lda, const void* Wt, long long 
     if (relu && g.lo < 0) g.lo = 0;
     const RoundParams rp = make_round_params(shift, rounding);
     g.mask = rp.mask; g.c0 = rp.c0;
-    const bool pre_clamp = shift >= 2 && shift <= 22;
+    const bool pre_clamp = shift >= 1 && shift <= 22;
     g.half = pre_clamp ? (1 << (shift - 1)) : 0;
     g.xhi = pre_clamp ? g.hi * (1 << shift) : 0;
     g.xlo = pre_clamp ? g.lo * (1 << shift) + g.half : 0;
-    g.one = 1;
-    g.mulm = pre_clamp ? (1 << (32 - shift)) : 0;
-    g.half_mul = 1LL << 31;
+    g.fmul = pre_clamp ? 1.0f / (float)(1 << shift) : 0.0f;
+    g.fadd = 12582912.0f - 12582912.0f * g.fmul;
     g.idesc = make_idesc(BM, BN, a_unsigned != 0);
     g.status = status_word;
     int dev = 0, sms = 148;
@@ -416,8 +433,8 @@ int a4c_launch_dense_tc(const void* A, long long lda, const void* Wt, long long 
         case A4C_RND_CEIL: err = launch_mode<A4C_RND_CEIL>(ma, mb, my, g, grid, stream); break;
         case A4C_RND_POSITIVE_INF:
             err = !pre_clamp ? launch_mode<A4C_RND_POSITIVE_INF>(ma, mb, my, g, grid, stream)
-                  : g.lo == 0 ? launch_mode<MODE_HALF_UP_RELU>(ma, mb, my, g, grid, stream)
-                              : launch_mode<MODE_HALF_UP_CLAMP>(ma, mb, my, g, grid, stream);
+                  : shift <= 13 ? launch_mode<MODE_HALF_UP_FLOAT>(ma, mb, my, g, grid, stream)
+                                : launch_mode<MODE_HALF_UP_CLAMP>(ma, mb, my, g, grid, stream);
             break;
         case A4C_RND_NEGATIVE_INF: err = launch_mode<A4C_RND_NEGATIVE_INF>(ma, mb, my, g, grid, stream); break;
         case A4C_RND_SYMMETRIC_INF: err = launch_mode<A4C_RND_SYMMETRIC_INF>(ma, mb, my, g, grid, stream); break;

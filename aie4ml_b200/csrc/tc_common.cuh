@@ -48,6 +48,34 @@ static __device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, vo
     }
 }
 
+// Same contract, but polls with the non-suspending test_wait: for a single-thread role whose wake-up latency
+// sits on the critical path (the MMA issuer waiting for an accumulator buffer).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+static __device__ __noinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                            int code) {
+    if (mbar_test_wait(bar, parity)) return true;
+    const uint64_t t0 = a4c_globaltimer();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if ((it & 1023u) == 0) {
+            if (*abort_flag) return false;
+            if (a4c_globaltimer() - t0 > A4C_SPIN_LIMIT_NS) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
