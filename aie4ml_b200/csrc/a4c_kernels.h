@@ -52,6 +52,14 @@ int a4c_launch_bmm_tc(const void* A, long long lda, long long stride_a, const vo
                       void* C, long long ldc, long long stride_c, long long batch, int M, int K, int N, int trans_b,
                       int shift, int rounding, int out_dtype, int a_unsigned, int* status_word, cudaStream_t stream);
 
+// A chain of narrow Dense layers as one kernel (mlp_small.cu), and the choice a4c_mlp_i8 makes (mlp_chain.cu).
+int a4c_mlp_small_supported(int n_layers, const int* dims, int out_dtype);
+int a4c_launch_mlp_small(const void* X, long long ldx, int x_unsigned, int n_layers, const int* dims,
+                         const int8_t* const* Wt, const long long* ldw, const int32_t* const* bias, const int* shift,
+                         const int* relu, int rounding, void* Y, long long ldy, int out_dtype, long long M,
+                         cudaStream_t stream);
+void a4c_mlp_set_path(int path);
+
 // Fused attention head (attention_tc.cu): scores, softmax and the value product in one kernel.
 int a4c_attention_tc_supported(const void* q, long long ldq, long long stride_q, const void* k, long long ldk,
                                long long stride_k, const void* v, long long ldv, long long stride_v, const void* out,

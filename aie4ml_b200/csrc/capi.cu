@@ -172,6 +172,10 @@ int a4c_set_option(int option, int value) {
         g_bmm_path = value;
         return A4C_OK;
     }
+    if (option == A4C_OPT_MLP_PATH && value >= 0 && value <= 2) {
+        a4c_mlp_set_path(value);
+        return A4C_OK;
+    }
     if (option == A4C_OPT_ROWOP_CHUNKS_PER_LANE && (value == 0 || value == 1 || value == 2 || value == 4)) {
         a4c_rowops_fast_tuning(value, -1);
         return A4C_OK;

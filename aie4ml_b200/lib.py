@@ -27,6 +27,7 @@ OPT_ROWOP_PATH = 0
 OPT_BMM_PATH = 1
 OPT_ROWOP_CHUNKS_PER_LANE = 2
 OPT_ROWOP_MIN_STAGES = 3
+OPT_MLP_PATH = 4
 
 # name -> (restype, argtypes); mirrors the header declaration by declaration
 SIGNATURES = {
@@ -43,6 +44,7 @@ SIGNATURES = {
     'a4c_set_option': (c_int, [c_int, c_int]),
     'a4c_mlp_i8': (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                            c_int, c_void_p, c_int64, c_int, c_int64, c_void_p]),
+    'a4c_mlp_i8_single_kernel': (c_int, [c_int, c_void_p, c_int, c_int64]),
     'a4c_mlp_i8_static': (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_int, c_void_p, c_int64, c_int, c_int64, ctypes.POINTER(c_int), c_void_p]),
     'a4c_softmax_i8': (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int, c_int, c_int,

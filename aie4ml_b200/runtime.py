@@ -109,7 +109,8 @@ class Plan:
     """Buffers, views, device constants and the launch list of one lowered model."""
 
     def __init__(self, ctx: BackendContext, device: Optional[str] = None, fuse_rowop_add: bool = True,
-                 dense_algo: int = _lib.ALGO_AUTO, share_params: Optional['Plan'] = None, fuse_attention: bool = True):
+                 dense_algo: int = _lib.ALGO_AUTO, share_params: Optional['Plan'] = None, fuse_attention: bool = True,
+                 fuse_dense_chain: bool = True):
         torch = _torch()
         self.ctx = ctx
         self.lib = _lib.load()
@@ -120,6 +121,7 @@ class Plan:
         self.dense_algo = int(dense_algo)
         self.fuse_rowop_add = bool(fuse_rowop_add)
         self.fuse_attention = bool(fuse_attention)
+        self.fuse_dense_chain = bool(fuse_dense_chain)
         graph = ctx.ir.logical
         self.graph = graph
 
@@ -175,6 +177,9 @@ class Plan:
         self.buffers: Dict[str, Any] = {}
         if fuse_attention:
             self._fuse_attention()
+        self._keepalive: List[Any] = []
+        if fuse_dense_chain:
+            self._fuse_dense_chain()
         if fuse_rowop_add:
             self._fuse_add_layernorm()
             self._fuse_rowop_add()
@@ -281,6 +286,62 @@ class Plan:
                 if op.get('fused_out'):
                     op['out'] = op.pop('fused_out')
             self.ops = [op for i, op in enumerate(self.ops) if i not in drop]
+
+    def _fuse_dense_chain(self) -> None:
+        """Consecutive Dense layers whose intermediates feed nothing else become one `mlp` op when the library
+        runs such a chain as a single kernel (a4c_mlp_i8_single_kernel): weights and activations then stay in
+        shared memory and the intermediates get no buffer."""
+        import ctypes
+
+        graph = self.graph
+        aliased = set(self.alias) | {p for p, _, _ in self.alias.values()}
+        consumer_of = {}
+        for i, op in enumerate(self.ops):
+            for key in ('lhs', 'rhs'):
+                if op.get(key):
+                    consumer_of.setdefault(op[key], []).append(i)
+
+        def chainable(op) -> bool:
+            return op['kind'] == 'dense' and not op['transpose_lhs']
+
+        used, chains = set(), []
+        for i, op in enumerate(self.ops):
+            if i in used or not chainable(op):
+                continue
+            chain = [i]
+            while True:
+                cur = self.ops[chain[-1]]
+                mid = cur['out']
+                nxt = consumer_of.get(mid, [])
+                if (len(nxt) != 1 or len(graph.tensors[mid].consumers) != 1 or mid in graph.output_tensor_names
+                        or mid in aliased or self.fmt[mid] != 'int8' or cur['out_dtype'] != 'int8'):
+                    break
+                j = nxt[0]
+                cand = self.ops[j]
+                if (j in used or not chainable(cand) or cand['lhs'] != mid or cand['rounding'] != op['rounding']
+                        or j != chain[-1] + 1):
+                    break
+                chain.append(j)
+            if len(chain) < 2:
+                continue
+            layers = [self.ops[j] for j in chain]
+            dims = [layers[0]['K']] + [l['N'] for l in layers]
+            rows = int(np.prod(graph.tensors[layers[0]['lhs']].shape[:-1]))
+            arr = (ctypes.c_int * len(dims))(*dims)
+            if not self.lib.a4c_mlp_i8_single_kernel(len(layers), arr, DTYPE_CODE[layers[-1]['out_dtype']], rows):
+                continue
+            chains.append((chain, layers, dims))
+            used.update(chain)
+        if not chains:
+            return
+        replace, drop = {}, set()
+        for chain, layers, dims in chains:
+            name = '+'.join(l['name'] for l in layers)
+            replace[chain[-1]] = {'kind': 'mlp', 'name': name, 'lhs': layers[0]['lhs'], 'out': layers[-1]['out'],
+                                  'layers': layers, 'dims': dims, 'rounding': layers[0]['rounding']}
+            drop.update(chain[:-1])
+            self.fused.append(name)
+        self.ops = [replace.get(i, op) for i, op in enumerate(self.ops) if i not in drop]
 
     def _fuse_add_layernorm(self) -> None:
         """add (same int8 type, shift 0) -> layer_norm becomes one launch that adds while it loads: the sum is
@@ -407,6 +468,28 @@ class Plan:
                     int(op['transpose_lhs']), int(op['transpose_rhs']), op['shift'], ROUNDING_CODE[op['rounding']],
                     DTYPE_CODE[op['out_dtype']], int(op['lhs_dtype'] == 'uint8'))
             return L.a4c_bmm_i8, args
+        if kind == 'mlp':
+            import ctypes
+
+            layers, dims = op['layers'], op['dims']
+            a, y = self._view(op['lhs']), self._view(op['out'])
+            a_off, M, K, lda = collapse_2d(a, f'{name}: input')
+            y_off, My, N, ldy = collapse_2d(y, f'{name}: output')
+            if M != My or K != dims[0] or N != dims[-1]:
+                raise ValueError(f'{name}: chain input / output views do not match the layer sizes.')
+            n = len(layers)
+            ws = [self.params[l['weight']] for l in layers]
+            bs = [self.params[l['bias']] if l['bias'] else None for l in layers]
+            c_dims = (ctypes.c_int * (n + 1))(*dims)
+            c_w = (ctypes.c_void_p * n)(*[w.data_ptr() for w in ws])
+            c_ldw = (ctypes.c_int64 * n)(*[int(w.shape[1]) for w in ws])
+            c_b = (ctypes.c_void_p * n)(*[b.data_ptr() if b is not None else None for b in bs])
+            c_shift = (ctypes.c_int * n)(*[l['shift'] for l in layers])
+            c_relu = (ctypes.c_int * n)(*[int(l['relu']) for l in layers])
+            self._keepalive.append((c_dims, c_w, c_ldw, c_b, c_shift, c_relu))
+            args = (self.ptr(a, a_off), lda, int(layers[0]['lhs_dtype'] == 'uint8'), n, c_dims, c_w, c_ldw, c_b, c_shift,
+                    c_relu, ROUNDING_CODE[op['rounding']], self.ptr(y, y_off), ldy, DTYPE_CODE[layers[-1]['out_dtype']], M)
+            return L.a4c_mlp_i8, args
         if kind == 'attention':
             args = self._attention_args(op) + (ROUNDING_CODE[op['rounding']], op['sm_mode'], op['B'], op['S'],
                                                op['Dmax'], op['inv_shift'], op['use_clb'], op['exp_kq'])

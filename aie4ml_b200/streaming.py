@@ -38,7 +38,8 @@ class HostPipeline:
         self.plans: List[Plan] = [first]
         for _ in range(depth - 1):
             self.plans.append(Plan(ctx, device=str(first.device), fuse_rowop_add=first.fuse_rowop_add,
-                                   fuse_attention=first.fuse_attention, dense_algo=first.dense_algo,
+                                   fuse_attention=first.fuse_attention, fuse_dense_chain=first.fuse_dense_chain,
+                                   dense_algo=first.dense_algo,
                                    share_params=first))
         self.device = first.device
         graph = first.graph
@@ -51,7 +52,7 @@ class HostPipeline:
                                  'the graph cannot be streamed along its first axis.')
         if use_graph:
             for p in self.plans:
-                if p.graph_exec is None and len(p.launches) > 1:
+                if p.graph_exec is None:
                     p.capture()
         self.s_in = torch.cuda.Stream(self.device)
         self.s_run = torch.cuda.Stream(self.device)

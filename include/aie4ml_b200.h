@@ -53,6 +53,7 @@ extern "C" {
 /* Options for a4c_set_option */
 #define A4C_OPT_ROWOP_PATH 0 /* 0 = auto (bandwidth-oriented row kernels when they apply), 1 = generic kernels only */
 #define A4C_OPT_BMM_PATH 1   /* 0 = auto (tcgen05 batched MatMul when its alignment rules hold), 1 = dp4a kernel only */
+#define A4C_OPT_MLP_PATH 4   /* a4c_mlp_i8: 0 = auto, 1 = one Dense launch per layer, 2 = the single-kernel narrow chain only */
 /* Tuning of the bandwidth-oriented row kernels (results do not depend on either): */
 #define A4C_OPT_ROWOP_CHUNKS_PER_LANE 2 /* 0 = automatic (default), else 1, 2 or 4: 16-element chunks of one row per lane */
 #define A4C_OPT_ROWOP_MIN_STAGES 3      /* 0 = automatic (default), else 2..4: least depth of the per-warp copy ring */
@@ -198,6 +199,14 @@ A4C_API int a4c_add_sat(const void* a, int64_t lda, const void* b, int64_t ldb, 
 A4C_API int a4c_mlp_i8(const void* X, int64_t ldx, int x_unsigned, int n_layers, const int* dims,
                        const int8_t* const* Wt, const int64_t* ldw, const int32_t* const* bias, const int* shift,
                        const int* relu, int rounding, void* Y, int64_t ldy, int out_dtype, int64_t M, void* stream);
+
+/*
+ * 1 when a4c_mlp_i8 would run this chain as ONE kernel that keeps every weight and the activations between
+ * layers in shared memory (automatic choice: no layer wider than 64, M <= 65536, int8 / uint8 output; with
+ * A4C_OPT_MLP_PATH = 2: any chain of up to 8 layers no wider than 256 whose constants fit in shared memory), in
+ * which case it uses no scratch memory at all; 0 otherwise.
+ */
+A4C_API int a4c_mlp_i8_single_kernel(int n_layers, const int* dims, int out_dtype, int64_t M);
 
 /*
  * a4c_mlp_i8 for callers that must not allocate.  (This entry point has no counterpart in the reference: it

@@ -305,9 +305,34 @@ def _chain_oracle(x, layers, tok, out_dtype='int8'):
     return cur
 
 
-@pytest.mark.parametrize('dims', [(16, 64, 32, 32, 5), (512, 1024, 1024, 10), (64, 48), (100, 72, 40, 24)])
-def test_mlp_chain_matches_layer_by_layer_oracle(dims):
+@pytest.fixture(params=['auto', 'per_layer', 'single_kernel'])
+def mlp_path(request):
+    """a4c_mlp_i8 with its automatic choice, forced to one Dense launch per layer, and forced to the
+    single-kernel narrow chain (which answers 'unsupported' for chains it cannot hold)."""
+    from aie4ml_b200 import lib as a4c
+
+    L = a4c.load()
+    assert L.a4c_set_option(a4c.OPT_MLP_PATH, ['auto', 'per_layer', 'single_kernel'].index(request.param)) == 0
+    yield request.param
+    assert L.a4c_set_option(a4c.OPT_MLP_PATH, 0) == 0
+
+
+@pytest.mark.parametrize('dims', [(16, 64, 32, 32, 5), (512, 1024, 1024, 10), (64, 48), (100, 72, 40, 24),
+                                  (256, 256, 200, 16)])
+def test_mlp_chain_matches_layer_by_layer_oracle(dims, mlp_path):
     import gpu_util as G
+    from aie4ml_b200 import lib as a4c
+
+    if mlp_path == 'single_kernel' and max(dims) > 256:
+        x = np.zeros((4, dims[0]), np.int8)
+        with pytest.raises(a4c.A4cError, match='no kernel'):
+            G.mlp_chain(x, _chain_layers(1, dims), tok='floor')
+        return
+    if mlp_path == 'single_kernel':
+        u = np.random.default_rng(1).integers(0, 256, (45, dims[0])).astype(np.uint8)   # unsigned first operand
+        layers = _chain_layers(2, dims)
+        np.testing.assert_array_equal(G.mlp_chain(u, layers, tok='symmetric_inf', out_dtype='uint8'),
+                                      _chain_oracle(u, layers, 'symmetric_inf', out_dtype='uint8'))
 
     rng = np.random.default_rng(sum(dims))
     for M in (1, 300, 2048):
@@ -317,8 +342,9 @@ def test_mlp_chain_matches_layer_by_layer_oracle(dims):
             np.testing.assert_array_equal(G.mlp_chain(x, layers, tok=tok), _chain_oracle(x, layers, tok))
     layers = _chain_layers(3, dims, bias=False)
     x = rng.integers(-128, 128, (77, dims[0])).astype(np.int8)
-    np.testing.assert_array_equal(G.mlp_chain(x, layers, tok='floor', out_dtype='int16'),
-                                  _chain_oracle(x, layers, 'floor', out_dtype='int16'))
+    od = 'int8' if mlp_path == 'single_kernel' else 'int16'   # the single kernel writes 8-bit outputs only
+    np.testing.assert_array_equal(G.mlp_chain(x, layers, tok='floor', out_dtype=od),
+                                  _chain_oracle(x, layers, 'floor', out_dtype=od))
 
 
 def test_empty_inputs_are_no_ops():

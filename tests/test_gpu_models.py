@@ -24,7 +24,11 @@ def _check(builder, inputs, **cfg):
 
 @pytest.mark.parametrize('rounding', ['half_up', 'conv_even'])
 def test_cfg1_mlp(rounding):
-    _check(*W.mlp_cfg1(1024, rounding=rounding))
+    model = _check(*W.mlp_cfg1(1024, rounding=rounding))
+    # the four narrow layers run as one kernel; the three intermediates have no buffer
+    assert [op['kind'] for op in model.plan.ops] == ['mlp'] and len(model.plan.buffers) == 2
+    unfused = _check(*W.mlp_cfg1(1000, rounding=rounding), FusionPolicy={'dense_chain': False})
+    assert [op['kind'] for op in unfused.plan.ops] == ['dense'] * 4
 
 
 @pytest.mark.parametrize('shape', [(1024, 1024, 1024), (512, 4096, 1024), (256, 1024, 4096)])
