@@ -74,6 +74,7 @@ struct TcArgs {
     long long ldy;
     long long M;
     int K, N;
+    int n_full;          // N rounded down to whole 16-byte pieces of an output row
     int num_m_tiles, num_n_tiles;
     int shift, lo, hi;
     uint32_t mask, c0;   // rounding constants (see round_shift_i32_t)
@@ -140,7 +141,20 @@ __device__ __forceinline__ void epilogue_pair(const uint32_t* r, const int32_t* 
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> TMA read
     __syncwarp();
-    if (lane == 0) tma_store_2d(tmap_y, col0, row0, my_stage);
+    // The tensor map ends at the last whole 16-byte piece of a row (n_full columns): a TMA store writes whole
+    // pieces, and the bytes between N and the row pitch may belong to a neighbouring view.
+    if (lane == 0 && col0 < g.n_full) tma_store_2d(tmap_y, col0, row0, my_stage);
+    if (g.N > g.n_full && col0 <= g.n_full && g.n_full < col0 + 64) {
+        // the ragged last piece: each lane copies the valid bytes of its own row
+        const int piece = (g.n_full - col0) >> 4;
+        const uint4 v = *reinterpret_cast<const uint4*>(my_stage + lane * 64 + ((piece ^ sw_w) << 4));
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        const long long row = (long long)row0 + lane;
+        if (row < g.M) {
+            uint8_t* dst = g.Y + row * g.ldy + g.n_full;
+            for (int b = 0; b < g.N - g.n_full; ++b) dst[b] = (uint8_t)(w[b >> 2] >> (8 * (b & 3)));
+        }
+    }
 }
 
 // MODE = rounding token, or -1 when shift == 0 (no rounding step).
@@ -385,7 +399,7 @@ cudaError_t launch_mode(const CUtensorMap& ma, const CUtensorMap& mb, const CUte
 int a4c_dense_tc_supported(const void* A, long long lda, const void* Wt, long long ldw, const void* Y,
                            long long ldy, long long M, int K, int N, int out_dtype) {
     if (out_dtype != A4C_I8 && out_dtype != A4C_U8) return A4C_ERR_UNSUPPORTED;
-    if (N % 16 != 0 || K < 16) return A4C_ERR_UNSUPPORTED;
+    if (K < 16) return A4C_ERR_UNSUPPORTED;   // any N: TMA zero-fills absent weight rows and clips stored columns
     if (lda % 16 || ldw % 16 || ldy % 16) return A4C_ERR_ALIGNMENT;
     if (((uintptr_t)A | (uintptr_t)Wt | (uintptr_t)Y) & 15u) return A4C_ERR_ALIGNMENT;
     if (M > 2147483647LL - BM || lda < K || ldw < K) return A4C_ERR_INVALID_ARG;
@@ -402,10 +416,11 @@ int a4c_launch_dense_tc(const void* A, long long lda, const void* Wt, long long 
     if (sup != A4C_OK) return sup;
     if (M == 0) return A4C_OK;
     CUtensorMap ma, mb, my;
-    if (!make_map(&ma, A, M, K, lda, BM) || !make_map(&mb, Wt, N, K, ldw, BN) || !make_out_map(&my, Y, M, N, ldy))
+    if (!make_map(&ma, A, M, K, lda, BM) || !make_map(&mb, Wt, N, K, ldw, BN) || !make_out_map(&my, Y, M, N >= 16 ? (N / 16) * 16 : 16, ldy))
         return A4C_ERR_CUDA;
     TcArgs g;
     g.bias = bias; g.Y = (uint8_t*)Y; g.ldy = ldy; g.M = M; g.K = K; g.N = N;
+    g.n_full = (N / 16) * 16;
     g.num_m_tiles = (int)((M + BM - 1) / BM);
     g.num_n_tiles = (N + BN - 1) / BN;
     g.shift = shift;
@@ -419,7 +434,9 @@ int a4c_launch_dense_tc(const void* A, long long lda, const void* Wt, long long 
     g.xlo = pre_clamp ? g.lo * (1 << shift) + g.half : 0;
     g.fmul = pre_clamp ? 1.0f / (float)(1 << shift) : 0.0f;
     g.fadd = 12582912.0f - 12582912.0f * g.fmul;
-    g.idesc = make_idesc(BM, BN, a_unsigned != 0);
+    // a single narrow N tile (N <= 256) issues MMAs only as wide as the layer, rounded up to 16 columns
+    const int umma_n = g.num_n_tiles == 1 ? ((N + 15) / 16) * 16 : BN;
+    g.idesc = make_idesc(BM, umma_n, a_unsigned != 0);
     g.status = status_word;
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);

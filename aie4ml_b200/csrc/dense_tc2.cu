@@ -315,6 +315,7 @@ int a4c_launch_dense_tc2(const void* A, long long lda, const void* Wt, long long
                          int out_dtype, int a_unsigned, int* status_word, cudaStream_t stream) {
     const int sup = a4c_dense_tc_supported(A, lda, Wt, ldw, Y, ldy, M, K, N, out_dtype);
     if (sup != A4C_OK) return sup;
+    if (N % 16 != 0) return A4C_ERR_UNSUPPORTED;   // this kernel stores 16-byte pieces of a row directly
     if (M == 0) return A4C_OK;
     CUtensorMap ma, mb;
     if (!make_map(&ma, A, M, K, lda, BM_CTA) || !make_map(&mb, Wt, N, K, ldw, BN_CTA)) return A4C_ERR_CUDA;

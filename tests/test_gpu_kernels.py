@@ -56,6 +56,21 @@ def test_dense_tcgen05_shapes(shape, algo):
     np.testing.assert_array_equal(got, oracle.dense(a, w, bias, shift=10, tok='positive_inf', relu=True))
 
 
+@pytest.mark.parametrize('shape', [(300, 1024, 10), (1000, 64, 5), (260, 128, 200), (129, 48, 270)])
+def test_dense_tcgen05_output_widths_that_are_not_multiples_of_16(shape):
+    """Classifier heads (N = 10, 5) and ragged widths: absent weight rows read as zero, stored columns are clipped,
+    bytes between N and the row pitch stay untouched."""
+    import gpu_util as G
+
+    M, K, N = shape
+    a, w, bias = _rand_dense(sum(shape), M, K, N)
+    for relu, od in ((True, 'int8'), (False, 'uint8')):
+        got = G.dense(a, w, bias, shift=9, tok='positive_inf', relu=relu, out_dtype=od, algo=TC)
+        np.testing.assert_array_equal(got, oracle.dense(a, w, bias, shift=9, tok='positive_inf', relu=relu, out_dtype=od))
+    got = G.dense(a, w, None, shift=6, tok='conv_even', relu=False, algo=TC)
+    np.testing.assert_array_equal(got, oracle.dense(a, w, None, shift=6, tok='conv_even', relu=False))
+
+
 @pytest.mark.parametrize('tok', TOKENS)
 @pytest.mark.parametrize('algo', [TC, TC2])
 def test_dense_tcgen05_every_rounding_mode(tok, algo):
@@ -114,11 +129,14 @@ def test_dense_auto_picks_a_working_kernel_and_rejects_bad_arguments():
     a, w, bias = _rand_dense(41, 256, 256, 256)
     np.testing.assert_array_equal(G.dense(a, w, bias, shift=10, tok='positive_inf', relu=True, algo=0),
                                   oracle.dense(a, w, bias, shift=10, tok='positive_inf', relu=True))
-    a2, w2, b2 = _rand_dense(42, 9, 20, 5)  # N = 5: the tensor-core path cannot take it, auto must still work
+    a2, w2, b2 = _rand_dense(42, 9, 8, 5)  # K = 8: the tensor-core path cannot take it, auto must still work
     np.testing.assert_array_equal(G.dense(a2, w2, b2, shift=7, tok='positive_inf', relu=False, algo=0),
                                   oracle.dense(a2, w2, b2, shift=7, tok='positive_inf', relu=False))
     with pytest.raises(a4c.A4cError):
         G.dense(a2, w2, b2, shift=7, tok='positive_inf', relu=False, algo=TC)
+    a3, w3, b3 = _rand_dense(43, 300, 64, 40)
+    with pytest.raises(a4c.A4cError):   # the CTA-pair kernel stores whole 16-byte pieces: N must be a multiple of 16
+        G.dense(a3, w3, b3, shift=7, tok='positive_inf', relu=False, algo=TC2)
     with pytest.raises(a4c.A4cError):
         G.dense(a, w, bias, shift=40, tok='positive_inf', relu=False)
 

@@ -154,3 +154,18 @@ def test_predict_with_iterations_uses_the_pipeline_and_matches_single_runs():
     want = np.concatenate([next(iter(oracle.run_plan(plan, {'x': x[i]}).values())) for i in range(5)], axis=0)
     np.testing.assert_array_equal(np.asarray(got), want.astype(np.int64))
     assert model._pipeline is not None
+
+
+def test_report_times_every_launch_and_names_the_bound():
+    from aie4ml_b200.report import format_rows, profile_plan
+
+    b, _ = W.encoder_cfg3(8, softmax='exp')
+    model = from_graph(b)
+    model.compile()
+    rows = profile_plan(model.plan, iters=3)
+    assert len(rows) == len(model.plan.launches) and all(r['ms'] > 0 and r['bytes'] > 0 for r in rows)
+    kinds = {r['kind'] for r in rows}
+    assert {'dense', 'attention', 'layer_norm'} <= kinds
+    assert all(r['bound'] == 'hbm' for r in rows if r['kind'] == 'layer_norm')
+    text = format_rows(rows)
+    assert 'sum of launches' in text and 'attention' in text

@@ -162,3 +162,19 @@ def test_shard_rows_partitions_exactly():
         assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
         sizes = [e - s for s, e in spans]
         assert max(sizes) - min(sizes) <= 1
+
+
+def test_plan_dump_reads_back_and_the_oracle_runs_it(tmp_path):
+    from aie4ml_b200.report import load_plan
+    from oracle import oracle
+
+    b, inp = W.mlp_cfg1(8)
+    m = from_graph(b)
+    m.dump(tmp_path)
+    plan = load_plan(tmp_path)
+    live = m.export_plan()
+    assert [op['name'] for op in plan['ops']] == [op['name'] for op in live['ops']]
+    for k, v in live['params'].items():
+        np.testing.assert_array_equal(plan['params'][k], v)
+    (name, want), = oracle.run_plan(live, inp).items()
+    np.testing.assert_array_equal(oracle.run_plan(plan, inp)[name], want)
