@@ -24,6 +24,58 @@ from . import lib as _lib
 from .runtime import Plan
 
 
+def gpu_local_cpus(device_index: int) -> Optional[List[int]]:
+    """CPUs on the NUMA node nearest to a CUDA device (NVML's ideal affinity, read-only query), restricted to the
+    CPUs this process may use; None when NVML or the query is unavailable."""
+    import os
+
+    try:
+        import pynvml
+        import torch
+
+        props = torch.cuda.get_device_properties(device_index)
+        bus = f'{props.pci_domain_id:08x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0'
+        pynvml.nvmlInit()
+        try:
+            handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+            n_cpu = os.cpu_count() or 1
+            words = pynvml.nvmlDeviceGetCpuAffinity(handle, (n_cpu + 63) // 64)
+        finally:
+            pynvml.nvmlShutdown()
+        cpus = [w * 64 + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1]
+        allowed = os.sched_getaffinity(0) if hasattr(os, 'sched_getaffinity') else set(range(n_cpu))
+        cpus = [c for c in cpus if c in allowed]
+        return cpus or None
+    except Exception:
+        return None
+
+
+class near_gpu:
+    """Context manager: run the calling thread on the CPUs nearest to a GPU, so that host buffers allocated and
+    pinned inside the block land in that NUMA node's memory (first touch); the previous affinity is restored on
+    exit.  Copies between such buffers and the GPU do not cross the socket interconnect.  A no-op when the
+    topology cannot be read."""
+
+    def __init__(self, device_index: int):
+        self.cpus = gpu_local_cpus(device_index)
+        self.saved = None
+
+    def __enter__(self):
+        import os
+
+        if self.cpus and hasattr(os, 'sched_setaffinity'):
+            self.saved = os.sched_getaffinity(0)
+            os.sched_setaffinity(0, self.cpus)
+        return self
+
+    def __exit__(self, *exc):
+        import os
+
+        if self.saved is not None:
+            os.sched_setaffinity(0, self.saved)
+        return False
+
+
 class HostPipeline:
     def __init__(self, ctx, depth: int = 3, *, first_plan: Optional[Plan] = None, fuse_rowop_add: bool = True,
                  dense_algo: int = _lib.ALGO_AUTO, use_graph: bool = True):

@@ -270,8 +270,9 @@ def main():
     ap.add_argument('--rounding', default='half_up', choices=['half_up', 'conv_even', 'floor', 'sym_inf'])
     ap.add_argument('--no-cpu', action='store_true', help='skip the CPU baseline leg')
     ap.add_argument('--no-e2e', action='store_true')
-    ap.add_argument('--e2e-chunks', type=int, default=8, help='row chunks of the end-to-end pipeline')
+    ap.add_argument('--e2e-chunks', type=int, default=16, help='row chunks of the end-to-end pipeline')
     ap.add_argument('--no-graph', action='store_true')
+    ap.add_argument('--no-numa', action='store_true', help='do not place the pinned host buffers next to the GPU')
     ap.add_argument('--algo', type=int, default=0, help='dense kernel: 0 auto, 1 simt, 2 tcgen05')
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
@@ -305,8 +306,19 @@ def main():
     in_names, out_names = list(graph.input_tensor_names), list(graph.output_tensor_names)
 
     # pinned host buffers (the e2e leg copies from / to these every step)
-    host_in = {n: torch.from_numpy(np.ascontiguousarray(wl['inputs'][n])).pin_memory() for n in in_names}
-    host_out = {n: torch.empty(plan.tensor_of(n).shape, dtype=plan.tensor_of(n).dtype).pin_memory() for n in out_names}
+    # allocated (first touch) on the NUMA node nearest to this rank's GPU unless --no-numa
+    from aie4ml_b200.streaming import near_gpu
+    import contextlib
+
+    with (contextlib.nullcontext() if args.no_numa else near_gpu(local_rank)) as numa:
+        host_in = {n: torch.empty(wl['inputs'][n].shape, dtype=torch.from_numpy(wl['inputs'][n][:0]).dtype).pin_memory()
+                   for n in in_names}
+        host_out = {n: torch.empty(plan.tensor_of(n).shape, dtype=plan.tensor_of(n).dtype).pin_memory() for n in out_names}
+        for n in in_names:
+            host_in[n].copy_(torch.from_numpy(np.ascontiguousarray(wl['inputs'][n])))
+        for n in out_names:
+            host_out[n].zero_()
+    numa_cpus = len(numa.cpus) if (numa is not None and getattr(numa, 'cpus', None)) else 0
     h2d = sum(t.numel() * t.element_size() for t in host_in.values())
     d2h = sum(t.numel() * t.element_size() for t in host_out.values())
     for n in in_names:
@@ -400,7 +412,8 @@ def main():
         e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / k2
         e2e = {'value': world * wl['units'] / (e2e_ms * 1e-3), 'unit': 'inferences/s', 'h2d_bytes_per_step': h2d,
                'd2h_bytes_per_step': d2h, 'ms_per_step': e2e_ms, 'chunks': chunks,
-               'gpu_launches_per_step': pipe.launches_per_chunk * chunks, 'equals_device_resident_run': same}
+               'gpu_launches_per_step': pipe.launches_per_chunk * chunks, 'equals_device_resident_run': same,
+               'host_buffers_on_gpu_numa_node': numa_cpus > 0}
 
     # ---- roofline of the dominant kernel --------------------------------------------------------
     peaks = measured_peaks()
