@@ -10,6 +10,13 @@ int a4c_launch_gemm_simt(const void* A, long long a_rs, long long a_cs, long lon
                          long long ldc, long long c_bs, long long batch, long long M, int K, int N, int shift,
                          int rounding, int relu, int out_dtype, int a_unsigned, cudaStream_t stream);
 
+// 16-bit operand combinations (gemm_wide.cu): A int8/int16, B int8/int16, 32-bit wrapping or 64-bit accumulator.
+// Strides in elements.
+int a4c_launch_gemm_wide(const void* A, int a_bytes, long long a_rs, long long a_cs, long long a_bs, const void* B,
+                         int b_bytes, long long b_ks, long long b_ns, long long b_bs, const int32_t* bias, void* C,
+                         long long ldc, long long c_bs, long long batch, long long M, int K, int N, int shift,
+                         int rounding, int relu, int out_dtype, int acc_bits, cudaStream_t stream);
+
 // tcgen05 / TMA / TMEM int8 GEMM: A [M,K] K-contiguous, Wt [N,K] K-contiguous.
 // cta_pair = 0: one CTA per 128x256 tile; 1: a CTA pair (cta_group::2) per 256x256 tile.
 int a4c_launch_dense_tc(const void* A, long long lda, const void* Wt, long long ldw, const int32_t* bias,

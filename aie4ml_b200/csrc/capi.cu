@@ -139,6 +139,39 @@ int a4c_bmm_i8(const void* A, int64_t lda, int64_t stride_a, const int8_t* B, in
     return finish();
 }
 
+int a4c_dense_i16(const int16_t* A, int64_t lda, const void* Wt, int w_dtype, int64_t ldw, const int32_t* bias,
+                  void* Y, int64_t ldy, int64_t M, int K, int N, int shift, int rounding, int relu, int out_dtype,
+                  void* stream) {
+    if (A == nullptr || Wt == nullptr || Y == nullptr) return A4C_ERR_INVALID_ARG;
+    if (M < 0 || K <= 0 || N <= 0 || lda < K || ldw < K || ldy < N) return A4C_ERR_INVALID_ARG;
+    if ((w_dtype != A4C_I8 && w_dtype != A4C_I16) || !valid_round(rounding) || !valid_dtype(out_dtype))
+        return A4C_ERR_INVALID_ARG;
+    const int wide = w_dtype == A4C_I16;
+    // W^T [N, ldw]: k stride 1, n stride ldw.  int16 x int8 accumulates in 32 bits, int16 x int16 in 64.
+    const int rc = a4c_launch_gemm_wide(A, 2, lda, 1, 0, Wt, wide ? 2 : 1, 1, ldw, 0, bias, Y, ldy, 0, 1, M, K, N, shift,
+                                        rounding, relu, out_dtype, wide ? 64 : 32, (cudaStream_t)stream);
+    if (rc != A4C_OK) { if (rc == A4C_ERR_CUDA) note(cudaGetLastError()); return rc; }
+    return finish();
+}
+
+int a4c_bmm_i16(const int16_t* A, int64_t lda, int64_t stride_a, const void* B, int b_dtype, int64_t ldb,
+                int64_t stride_b, void* C, int64_t ldc, int64_t stride_c, int64_t batch, int M, int K, int N,
+                int trans_a, int trans_b, int shift, int rounding, int out_dtype, void* stream) {
+    if (A == nullptr || B == nullptr || C == nullptr) return A4C_ERR_INVALID_ARG;
+    if (batch < 0 || M <= 0 || K <= 0 || N <= 0 || ldc < N) return A4C_ERR_INVALID_ARG;
+    if (lda < (trans_a ? M : K) || ldb < (trans_b ? K : N)) return A4C_ERR_INVALID_ARG;
+    if ((b_dtype != A4C_I8 && b_dtype != A4C_I16) || !valid_round(rounding) || !valid_dtype(out_dtype))
+        return A4C_ERR_INVALID_ARG;
+    const int wide = b_dtype == A4C_I16;
+    const long long a_rs = trans_a ? 1 : lda, a_cs = trans_a ? lda : 1;
+    const long long b_ks = trans_b ? 1 : ldb, b_ns = trans_b ? ldb : 1;
+    const int rc = a4c_launch_gemm_wide(A, 2, a_rs, a_cs, stride_a, B, wide ? 2 : 1, b_ks, b_ns, stride_b, nullptr, C, ldc,
+                                        stride_c, batch, M, K, N, shift, rounding, 0, out_dtype, wide ? 64 : 32,
+                                        (cudaStream_t)stream);
+    if (rc != A4C_OK) { if (rc == A4C_ERR_CUDA) note(cudaGetLastError()); return rc; }
+    return finish();
+}
+
 int a4c_attention_i8_supported(const int8_t* q, int64_t ldq, int64_t stride_q, const int8_t* k, int64_t ldk,
                                int64_t stride_k, const int8_t* v, int64_t ldv, int64_t stride_v, const int8_t* out,
                                int64_t ldo, int64_t stride_o, int64_t batch, int sq, int sk, int dh, int qk_shift,

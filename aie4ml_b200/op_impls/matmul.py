@@ -155,7 +155,10 @@ def _bitwidths_supported(node: OpNode) -> bool:
         p = _resolve_numeric(node)
     except (ValueError, RuntimeError):
         return False
-    return p['lhs'].width == 8 and p['rhs'].width == 8 and p['rhs'].signed
+    # the reference's width table (families/matmul/common.py:52); 16-bit operands are signed
+    if (p['lhs'].width, p['rhs'].width) not in ((8, 8), (16, 8), (16, 16)) or not p['rhs'].signed:
+        return False
+    return p['lhs'].width == 8 or p['lhs'].signed
 
 
 def _shift_for(node: OpNode) -> int:
@@ -205,9 +208,10 @@ class CudaDenseVariant(OpImplVariant):
     def validate_config(self, node: OpNode, config: DenseConfig, _device) -> None:
         if config.shift < 0:
             raise ValueError(f'{node.name}: dense accumulator output shift must be non-negative, got {config.shift}.')
-        if config.shift > 31:
-            raise ValueError(f'{node.name}: dense accumulator output shift {config.shift} exceeds the 32-bit '
-                             'accumulator.')
+        limit = 62 if config.accumulator_tag == 'acc64' else 31
+        if config.shift > limit:
+            raise ValueError(f'{node.name}: dense accumulator output shift {config.shift} exceeds the '
+                             f'{limit + 1}-bit accumulator.')
         if config.precision['output'].format not in ('int8', 'uint8', 'int16'):
             raise ValueError(f'{node.name}: dense output must be int8, uint8 or int16, got '
                              f'{config.precision["output"].format!r}.')
@@ -235,9 +239,10 @@ class CudaDenseVariant(OpImplVariant):
         W, b = self._quantize_weight_bias(inst)
         K, N = int(W.shape[0]), int(W.shape[1])
         kp = (K + 15) // 16 * 16
-        packed = np.zeros((N, kp), dtype=np.int8)
-        packed[:, :K] = W.T.astype(np.int8)
-        out = {'weights_kn': W.astype(np.int8), 'packed_weights': packed}
+        wdt = np.int16 if inst.config.precision['rhs'].width > 8 else np.int8
+        packed = np.zeros((N, kp), dtype=wdt)
+        packed[:, :K] = W.T.astype(wdt)
+        out = {'weights_kn': W.astype(wdt), 'packed_weights': packed}
         out['packed_bias'] = None if b is None else np.asarray(b, dtype=np.int32).reshape(-1)
         return out
 
@@ -249,7 +254,8 @@ class CudaDenseVariant(OpImplVariant):
             'weight': f'{node.name}/weights', 'bias': f'{node.name}/bias' if cfg.flags.use_bias else None,
             'K': cfg.n_in, 'N': cfg.n_out, 'shift': int(cfg.shift), 'rounding': cfg.rounding_mode,
             'relu': bool(cfg.flags.use_relu), 'transpose_lhs': bool(cfg.flags.transpose_lhs),
-            'lhs_dtype': cfg.precision['lhs'].format, 'out_dtype': cfg.precision['output'].format,
+            'lhs_dtype': cfg.precision['lhs'].format, 'rhs_dtype': cfg.precision['rhs'].format,
+            'out_dtype': cfg.precision['output'].format, 'acc_bits': 64 if cfg.accumulator_tag == 'acc64' else 32,
         }
 
 
@@ -292,5 +298,6 @@ class CudaMatmulVariant(OpImplVariant):
             'lhs': input_tensor_for_role(node, 'lhs').name, 'rhs': input_tensor_for_role(node, 'rhs').name,
             'out': node.outputs[0].name, 'shift': int(cfg.shift), 'rounding': cfg.rounding_mode,
             'transpose_lhs': bool(cfg.flags.transpose_lhs), 'transpose_rhs': bool(cfg.flags.transpose_rhs),
-            'lhs_dtype': cfg.precision['lhs'].format, 'out_dtype': cfg.precision['output'].format,
+            'lhs_dtype': cfg.precision['lhs'].format, 'rhs_dtype': cfg.precision['rhs'].format,
+            'out_dtype': cfg.precision['output'].format, 'acc_bits': 64 if cfg.accumulator_tag == 'acc64' else 32,
         }

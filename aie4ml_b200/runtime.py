@@ -302,7 +302,8 @@ class Plan:
                     consumer_of.setdefault(op[key], []).append(i)
 
         def chainable(op) -> bool:
-            return op['kind'] == 'dense' and not op['transpose_lhs']
+            return (op['kind'] == 'dense' and not op['transpose_lhs'] and op['lhs_dtype'] in ('int8', 'uint8')
+                    and op.get('rhs_dtype', 'int8') == 'int8')
 
         used, chains = set(), []
         for i, op in enumerate(self.ops):
@@ -445,6 +446,12 @@ class Plan:
                 raise ValueError(f'{name}: shape mismatch between views (M={M}/{My}, K={K}/{op["K"]}, N={N}/{op["N"]}).')
             w = self.params[op['weight']]
             bias = self.params[op['bias']] if op['bias'] else None
+            if op['lhs_dtype'] == 'int16':
+                # 16-bit activations: int16 x int8 (32-bit accumulator) or int16 x int16 (64-bit accumulator)
+                args = (self.ptr(a, a_off), lda, w.data_ptr(), DTYPE_CODE[op['rhs_dtype']], int(w.shape[1]),
+                        bias.data_ptr() if bias is not None else None, self.ptr(y, y_off), ldy, M, K, N, op['shift'],
+                        ROUNDING_CODE[op['rounding']], int(op['relu']), DTYPE_CODE[op['out_dtype']])
+                return L.a4c_dense_i16, args
             args = (self.ptr(a, a_off), lda, w.data_ptr(), int(w.shape[1]), bias.data_ptr() if bias is not None else None,
                     self.ptr(y, y_off), ldy, M, K, N, op['shift'], ROUNDING_CODE[op['rounding']], int(op['relu']),
                     DTYPE_CODE[op['out_dtype']], int(op['lhs_dtype'] == 'uint8'), self.dense_algo)
@@ -464,6 +471,11 @@ class Plan:
                 raise ValueError(f'{name}: batch extents differ (A {ba}, B {bb}, C {bc_}).')
             if bb == 1:
                 sb = 0
+            if op['lhs_dtype'] == 'int16':
+                args = (self.ptr(a, a_off), lda, sa, self.ptr(b, b_off), DTYPE_CODE[op['rhs_dtype']], ldb, sb,
+                        self.ptr(c, c_off), ldc, sc, bc_, M, Ka, N, int(op['transpose_lhs']), int(op['transpose_rhs']),
+                        op['shift'], ROUNDING_CODE[op['rounding']], DTYPE_CODE[op['out_dtype']])
+                return L.a4c_bmm_i16, args
             args = (self.ptr(a, a_off), lda, sa, self.ptr(b, b_off), ldb, sb, self.ptr(c, c_off), ldc, sc, bc_, M, Ka, N,
                     int(op['transpose_lhs']), int(op['transpose_rhs']), op['shift'], ROUNDING_CODE[op['rounding']],
                     DTYPE_CODE[op['out_dtype']], int(op['lhs_dtype'] == 'uint8'))

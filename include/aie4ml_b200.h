@@ -149,6 +149,21 @@ A4C_API int a4c_softmax_i8(const int8_t* x, int64_t ldx, const void* addend, int
                    int exp_kq, int out_dtype, void* stream);
 
 /*
+ * The 16-bit operand combinations of the same two operators (reference width table
+ * src/aie4ml/op_impls/families/matmul/common.py:52: int16 x int8 and int16 x int16; accumulator choice
+ * src/aie4ml/op_impls/utils/precision.py:116-127): A is int16; W / B is int8 (w_dtype 0: 32-bit accumulator that
+ * wraps) or int16 (w_dtype 2: 64-bit accumulator).  Otherwise the contracts of a4c_dense_i8 / a4c_bmm_i8
+ * (dense_bias_relu.cpp:67-166, matmul.cpp:32-118): bias int32, SRS, saturation, ReLU after it; shift <= 31
+ * (acc32) or <= 62 (acc64).  Pitches and strides in ELEMENTS of the respective tensor.
+ */
+A4C_API int a4c_dense_i16(const int16_t* A, int64_t lda, const void* Wt, int w_dtype, int64_t ldw, const int32_t* bias,
+                  void* Y, int64_t ldy, int64_t M, int K, int N, int shift, int rounding, int relu, int out_dtype,
+                  void* stream);
+A4C_API int a4c_bmm_i16(const int16_t* A, int64_t lda, int64_t stride_a, const void* B, int b_dtype, int64_t ldb,
+                int64_t stride_b, void* C, int64_t ldc, int64_t stride_c, int64_t batch, int M, int K, int N,
+                int trans_a, int trans_b, int shift, int rounding, int out_dtype, void* stream);
+
+/*
  * One attention head, fused:  out_b = srs( softmax_u8( srs(Q_b . K_b^T, qk_shift) ) . V_b, pv_shift )  for every
  * batch entry b.  The reference has no single kernel for this: it is the chain of its three kernels
  *   matmul_single::run with TRANSPOSE_B (src/aie4ml/templates/nnet_utils/matmul/matmul.cpp:32-118)

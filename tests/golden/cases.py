@@ -90,7 +90,21 @@ def case_residual_add():
     return b
 
 
+def case_dense_16_bit(w_width: int):
+    """int16 activations against int8 weights (32-bit accumulator) or int16 weights (64-bit accumulator)."""
+    r = _rng(14 + w_width)
+    b = GraphBuilder({'Part': 'cuda_b200'}, name=f'dense16x{w_width}')
+    x = b.input('x', (8, 32), intent(16, 9))
+    w_frac = 6 if w_width == 8 else 12
+    y = b.dense('fc', x, r.uniform(-1.5, 1.5, (32, 16)), intent(w_width, w_frac), intent(16 if w_width == 8 else 8, 5),
+                bias=r.uniform(-2, 2, 16), bias_precision=intent(32, 9 + w_frac), relu=(w_width == 16))
+    b.output(y)
+    return b
+
+
 CASES = {
+    'dense_int16_x_int8': lambda: case_dense_16_bit(8),
+    'dense_int16_x_int16': lambda: case_dense_16_bit(16),
     'mlp_onnx_style': case_mlp_onnx_style,
     'dense_rnd_trn': lambda: case_dense_modes('RND', 'TRN', 'WRAP'),
     'dense_trnzero_rndzero': lambda: case_dense_modes('TRN_ZERO', 'RND_ZERO', 'SAT_SYM'),

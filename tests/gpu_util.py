@@ -174,3 +174,39 @@ def attention(qkv, heads_at, *, qk_shift, pv_shift, tok, mode, B=0, S=0, Dmax=0,
     a4c.check(rc, 'a4c_attention_i8')
     a4c.device_status(stream())
     return out.cpu().numpy()
+
+
+def dense16(a, w_kn, bias, *, shift, tok, relu, out_dtype='int8'):
+    """int16 activations against int8 (32-bit wrapping accumulator) or int16 (64-bit accumulator) weights."""
+    L = a4c.load()
+    M, K = a.shape
+    N = w_kn.shape[1]
+    wide = w_kn.dtype == np.int16
+    esz = np.dtype(NP[out_dtype]).itemsize
+    ldy = (N * esz + 15) // 16 * 16 // esz
+    a_d = dev(np.ascontiguousarray(a.astype(np.int16)))
+    wt = dev(np.ascontiguousarray(w_kn.T))
+    b_d = dev(bias.astype(np.int32)) if bias is not None else None
+    y_d = torch.full((M, ldy), 0x5A if esz == 1 else 0x5A5A, dtype=TD[out_dtype], device='cuda')
+    rc = L.a4c_dense_i16(a_d.data_ptr(), K, wt.data_ptr(), 2 if wide else 0, K, b_d.data_ptr() if b_d is not None else None,
+                         y_d.data_ptr(), ldy, M, K, N, shift, ROUNDING_CODE[tok], int(relu), DTYPE_CODE[out_dtype], stream())
+    a4c.check(rc, 'a4c_dense_i16')
+    y = y_d.cpu().numpy()
+    assert (y[:, N:] == (0x5A if esz == 1 else 0x5A5A)).all(), 'kernel wrote into the row padding'
+    return y[:, :N]
+
+
+def bmm16(a, b, *, shift, tok, trans_a=False, trans_b=False, out_dtype='int16'):
+    L = a4c.load()
+    batch = a.shape[0]
+    M = a.shape[2] if trans_a else a.shape[1]
+    K = a.shape[1] if trans_a else a.shape[2]
+    N = b.shape[1] if trans_b else b.shape[2]
+    wide = b.dtype == np.int16
+    a_d, b_d = dev(np.ascontiguousarray(a.astype(np.int16))), dev(np.ascontiguousarray(b))
+    c_d = torch.zeros((batch, M, N), dtype=TD[out_dtype], device='cuda')
+    rc = L.a4c_bmm_i16(a_d.data_ptr(), a.shape[2], a.shape[1] * a.shape[2], b_d.data_ptr(), 2 if wide else 0, b.shape[2],
+                       b.shape[1] * b.shape[2], c_d.data_ptr(), N, M * N, batch, M, K, N, int(trans_a), int(trans_b), shift,
+                       ROUNDING_CODE[tok], DTYPE_CODE[out_dtype], stream())
+    a4c.check(rc, 'a4c_bmm_i16')
+    return c_d.cpu().numpy()

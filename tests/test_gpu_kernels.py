@@ -436,3 +436,44 @@ def test_fused_attention_other_softmax_parameters_and_rejections():
     assert L.a4c_attention_i8_supported(*misaligned) == a4c.A4C_ERR_ALIGNMENT
     one_zero_shift = list(ok); one_zero_shift[16] = 0
     assert L.a4c_attention_i8_supported(*one_zero_shift) == a4c.A4C_ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize('wide', [False, True])
+@pytest.mark.parametrize('tok', ['positive_inf', 'conv_even', 'floor', 'symmetric_zero'])
+def test_dense_16_bit_operands(wide, tok):
+    """int16 x int8 accumulates in 32 bits and wraps (large K and full-range codes make it wrap), int16 x int16 in 64
+    bits exactly; bias, ReLU and every output type as for int8."""
+    import gpu_util as G
+
+    rng = np.random.default_rng(90 + wide)
+    M, K, N = 77, 300, 45
+    a = rng.integers(-32768, 32768, (M, K)).astype(np.int16)
+    w = (rng.integers(-32768, 32768, (K, N)).astype(np.int16) if wide else rng.integers(-128, 128, (K, N)).astype(np.int8))
+    bias = rng.integers(-(1 << 20), 1 << 20, N).astype(np.int32)
+    acc_bits = 64 if wide else 32
+    for shift, relu, od in ((17 if wide else 9, False, 'int16'), (24 if wide else 16, True, 'int8'), (0, False, 'int16'),
+                            (22 if wide else 14, False, 'uint8')):
+        got = G.dense16(a, w, bias, shift=shift, tok=tok, relu=relu, out_dtype=od)
+        want = oracle.dense(a, w, bias, shift=shift, tok=tok, relu=relu, out_dtype=od, acc_bits=acc_bits)
+        np.testing.assert_array_equal(got, want)
+    got = G.dense16(a, w, None, shift=40 if wide else 12, tok=tok, relu=False, out_dtype='int16')
+    np.testing.assert_array_equal(got, oracle.dense(a, w, None, shift=40 if wide else 12, tok=tok, relu=False,
+                                                    out_dtype='int16', acc_bits=acc_bits))
+
+
+def test_bmm_16_bit_operands_with_transposes():
+    import gpu_util as G
+
+    rng = np.random.default_rng(95)
+    a = rng.integers(-3000, 3000, (4, 33, 70)).astype(np.int16)
+    b16 = rng.integers(-3000, 3000, (4, 70, 20)).astype(np.int16)
+    np.testing.assert_array_equal(G.bmm16(a, b16, shift=14, tok='conv_even'),
+                                  oracle.matmul(a, b16, shift=14, tok='conv_even', out_dtype='int16', acc_bits=64))
+    bt8 = rng.integers(-128, 128, (4, 20, 70)).astype(np.int8)          # stored [N, K]
+    np.testing.assert_array_equal(G.bmm16(a, bt8, shift=9, tok='positive_inf', trans_b=True, out_dtype='int8'),
+                                  oracle.matmul(a, bt8, shift=9, tok='positive_inf', transpose_b=True, out_dtype='int8',
+                                                acc_bits=32))
+    at = rng.integers(-32768, 32768, (2, 70, 33)).astype(np.int16)      # stored [K, M]
+    np.testing.assert_array_equal(G.bmm16(at, b16[:2], shift=20, tok='floor', trans_a=True),
+                                  oracle.matmul(at, b16[:2], shift=20, tok='floor', transpose_a=True, out_dtype='int16',
+                                                acc_bits=64))

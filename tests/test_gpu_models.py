@@ -169,3 +169,24 @@ def test_report_times_every_launch_and_names_the_bound():
     assert all(r['bound'] == 'hbm' for r in rows if r['kind'] == 'layer_norm')
     text = format_rows(rows)
     assert 'sum of launches' in text and 'attention' in text
+
+
+def test_model_with_16_bit_activations_and_weights():
+    """A three-layer network whose first two layers keep 16-bit activations: int16 x int8 (acc32) into int16,
+    int16 x int16 (acc64) into int8, then an ordinary int8 layer; against the oracle on the exported plan."""
+    from aie4ml_b200.frontends.graph import GraphBuilder, intent
+
+    rng = np.random.default_rng(3)
+    b = GraphBuilder({'Part': 'cuda_b200'}, name='wide')
+    x = b.input('x', (50, 48), intent(16, 8))
+    h1 = b.dense('fc0', x, rng.uniform(-1, 1, (48, 40)), intent(8, 6), intent(16, 9), bias=rng.uniform(-1, 1, 40),
+                 bias_precision=intent(32, 14), relu=True)
+    h2 = b.dense('fc1', h1, rng.uniform(-1, 1, (40, 32)), intent(16, 13), intent(8, 4))
+    y = b.dense('fc2', h2, rng.uniform(-1, 1, (32, 10)), intent(8, 6), intent(8, 3))
+    b.output(y)
+    xin = rng.integers(-32768, 32768, (50, 48)).astype(np.int16)
+    model = _check(b, {'x': xin})
+    ops = model.plan.ops
+    assert [op['kind'] for op in ops] == ['dense', 'dense', 'dense']
+    assert (ops[0]['lhs_dtype'], ops[0]['rhs_dtype'], ops[0]['acc_bits'], ops[0]['out_dtype']) == ('int16', 'int8', 32, 'int16')
+    assert (ops[1]['lhs_dtype'], ops[1]['rhs_dtype'], ops[1]['acc_bits']) == ('int16', 'int16', 64)
