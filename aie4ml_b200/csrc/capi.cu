@@ -172,6 +172,40 @@ int a4c_bmm_i16(const int16_t* A, int64_t lda, int64_t stride_a, const void* B, 
     return finish();
 }
 
+int a4c_dense_f(const void* A, int fdtype, int64_t lda, const void* Wt, int64_t ldw, const float* bias, void* Y,
+                int64_t ldy, int64_t M, int K, int N, int relu, void* stream) {
+    if (A == nullptr || Wt == nullptr || Y == nullptr) return A4C_ERR_INVALID_ARG;
+    if (M < 0 || K <= 0 || N <= 0 || lda < K || ldw < K || ldy < N || (fdtype != 0 && fdtype != 1)) return A4C_ERR_INVALID_ARG;
+    const int rc = a4c_launch_gemm_float(A, lda, 1, 0, Wt, 1, ldw, 0, bias, Y, ldy, 0, 1, M, K, N, relu, fdtype == 0,
+                                         (cudaStream_t)stream);
+    if (rc != A4C_OK) { if (rc == A4C_ERR_CUDA) note(cudaGetLastError()); return rc; }
+    return finish();
+}
+
+int a4c_bmm_f(const void* A, int fdtype, int64_t lda, int64_t stride_a, const void* B, int64_t ldb, int64_t stride_b,
+              void* C, int64_t ldc, int64_t stride_c, int64_t batch, int M, int K, int N, int trans_a, int trans_b,
+              void* stream) {
+    if (A == nullptr || B == nullptr || C == nullptr) return A4C_ERR_INVALID_ARG;
+    if (batch < 0 || M <= 0 || K <= 0 || N <= 0 || ldc < N || (fdtype != 0 && fdtype != 1)) return A4C_ERR_INVALID_ARG;
+    if (lda < (trans_a ? M : K) || ldb < (trans_b ? K : N)) return A4C_ERR_INVALID_ARG;
+    const long long a_rs = trans_a ? 1 : lda, a_cs = trans_a ? lda : 1;
+    const long long b_ks = trans_b ? 1 : ldb, b_ns = trans_b ? ldb : 1;
+    const int rc = a4c_launch_gemm_float(A, a_rs, a_cs, stride_a, B, b_ks, b_ns, stride_b, nullptr, C, ldc, stride_c, batch,
+                                         M, K, N, 0, fdtype == 0, (cudaStream_t)stream);
+    if (rc != A4C_OK) { if (rc == A4C_ERR_CUDA) note(cudaGetLastError()); return rc; }
+    return finish();
+}
+
+int a4c_add_f(const void* a, int64_t lda, const void* b, int64_t ldb, void* out, int64_t ldo, int64_t rows, int64_t cols,
+              int fdtype, void* stream) {
+    if (a == nullptr || b == nullptr || out == nullptr || rows < 0 || cols < 0 || (fdtype != 0 && fdtype != 1))
+        return A4C_ERR_INVALID_ARG;
+    if (lda < cols || ldb < cols || ldo < cols) return A4C_ERR_INVALID_ARG;
+    const int rc = a4c_launch_add_float(a, lda, b, ldb, out, ldo, rows, cols, fdtype == 0, (cudaStream_t)stream);
+    if (rc != A4C_OK) { if (rc == A4C_ERR_CUDA) note(cudaGetLastError()); return rc; }
+    return finish();
+}
+
 int a4c_attention_i8_supported(const int8_t* q, int64_t ldq, int64_t stride_q, const int8_t* k, int64_t ldk,
                                int64_t stride_k, const int8_t* v, int64_t ldv, int64_t stride_v, const int8_t* out,
                                int64_t ldo, int64_t stride_o, int64_t batch, int sq, int sk, int dh, int qk_shift,

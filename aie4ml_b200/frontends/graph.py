@@ -64,6 +64,8 @@ def create_context(config: Optional[Dict[str, Any]], project_name: str = 'model'
     if target != 'cuda':
         raise ValueError(f"AIEConfig.Target={target!r} is not available in this backend; use 'cuda'.")
     aie_cfg.setdefault('Iterations', 1)
+    if config.get('ComputeDtype'):   # float-simulation switch, accepted at the top level too
+        aie_cfg.setdefault('ComputeDtype', config['ComputeDtype'])
     aie_cfg['Part'] = device.part
     aie_cfg['Target'] = 'cuda'
     return BackendContext(device=device, aie_config=aie_cfg, project_name=project_name, output_dir=output_dir)

@@ -53,6 +53,11 @@ SIGNATURES = {
                               c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'a4c_bmm_i16': (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int, c_int64, c_int64, c_void_p, c_int64, c_int64,
                             c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    'a4c_dense_f': (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int,
+                            c_int, c_void_p]),
+    'a4c_bmm_f': (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
+                          c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    'a4c_add_f': (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
     'a4c_add_layernorm_i8': (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
                                      c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'a4c_attention_i8_supported': (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64,

@@ -20,7 +20,9 @@ import numpy as np
 from .ir import BackendContext
 from .op_impls.precision import resolve_exact_storage_dtype
 from .passes import DEFAULT_PIPELINE, run_aie_passes
-from .quant_utils import apply_rounding, dequantize, dtype_for_precision, handle_overflow
+from .qtypes import FLOAT_FORMATS
+from .quant_utils import (apply_rounding, dequantize, dtype_for_precision, from_storage_float, handle_overflow,
+                          to_storage_float)
 
 log = logging.getLogger(__name__)
 
@@ -88,29 +90,27 @@ class CudaModel:
                                   for n in list(graph.input_tensor_names) + list(graph.output_tensor_names)):
             # iterations are chunks of one long batch: copy-in, launches and copy-out overlap across them
             pipe = self.pipeline()
-            host_in = {n: torch.from_numpy(np.ascontiguousarray(a.reshape(-1, *a.shape[2:]))).pin_memory()
-                       for n, a in prepared.items()}
+            host_in = {n: _host_tensor(a.reshape(-1, *a.shape[2:])).pin_memory() for n, a in prepared.items()}
             host_out = {}
             for n in outs:
                 t = plan.tensor_of(n)
                 host_out[n] = torch.empty((iterations * t.shape[0], *t.shape[1:]), dtype=t.dtype).pin_memory()
             pipe.run_and_wait(host_in, host_out)
             for n in outs:
-                arr = host_out[n].numpy().astype(np.int64)
+                arr = _host_array(host_out[n])
                 outs[n] = list(arr.reshape(iterations, -1, *arr.shape[1:]))
         else:
             for it in range(iterations):
                 for name, arr in prepared.items():
-                    host = torch.from_numpy(np.ascontiguousarray(arr[it]))
-                    plan.tensor_of(name).copy_(host.to(plan.device, non_blocking=False))
+                    plan.tensor_of(name).copy_(_host_tensor(arr[it]).to(plan.device, non_blocking=False))
                 plan.run()
                 plan.check_status()
                 for name in outs:
-                    outs[name].append(plan.tensor_of(name).cpu().numpy().astype(np.int64))
+                    outs[name].append(_host_array(plan.tensor_of(name).cpu()))
         result: Dict[str, np.ndarray] = {}
         for name, chunks in outs.items():
             arr = np.stack(chunks, axis=0)
-            if dequantize_out:
+            if dequantize_out and self.tensor_dtype(name).format not in FLOAT_FORMATS:
                 arr = dequantize(arr, self.tensor_dtype(name).frac)
             result[name] = arr.reshape(arr.shape[0] * arr.shape[1], *arr.shape[2:]) if arr.ndim >= 2 else arr
         if len(result) == 1:
@@ -153,6 +153,9 @@ class CudaModel:
                 raise ValueError(f'{name}: expected shape {expected}, (1, *{expected}) or ({iterations}, *{expected}); '
                                  f'got {tuple(arr.shape)}')
             dt = self.tensor_dtype(name)
+            if dt.format in FLOAT_FORMATS:
+                prepared[name] = to_storage_float(arr, dt.format)[0]   # float-simulation path: a cast, no codes
+                continue
             np_dt = dtype_for_precision(dt.width, dt.signed)
             if np.issubdtype(arr.dtype, np.integer):
                 prepared[name] = arr.astype(np_dt, copy=False)
@@ -181,6 +184,25 @@ class CudaModel:
         np.savez(out / 'params.npz', **{k.replace('/', '__'): v for k, v in params.items()})
         (out / 'cuda_pipeline.json').write_text(json.dumps(plan, indent=1, default=str))
         return out / 'cuda_pipeline.json'
+
+
+def _host_tensor(arr: np.ndarray):
+    """NumPy storage array -> torch CPU tensor of the plan's dtype (bfloat16 arrives as its 16 bits)."""
+    import torch
+
+    arr = np.ascontiguousarray(arr)
+    if arr.dtype == np.uint16:
+        return torch.from_numpy(arr.view(np.int16)).view(torch.bfloat16)
+    return torch.from_numpy(arr)
+
+
+def _host_array(t) -> np.ndarray:
+    """torch CPU tensor -> int64 codes, or float32 values for the float-simulation path."""
+    import torch
+
+    if t.dtype in (torch.bfloat16, torch.float32):
+        return t.float().numpy()
+    return t.numpy().astype(np.int64)
 
 
 class _ExportShim:

@@ -8,7 +8,7 @@ from .base import (
     get_op_impl_registry,
     register_variant,
 )
-from . import add, layernorm, matmul, softmax  # noqa: F401  (registration side effects)
+from . import add, floatsim, layernorm, matmul, softmax  # noqa: F401  (registration side effects)
 
 __all__ = [
     'FamilyResolver',

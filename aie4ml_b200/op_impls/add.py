@@ -53,8 +53,11 @@ class CudaAddVariant(OpImplVariant):
     variant_id = 'add.cuda.v1'
     op_type = 'add'
 
-    def matches(self, _node: OpNode, device) -> bool:
-        return device.generation in CUDA_GENERATIONS
+    def matches(self, node: OpNode, device) -> bool:
+        from ..qtypes import FloatIntent
+
+        return (device.generation in CUDA_GENERATIONS
+                and not isinstance(input_tensor_for_role(node, 'lhs').precision, FloatIntent))
 
     def resolve(self, node: OpNode, device, directives=None) -> AddConfig:
         lhs = input_tensor_for_role(node, 'lhs')

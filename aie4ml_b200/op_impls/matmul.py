@@ -20,7 +20,7 @@ from typing import Any, Dict, Optional
 import numpy as np
 
 from ..ir import ExecutionEntry, OpNode, input_tensor_for_role, optional_tensor_for_role
-from ..qtypes import AIEDataType
+from ..qtypes import FLOAT_FORMATS, AIEDataType
 from ..quant_utils import quantize_to_int
 from .base import CUDA_GENERATIONS, FamilyResolver, OpImplVariant, family_resolver, register_variant
 from .precision import (
@@ -155,6 +155,8 @@ def _bitwidths_supported(node: OpNode) -> bool:
         p = _resolve_numeric(node)
     except (ValueError, RuntimeError):
         return False
+    if p['lhs'].format in FLOAT_FORMATS or p['rhs'].format in FLOAT_FORMATS:
+        return False   # the float-simulation variants take those
     # the reference's width table (families/matmul/common.py:52); 16-bit operands are signed
     if (p['lhs'].width, p['rhs'].width) not in ((8, 8), (16, 8), (16, 16)) or not p['rhs'].signed:
         return False

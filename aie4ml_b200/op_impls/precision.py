@@ -9,7 +9,7 @@ from __future__ import annotations
 
 from typing import Any, Dict, Optional
 
-from ..qtypes import AIEDataType, QuantIntent, RoundingMode
+from ..qtypes import AIEDataType, FloatIntent, QuantIntent, RoundingMode
 
 ROUNDING_TOKEN_MAP: Dict[RoundingMode, str] = {
     RoundingMode.TRN: 'floor',
@@ -27,6 +27,8 @@ ROUNDING_CODE = {'floor': 0, 'ceil': 1, 'positive_inf': 2, 'negative_inf': 3, 's
                  'symmetric_zero': 5, 'conv_even': 6, 'conv_odd': 7}
 # Codes the C ABI takes for an element type.
 DTYPE_CODE = {'int8': 0, 'uint8': 1, 'int16': 2}
+# Codes the floating-point entry points take.
+FLOAT_CODE = {'bfloat16': 0, 'float32': 1}
 
 
 def to_quant_intent(precision: Any) -> QuantIntent:
@@ -42,6 +44,8 @@ def resolve_exact_storage_dtype(precision: Any, *, namespace: str, layer_name: s
     """Narrowest of 8/16/32-bit storage that holds the intent's width, keeping frac/rounding/saturation."""
     if precision is None:
         raise ValueError(f'{layer_name}: missing precision metadata for {namespace}.')
+    if isinstance(precision, FloatIntent):
+        return AIEDataType(format=precision.format.value, frac=0)
     intent = to_quant_intent(precision)
     width = int(intent.width)
     if width <= 0:

@@ -296,7 +296,33 @@ class PackKernelArtifacts(AIEPass):
         return changed
 
 
-DEFAULT_PIPELINE = (FoldBias, FoldScale, FuseActivationCasts, FoldViewOps, Resolve, PackKernelArtifacts)
+class ForceFloatMode(AIEPass):
+    """Replaces every quantisation intent in the logical IR by a floating-point one when ``AIEConfig.ComputeDtype``
+    is ``'bfloat16'`` or ``'float32'`` / ``'float'`` (reference ``passes/force_float_mode.py:22-46``): the graph
+    is then computed in that type -- Dense / MatMul with float32 accumulation, Add, ReLU -- instead of integers."""
+
+    name = 'force_float_mode'
+    _FORMATS = {'bfloat16': ('BF16', 16), 'float32': ('FP32', 32), 'float': ('FP32', 32)}
+
+    def transform(self, ctx: BackendContext) -> bool:
+        from .qtypes import FloatFormat, FloatIntent, QuantIntent
+
+        fmt = str(ctx.aie_config.get('ComputeDtype') or '').lower()
+        if not fmt:
+            return False
+        if fmt not in self._FORMATS:
+            raise ValueError(f'ComputeDtype={fmt!r} is not recognised. Use one of: {list(self._FORMATS)}')
+        name, width = self._FORMATS[fmt]
+        intent = FloatIntent(width=width, format=FloatFormat[name])
+        changed = False
+        for t in ctx.ir.logical.tensors.values():
+            if isinstance(t.precision, QuantIntent):
+                t.precision = intent
+                changed = True
+        return changed
+
+
+DEFAULT_PIPELINE = (ForceFloatMode, FoldBias, FoldScale, FuseActivationCasts, FoldViewOps, Resolve, PackKernelArtifacts)
 
 
 def run_aie_passes(ctx: BackendContext, passes: Iterable[AIEPass]) -> None:

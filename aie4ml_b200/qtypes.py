@@ -54,8 +54,26 @@ class QuantIntent:
                    saturation=SaturationMode[str(d.get('saturation', 'SAT'))])
 
 
-# format -> (bits, signed, numpy dtype, C type)
+class FloatFormat(Enum):
+    BF16 = 'bfloat16'
+    FP32 = 'float32'
+
+
+@dataclass(frozen=True)
+class FloatIntent:
+    """A tensor computed in floating point (the reference's float-simulation path,
+    ``src/aie4ml/aie_types.py:95-98``; set by ``ForceFloatMode`` from ``AIEConfig.ComputeDtype``)."""
+
+    width: int
+    format: FloatFormat
+
+
+FLOAT_FORMATS = ('bfloat16', 'float32')
+
+# format -> (bits, signed, numpy dtype, C type); bfloat16 is stored as its 16 bits
 _FORMATS = {
+    'bfloat16': (16, True, np.uint16, 'uint16_t'),
+    'float32': (32, True, np.float32, 'float'),
     'int8': (8, True, np.int8, 'int8_t'),
     'uint8': (8, False, np.uint8, 'uint8_t'),
     'int16': (16, True, np.int16, 'int16_t'),

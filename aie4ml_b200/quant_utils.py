@@ -75,3 +75,32 @@ def dequantize(codes, frac: int):
     """integer codes -> float64 (reference: ``src/aie4ml/simulation.py:248-257``)."""
     frac = max(0, int(frac))
     return np.asarray(codes, dtype=np.float64) / float(1 << frac)
+
+
+# ---- floating-point storage (the float-simulation path) ---------------------------------------
+def to_bf16_bits(values) -> np.ndarray:
+    """float -> bfloat16 bit patterns (uint16), round to nearest even (NaN payloads are not preserved)."""
+    f = np.ascontiguousarray(np.asarray(values, dtype=np.float32))
+    u = f.view(np.uint32).astype(np.uint64)
+    rounded = (u + 0x7FFF + ((u >> 16) & 1)) >> 16
+    return rounded.astype(np.uint16).reshape(f.shape)
+
+
+def from_bf16_bits(bits) -> np.ndarray:
+    b = np.ascontiguousarray(np.asarray(bits, dtype=np.uint16))
+    return (b.astype(np.uint32) << 16).view(np.float32).reshape(b.shape)
+
+
+def to_storage_float(values, fmt: str):
+    """-> (array in storage form, float32 values that storage holds) for 'bfloat16' or 'float32'."""
+    if fmt == 'bfloat16':
+        bits = to_bf16_bits(values)
+        return bits, from_bf16_bits(bits)
+    if fmt == 'float32':
+        f = np.ascontiguousarray(np.asarray(values, dtype=np.float32))
+        return f, f
+    raise ValueError(f'not a floating-point storage format: {fmt!r}')
+
+
+def from_storage_float(stored, fmt: str) -> np.ndarray:
+    return from_bf16_bits(stored) if fmt == 'bfloat16' else np.asarray(stored, dtype=np.float32)

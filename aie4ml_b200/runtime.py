@@ -20,10 +20,11 @@ import numpy as np
 
 from . import lib as _lib
 from .ir import BackendContext, input_tensor_for_role
-from .op_impls.precision import DTYPE_CODE, ROUNDING_CODE, resolve_exact_storage_dtype
+from .op_impls.precision import DTYPE_CODE, FLOAT_CODE, ROUNDING_CODE, resolve_exact_storage_dtype
 
-ESZ = {'int8': 1, 'uint8': 1, 'int16': 2, 'int32': 4}
-NP_DT = {'int8': np.int8, 'uint8': np.uint8, 'int16': np.int16, 'int32': np.int32}
+ESZ = {'int8': 1, 'uint8': 1, 'int16': 2, 'int32': 4, 'bfloat16': 2, 'float32': 4}
+NP_DT = {'int8': np.int8, 'uint8': np.uint8, 'int16': np.int16, 'int32': np.int32, 'bfloat16': np.uint16,
+         'float32': np.float32}
 
 
 def _torch():
@@ -131,7 +132,7 @@ class Plan:
             if t.is_parameter:
                 continue
             self.fmt[name] = resolve_exact_storage_dtype(t.precision, namespace='tensor', layer_name=name).format
-            if self.fmt[name] not in ('int8', 'uint8', 'int16'):
+            if self.fmt[name] not in ('int8', 'uint8', 'int16', 'bfloat16', 'float32'):
                 raise NotImplementedError(f'{name}: activation format {self.fmt[name]!r} has no kernel.')
 
         # 2. aliases introduced by view placeholders
@@ -160,14 +161,14 @@ class Plan:
             if inst is None:
                 raise RuntimeError(f'{node.name}: not resolved; run the pass pipeline first.')
             op = inst.variant.plan_op(inst)
-            if op['kind'] == 'dense':
+            if op['kind'] in ('dense', 'dense_f'):
                 self.params_np[op['weight']] = inst.artifacts['packed_weights']
                 if op['bias']:
                     self.params_np[op['bias']] = inst.artifacts['packed_bias']
             elif op['kind'] == 'layer_norm':
                 self.params_np[op['gamma']] = inst.artifacts['packed_gamma']
                 self.params_np[op['beta']] = inst.artifacts['packed_beta']
-            elif op['kind'] == 'matmul':
+            elif op['kind'] in ('matmul', 'matmul_f'):
                 if input_tensor_for_role(node, 'rhs').is_parameter:
                     raise NotImplementedError(f'{node.name}: a constant RHS of rank > 2 has no kernel; '
                                               'express it as dense.')
@@ -246,7 +247,8 @@ class Plan:
         """A torch tensor (strided) over the view's storage, typed by the tensor's format."""
         torch = _torch()
         v = self._view(name)
-        dt = {'int8': torch.int8, 'uint8': torch.uint8, 'int16': torch.int16}[v.fmt]
+        dt = {'int8': torch.int8, 'uint8': torch.uint8, 'int16': torch.int16, 'bfloat16': torch.bfloat16,
+              'float32': torch.float32}[v.fmt]
         base = self.buffers[v.root].view(dt)
         return base.as_strided(v.shape, v.strides, v.offset)
 
@@ -480,6 +482,41 @@ class Plan:
                     int(op['transpose_lhs']), int(op['transpose_rhs']), op['shift'], ROUNDING_CODE[op['rounding']],
                     DTYPE_CODE[op['out_dtype']], int(op['lhs_dtype'] == 'uint8'))
             return L.a4c_bmm_i8, args
+        if kind == 'dense_f':
+            a, y = self._view(op['lhs']), self._view(op['out'])
+            a_off, M, K, lda = collapse_2d(a, f'{name}: input')
+            y_off, My, N, ldy = collapse_2d(y, f'{name}: output')
+            if (M, K, N) != (My, op['K'], op['N']):
+                raise ValueError(f'{name}: shape mismatch between views (M={M}/{My}, K={K}/{op["K"]}, N={N}/{op["N"]}).')
+            w = self.params[op['weight']]
+            bias = self.params[op['bias']] if op['bias'] else None
+            args = (self.ptr(a, a_off), FLOAT_CODE[op['dtype']], lda, w.data_ptr(), int(w.shape[1]),
+                    bias.data_ptr() if bias is not None else None, self.ptr(y, y_off), ldy, M, K, N, int(op['relu']))
+            return L.a4c_dense_f, args
+        if kind == 'matmul_f':
+            a, b, c = self._view(op['lhs']), self._view(op['rhs']), self._view(op['out'])
+            a_off, ba, ar, ac, lda, sa = collapse_batched(a, f'{name}: lhs')
+            b_off, bb, br, bc, ldb, sb = collapse_batched(b, f'{name}: rhs')
+            c_off, bc_, M, N, ldc, sc = collapse_batched(c, f'{name}: output')
+            Ka = ar if op['transpose_lhs'] else ac
+            Ma = ac if op['transpose_lhs'] else ar
+            Kb = bc if op['transpose_rhs'] else br
+            Nb = br if op['transpose_rhs'] else bc
+            if Ma != M or Nb != N or Ka != Kb or ba != bc_ or bb not in (1, bc_):
+                raise ValueError(f'{name}: operand shapes do not contract (A {a.shape}, B {b.shape}, C {c.shape}).')
+            args = (self.ptr(a, a_off), FLOAT_CODE[op['dtype']], lda, sa, self.ptr(b, b_off), ldb, 0 if bb == 1 else sb,
+                    self.ptr(c, c_off), ldc, sc, bc_, M, Ka, N, int(op['transpose_lhs']), int(op['transpose_rhs']))
+            return L.a4c_bmm_f, args
+        if kind == 'add_f':
+            x, o, y = self._view(op['lhs']), self._view(op['rhs']), self._view(op['out'])
+            x_off, rows, cols, ldx = collapse_2d(x, f'{name}: lhs')
+            o_off, ro, co, ldo_ = collapse_2d(o, f'{name}: rhs')
+            y_off, ry, cy, ldy = collapse_2d(y, f'{name}: output')
+            if (rows, cols) != (ro, co) or (rows, cols) != (ry, cy):
+                raise ValueError(f'{name}: operand shapes differ.')
+            args = (self.ptr(x, x_off), ldx, self.ptr(o, o_off), ldo_, self.ptr(y, y_off), ldy, rows, cols,
+                    FLOAT_CODE[op['dtype']])
+            return L.a4c_add_f, args
         if kind == 'mlp':
             import ctypes
 
@@ -588,7 +625,7 @@ class Plan:
                 continue
             inst = self.ctx.ir.execution.get(node.name)
             op = inst.variant.plan_op(inst)
-            if op['kind'] == 'dense':
+            if op['kind'] in ('dense', 'dense_f'):
                 params[op['weight']] = inst.artifacts['weights_kn']
                 if op['bias']:
                     params[op['bias']] = inst.artifacts['packed_bias']

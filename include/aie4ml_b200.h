@@ -164,6 +164,22 @@ A4C_API int a4c_bmm_i16(const int16_t* A, int64_t lda, int64_t stride_a, const v
                 int trans_a, int trans_b, int shift, int rounding, int out_dtype, void* stream);
 
 /*
+ * Float-simulation path (reference AIEConfig.ComputeDtype = 'bfloat16' | 'float32',
+ * src/aie4ml/passes/force_float_mode.py:22-46; float contract of the matmul family
+ * src/aie4ml/op_impls/families/matmul/resolver.py:110-127): the same Dense / MatMul / Add operators computed in
+ * floating point.  fdtype 0 = bfloat16 (tensors hold the 16 bits), 1 = float32; accumulation in float32, bias
+ * float32, optional ReLU, results rounded to nearest-even into the storage type.  Pitches / strides in elements.
+ * Held to the reference's tolerances (tests/test_float_sim.py:87-93), not to bit equality.
+ */
+A4C_API int a4c_dense_f(const void* A, int fdtype, int64_t lda, const void* Wt, int64_t ldw, const float* bias, void* Y,
+                int64_t ldy, int64_t M, int K, int N, int relu, void* stream);
+A4C_API int a4c_bmm_f(const void* A, int fdtype, int64_t lda, int64_t stride_a, const void* B, int64_t ldb,
+              int64_t stride_b, void* C, int64_t ldc, int64_t stride_c, int64_t batch, int M, int K, int N, int trans_a,
+              int trans_b, void* stream);
+A4C_API int a4c_add_f(const void* a, int64_t lda, const void* b, int64_t ldb, void* out, int64_t ldo, int64_t rows,
+              int64_t cols, int fdtype, void* stream);
+
+/*
  * One attention head, fused:  out_b = srs( softmax_u8( srs(Q_b . K_b^T, qk_shift) ) . V_b, pv_shift )  for every
  * batch entry b.  The reference has no single kernel for this: it is the chain of its three kernels
  *   matmul_single::run with TRANSPOSE_B (src/aie4ml/templates/nnet_utils/matmul/matmul.cpp:32-118)

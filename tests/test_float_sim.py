@@ -1,0 +1,99 @@
+"""The float-simulation path (AIEConfig.ComputeDtype): lowering on CPU, execution on the GPU within the
+tolerances the reference states for this path (reference tests/test_float_sim.py:87-93:
+bfloat16 rtol 1e-2 / atol 5e-2, float32 rtol 1e-3 / atol 1e-3, against a float model of the same network)."""
+
+import numpy as np
+import pytest
+
+from aie4ml_b200 import from_graph
+from aie4ml_b200.frontends.graph import GraphBuilder, intent
+from aie4ml_b200.quant_utils import from_bf16_bits, to_bf16_bits
+from oracle import oracle
+
+TOL = {'bfloat16': dict(rtol=1e-2, atol=5e-2), 'float32': dict(rtol=1e-3, atol=1e-3), 'float': dict(rtol=1e-3, atol=1e-3)}
+
+
+def _mlp(compute_dtype, batch=4, n_in=32, n_h=32, n_out=16, seed=0):
+    """The network of the reference's float test: Dense + ReLU + Dense, 16-bit quantisers, small normal weights."""
+    rng = np.random.default_rng(seed)
+    w0, b0 = rng.normal(0, 0.05, (n_in, n_h)), rng.normal(0, 0.05, n_h)
+    w1, b1 = rng.normal(0, 0.05, (n_h, n_out)), rng.normal(0, 0.05, n_out)
+    b = GraphBuilder({'Part': 'cuda_b200', 'AIEConfig': {'ComputeDtype': compute_dtype}}, name=f'mlp_{compute_dtype}')
+    x = b.input('x', (batch, n_in), intent(16, 13))
+    h = b.dense('dense0', x, w0, intent(16, 13), intent(16, 13), bias=b0, bias_precision=intent(16, 13), relu=True)
+    y = b.dense('dense1', h, w1, intent(16, 13), intent(16, 13), bias=b1, bias_precision=intent(16, 13))
+    b.output(y)
+    return b, (w0, b0, w1, b1)
+
+
+def _float_model(x, w0, b0, w1, b1):
+    return np.maximum(x @ w0 + b0, 0.0) @ w1 + b1
+
+
+@pytest.mark.parametrize('compute_dtype', ['bfloat16', 'float32', 'float'])
+def test_force_float_mode_relabels_every_tensor_and_selects_the_float_variants(compute_dtype):
+    b, _ = _mlp(compute_dtype)
+    plan = from_graph(b).export_plan()
+    fmt = 'bfloat16' if compute_dtype == 'bfloat16' else 'float32'
+    assert [(op['kind'], op['dtype'], op['relu']) for op in plan['ops']] == [('dense_f', fmt, True), ('dense_f', fmt, False)]
+    assert set(plan['formats'].values()) == {fmt}
+    assert all(v.dtype == np.float32 for v in plan['params'].values())
+
+
+def test_unknown_compute_dtype_is_rejected_and_integer_graphs_are_untouched():
+    b, _ = _mlp('float16')
+    with pytest.raises(ValueError, match="ComputeDtype='float16' is not recognised"):
+        from_graph(b).export_plan()
+    b2 = GraphBuilder({'Part': 'cuda_b200'}, name='int')
+    x = b2.input('x', (4, 16), intent(8, 4))
+    b2.output(b2.dense('fc', x, np.ones((16, 16)) / 8.0, intent(8, 6), intent(8, 3)))
+    assert from_graph(b2).export_plan()['ops'][0]['kind'] == 'dense'
+
+
+def test_bfloat16_bits_round_to_nearest_even():
+    f = np.array([1.0, 1.00390625, 1.01171875, -2.5, 0.1, 3.0e38, 0.0], dtype=np.float32)   # 1 + 2^-8 is a tie
+    bits = to_bf16_bits(f)
+    back = from_bf16_bits(bits)
+    assert back[0] == 1.0 and back[1] == 1.0 and back[2] == 1.015625 and back[3] == -2.5
+    np.testing.assert_allclose(back, f, rtol=2 ** -8)
+    np.testing.assert_array_equal(oracle.round_float(f, 'bfloat16'), back)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('compute_dtype', ['bfloat16', 'float32'])
+def test_float_mlp_matches_the_float_model_within_the_reference_tolerances(compute_dtype):
+    b, consts = _mlp(compute_dtype)
+    model = from_graph(b)
+    model.compile()
+    x = np.random.default_rng(42).uniform(-2.0, 2.0, (4, 32)).astype(np.float32)
+    got = np.asarray(model.predict(x))
+    assert got.dtype == np.float32 and got.shape == (4, 16)
+    np.testing.assert_allclose(got, _float_model(x.astype(np.float64), *consts), **TOL[compute_dtype])
+    # and against the oracle evaluating the exported plan with each tensor's storage rounding
+    (_, want), = oracle.run_plan(model.export_plan(), {'x': oracle.round_float(x, model.plan.fmt['x'])}).items()
+    np.testing.assert_allclose(got, want, **TOL[compute_dtype])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('compute_dtype', ['bfloat16', 'float32'])
+def test_float_matmul_add_and_larger_shapes(compute_dtype):
+    rng = np.random.default_rng(7)
+    b = GraphBuilder({'Part': 'cuda_b200', 'ComputeDtype': compute_dtype}, name='f2')
+    q = b.input('q', (3, 70, 48), intent(16, 12))
+    k = b.input('k', (3, 90, 48), intent(16, 12))
+    kt = b.transpose('kt', k, [0, 2, 1])
+    s = b.matmul('qk', q, kt, intent(16, 10))
+    w = rng.normal(0, 0.1, (90, 40))
+    d = b.dense('proj', s, w, intent(16, 12), intent(16, 10))
+    d2 = b.dense('proj2', s, w * 0.5, intent(16, 12), intent(16, 10), relu=True)
+    b.output(b.add('sum', d, d2, intent(16, 10)))
+    model = from_graph(b)
+    model.context.aie_config['Iterations'] = 2          # the streaming path with floating-point buffers
+    model.compile()
+    qa = rng.uniform(-1, 1, (2, 3, 70, 48)).astype(np.float32)
+    ka = rng.uniform(-1, 1, (2, 3, 90, 48)).astype(np.float32)
+    got = np.asarray(model.predict({'q': qa, 'k': ka}))
+    s_ref = qa.astype(np.float64) @ np.swapaxes(ka.astype(np.float64), -1, -2)
+    want = (s_ref @ w + np.maximum(s_ref @ (w * 0.5), 0.0)).reshape(got.shape)
+    tol = dict(rtol=2e-2, atol=2e-1) if compute_dtype == 'bfloat16' else TOL['float32']   # three bf16 roundings in a row
+    np.testing.assert_allclose(got, want, **tol)
