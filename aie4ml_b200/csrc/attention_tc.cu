@@ -269,6 +269,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         const int numer = 255 << g.inv_shift;
         const float numer_f = (float)numer;
         const float out_mul = __int_as_float((127 - (g.inv_shift + 85)) << 23);  // 2^-(inv_shift + 85)
+        const bool clb = g.use_clb && g.mode == 0;
         bool ok = true;
         for (int n = grp; ok && n < n_local; n += GROUPS) {
             const long long item = first + (long long)n * gridDim.x;
@@ -314,7 +315,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             const int sum = __float2int_rn((fs0 + fs1) * TWO_P64);
             const int s = sum > 0 ? sum : 1;
             int inv;
-            if (g.use_clb && g.mode == 0) {
+            if (clb) {
                 const int k = 31 - __clz(s);
                 inv = g.inv_shift - k >= 0 ? (255 << (g.inv_shift - k)) : (255 >> (k - g.inv_shift));
             } else {
@@ -335,10 +336,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 for (int q = 0; q < 4; ++q) {
                     const int i = c * 16 + q * 4;
                     // floor(score * inv / 2^shift) in the low bits of a subnormal (scores are non-negative)
-                    const int o0 = min(__float_as_int(__fmaf_rd(e[i + 0], invs, 0.0f)), 255);
-                    const int o1 = min(__float_as_int(__fmaf_rd(e[i + 1], invs, 0.0f)), 255);
-                    const int o2 = min(__float_as_int(__fmaf_rd(e[i + 2], invs, 0.0f)), 255);
-                    const int o3 = min(__float_as_int(__fmaf_rd(e[i + 3], invs, 0.0f)), 255);
+                    // with inv = floor(255 * 2^shift / sum) a score <= sum cannot exceed 255; only the power-of-two
+                    // reciprocal (use_clb) needs the saturation
+                    int o0 = __float_as_int(__fmaf_rd(e[i + 0], invs, 0.0f));
+                    int o1 = __float_as_int(__fmaf_rd(e[i + 1], invs, 0.0f));
+                    int o2 = __float_as_int(__fmaf_rd(e[i + 2], invs, 0.0f));
+                    int o3 = __float_as_int(__fmaf_rd(e[i + 3], invs, 0.0f));
+                    if (clb) { o0 = min(o0, 255); o1 = min(o1, 255); o2 = min(o2, 255); o3 = min(o3, 255); }
                     w[q] = pack4_i8(o0, o1, o2, o3);
                 }
                 // K-major, 128-byte swizzle: 16-byte piece c of row r sits at piece c ^ (r & 7)

@@ -426,7 +426,7 @@ __device__ __forceinline__ float lut_at(uint32_t lut_lane, uint32_t dw) {
     return lds32f((sh & 0x7F80u) + lut_lane);
 }
 
-template <int NCH, bool HAS_ADD>
+template <int NCH, bool HAS_ADD, bool CLB>
 __global__ void __launch_bounds__(kThreads) softmax_fast_kernel(SmFastArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     // layout: score table [256][32] floats (32 KB) | barriers | ring
@@ -543,7 +543,7 @@ __global__ void __launch_bounds__(kThreads) softmax_fast_kernel(SmFastArgs a) {
         const int sum = __reduce_add_sync(group_mask, __float2int_rn((fs0 + fs1) * TWO_P64));
         const int s = sum > 0 ? sum : 1;
         int inv;
-        if (a.use_clb && a.mode == 0) {
+        if (CLB) {
             const int k = 31 - __clz(s);
             inv = a.inv_shift - k >= 0 ? (255 << (a.inv_shift - k)) : (255 >> (k - a.inv_shift));
         } else {
@@ -569,10 +569,13 @@ __global__ void __launch_bounds__(kThreads) softmax_fast_kernel(SmFastArgs a) {
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
                 // floor(score * inv / 2^shift) lands in the low bits of a subnormal (scores are non-negative)
-                const int o0 = min(__float_as_int(__fmaf_rd(e[j][w * 4 + 0], invs, 0.0f)), 255);
-                const int o1 = min(__float_as_int(__fmaf_rd(e[j][w * 4 + 1], invs, 0.0f)), 255);
-                const int o2 = min(__float_as_int(__fmaf_rd(e[j][w * 4 + 2], invs, 0.0f)), 255);
-                const int o3 = min(__float_as_int(__fmaf_rd(e[j][w * 4 + 3], invs, 0.0f)), 255);
+                // With inv = floor(255 * 2^shift / sum) (or its clamp to 32767) a score <= sum gives a result <= 255 by
+                // itself; only the power-of-two reciprocal (use_clb) can exceed it and needs the saturation.
+                int o0 = __float_as_int(__fmaf_rd(e[j][w * 4 + 0], invs, 0.0f));
+                int o1 = __float_as_int(__fmaf_rd(e[j][w * 4 + 1], invs, 0.0f));
+                int o2 = __float_as_int(__fmaf_rd(e[j][w * 4 + 2], invs, 0.0f));
+                int o3 = __float_as_int(__fmaf_rd(e[j][w * 4 + 3], invs, 0.0f));
+                if (CLB) { o0 = min(o0, 255); o1 = min(o1, 255); o2 = min(o2, 255); o3 = min(o3, 255); }
                 uint32_t p01 = prmt((uint32_t)o0, (uint32_t)o1, 0x5410);
                 uint32_t p23 = prmt((uint32_t)o2, (uint32_t)o3, 0x5410);
                 if (HAS_ADD) {
@@ -713,10 +716,17 @@ int a4c_launch_softmax_fast(const int8_t* x, long long ldx, const void* addend, 
     plan_launch(256 * 32 * 4, slot, n_items, &a.stages, &smem, &grid);
 #define SM_LAUNCH(NCH_, ADD_)                                                                                      \
     do {                                                                                                           \
-        cudaFuncSetAttribute(softmax_fast_kernel<NCH_, ADD_>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
-                             (int)smem);                                                                           \
-        softmax_fast_kernel<NCH_, ADD_><<<grid, kThreads, smem, stream>>>(a);                                      \
+        if (clb) {                                                                                                 \
+            cudaFuncSetAttribute(softmax_fast_kernel<NCH_, ADD_, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                 (int)smem);                                                                       \
+            softmax_fast_kernel<NCH_, ADD_, true><<<grid, kThreads, smem, stream>>>(a);                            \
+        } else {                                                                                                   \
+            cudaFuncSetAttribute(softmax_fast_kernel<NCH_, ADD_, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                 (int)smem);                                                                       \
+            softmax_fast_kernel<NCH_, ADD_, false><<<grid, kThreads, smem, stream>>>(a);                           \
+        }                                                                                                          \
     } while (0)
+    const bool clb = use_clb && mode == 0;   // the power-of-two reciprocal of the HCCS kernel
     if (nch == 1) { if (addend) SM_LAUNCH(1, true); else SM_LAUNCH(1, false); }
     else if (nch == 2) { if (addend) SM_LAUNCH(2, true); else SM_LAUNCH(2, false); }
     else { if (addend) SM_LAUNCH(4, true); else SM_LAUNCH(4, false); }
