@@ -75,6 +75,7 @@ struct TcArgs {
     long long M;
     int K, N;
     int n_full;          // N rounded down to whole 16-byte pieces of an output row
+    int b_box_rows;      // weight rows one TMA box brings in: 256, or N rounded up to 16 for a single narrow tile
     int num_m_tiles, num_n_tiles;
     int shift, lo, hi;
     uint32_t mask, c0;   // rounding constants (see round_shift_i32_t)
@@ -202,7 +203,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     ok = mbar_wait(&tail->empty[stage], phase ^ 1u, abort_flag, g.status, 101);
                     if (!ok) break;
                     uint8_t* sa = smem + (size_t)stage * STAGE_BYTES;
-                    mbar_arrive_expect_tx(&tail->full[stage], STAGE_BYTES);
+                    mbar_arrive_expect_tx(&tail->full[stage], (uint32_t)(A_BYTES + g.b_box_rows * BK));
                     tma_load_2d(sa, &tmap_a, &tail->full[stage], kb * BK, m0);
                     tma_load_2d(sa + A_BYTES, &tmap_b, &tail->full[stage], kb * BK, n0);
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -416,7 +417,9 @@ int a4c_launch_dense_tc(const void* A, long long lda, const void* Wt, long long 
     if (sup != A4C_OK) return sup;
     if (M == 0) return A4C_OK;
     CUtensorMap ma, mb, my;
-    if (!make_map(&ma, A, M, K, lda, BM) || !make_map(&mb, Wt, N, K, ldw, BN) || !make_out_map(&my, Y, M, N >= 16 ? (N / 16) * 16 : 16, ldy))
+    const int w_box_rows = (N + BN - 1) / BN == 1 ? ((N + 15) / 16) * 16 : BN;
+    if (!make_map(&ma, A, M, K, lda, BM) || !make_map(&mb, Wt, N, K, ldw, w_box_rows) ||
+        !make_out_map(&my, Y, M, N >= 16 ? (N / 16) * 16 : 16, ldy))
         return A4C_ERR_CUDA;
     TcArgs g;
     g.bias = bias; g.Y = (uint8_t*)Y; g.ldy = ldy; g.M = M; g.K = K; g.N = N;
@@ -434,8 +437,10 @@ int a4c_launch_dense_tc(const void* A, long long lda, const void* Wt, long long 
     g.xlo = pre_clamp ? g.lo * (1 << shift) + g.half : 0;
     g.fmul = pre_clamp ? 1.0f / (float)(1 << shift) : 0.0f;
     g.fadd = 12582912.0f - 12582912.0f * g.fmul;
-    // a single narrow N tile (N <= 256) issues MMAs only as wide as the layer, rounded up to 16 columns
+    // a single narrow N tile (N <= 256) issues MMAs only as wide as the layer, rounded up to 16 columns, and its
+    // weight box is that many rows instead of 256 (absent rows would be zero-filled into shared memory for nothing)
     const int umma_n = g.num_n_tiles == 1 ? ((N + 15) / 16) * 16 : BN;
+    g.b_box_rows = umma_n;
     g.idesc = make_idesc(BM, umma_n, a_unsigned != 0);
     g.status = status_word;
     int dev = 0, sms = 148;
