@@ -4,8 +4,8 @@
 // SRS with the op's rounding token, the A operand possibly uint8 (a softmax output), the B operand stored
 // either [N, K] (a folded Transpose: TRANSPOSE_B, matmul.cpp:68-72) or [K, N].
 //
-// Same warp-specialised structure as the Dense kernel (TMA producer / MMA issuer / four epilogue warps, a
-// 4-stage shared-memory ring, two TMEM accumulators), with three differences:
+// Same main loop as the Dense kernel (TMA producer / MMA issuer, a 4-stage shared-memory ring, two TMEM
+// accumulators) with a simpler epilogue (four warps, lane = row, 16-byte global stores), and three differences:
 //   * operands come through 3-D tensor maps {inner, rows, batch}, so a tile never reads rows of the next
 //     batch entry: rows past the matrix edge are zero-filled by TMA;
 //   * B stored [N, K] is a K-major operand exactly like Dense weights; B stored [K, N] is an MN-major operand:

@@ -5,14 +5,16 @@
 // which is dense_single::run of aie4ml (dense_bias_relu.cpp:67-166): int32 accumulation, bias as
 // the accumulator's initial value, SRS (rounding shift + saturation), ReLU after the saturation.
 //
-// Structure (one persistent CTA per SM, 192 threads, warp-specialised):
-//   warp 0     TMA producer: A tile [128 x 128B] and W^T tile [256 x 128B] per stage, 128-byte swizzle,
+// Structure (one persistent CTA per SM, 320 threads, warp-specialised):
+//   warp 0     TMA producer: A tile [128 x 128B] and W^T tile [up to 256 x 128B] per stage, 128-byte swizzle,
 //              4-stage shared-memory ring, mbarrier expect-tx completion
-//   warp 1     MMA issuer: one elected lane issues tcgen05.mma.kind::i8 (M=128, N=256, K=32), four per
+//   warp 1     MMA issuer: one elected lane issues tcgen05.mma.kind::i8 (M=128, N<=256, K=32), four per
 //              stage; tcgen05.commit releases the stage; accumulators live in TMEM, two of them
 //              (2 x 256 columns) so the epilogue of tile i overlaps the main loop of tile i+1
-//   warps 2-5  epilogue: tcgen05.ld the accumulator (lane = row), add bias, rounding shift, saturate,
-//              pack four int8 per word, 16-byte global stores
+//   warps 2-9  epilogue, two groups of four warps on alternate tiles (group g owns accumulator g): tcgen05.ld
+//              of 64 columns at a time (lane = row) with the next 64 in flight, bias from a resident
+//              shared-memory copy, requantise, pack four int8 per word into the warp's swizzled 32 x 64-byte
+//              staging patch, TMA store; the accumulator goes back to the issuer at half-tile
 // Every wait is bounded: when a wait gives up, the CTA records a code in the status word, stops
 // issuing work, lets what is in flight land, frees its TMEM and returns.
 #include <cuda.h>
