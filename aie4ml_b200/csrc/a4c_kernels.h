@@ -29,6 +29,7 @@ int a4c_launch_add_float(const void* a, long long lda, const void* b, long long 
 int a4c_launch_dense_tc(const void* A, long long lda, const void* Wt, long long ldw, const int32_t* bias,
                         void* Y, long long ldy, long long M, int K, int N, int shift, int rounding, int relu,
                         int out_dtype, int a_unsigned, int cta_pair, int* status_word, cudaStream_t stream);
+void a4c_dense_tc_set_resident_w(int on);
 // 0 if the tensor-core path can take this problem, else an A4C_ERR_* code saying why not.
 int a4c_dense_tc_supported(const void* A, long long lda, const void* Wt, long long ldw, const void* Y,
                            long long ldy, long long M, int K, int N, int out_dtype);

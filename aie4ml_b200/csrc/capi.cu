@@ -239,6 +239,10 @@ int a4c_set_option(int option, int value) {
         g_bmm_path = value;
         return A4C_OK;
     }
+    if (option == A4C_OPT_DENSE_RESIDENT_W && (value == 0 || value == 1)) {
+        a4c_dense_tc_set_resident_w(value);
+        return A4C_OK;
+    }
     if (option == A4C_OPT_MLP_PATH && value >= 0 && value <= 2) {
         a4c_mlp_set_path(value);
         return A4C_OK;

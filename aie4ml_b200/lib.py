@@ -28,6 +28,7 @@ OPT_BMM_PATH = 1
 OPT_ROWOP_CHUNKS_PER_LANE = 2
 OPT_ROWOP_MIN_STAGES = 3
 OPT_MLP_PATH = 4
+OPT_DENSE_RESIDENT_W = 5
 
 # name -> (restype, argtypes); mirrors the header declaration by declaration
 SIGNATURES = {

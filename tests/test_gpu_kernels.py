@@ -71,6 +71,27 @@ def test_dense_tcgen05_output_widths_that_are_not_multiples_of_16(shape):
     np.testing.assert_array_equal(got, oracle.dense(a, w, None, shift=6, tok='conv_even', relu=False))
 
 
+@pytest.mark.parametrize('shape', [(76000, 256, 256), (19100, 128, 1024), (25300, 384, 700), (77000, 512, 40)])
+@pytest.mark.parametrize('resident', [1, 0])
+def test_dense_tcgen05_small_k_with_and_without_a_resident_weight_tile(shape, resident):
+    """Shapes large enough for the resident-W tile order (one weight tile per CTA kept in shared memory, A streamed
+    through a deeper ring): one, three and four column tiles, ragged last row tile, a narrow classifier head."""
+    import gpu_util as G
+    from aie4ml_b200 import lib as a4c
+
+    L = a4c.load()
+    assert L.a4c_set_option(a4c.OPT_DENSE_RESIDENT_W, resident) == 0
+    try:
+        M, K, N = shape
+        a, w, bias = _rand_dense(sum(shape), M, K, N)
+        got = G.dense(a, w, bias, shift=9, tok='positive_inf', relu=True, algo=TC)
+        np.testing.assert_array_equal(got, oracle.dense(a, w, bias, shift=9, tok='positive_inf', relu=True))
+        got = G.dense(a, w, None, shift=8, tok='conv_even', relu=False, algo=TC)
+        np.testing.assert_array_equal(got, oracle.dense(a, w, None, shift=8, tok='conv_even', relu=False))
+    finally:
+        assert L.a4c_set_option(a4c.OPT_DENSE_RESIDENT_W, 1) == 0
+
+
 @pytest.mark.parametrize('tok', TOKENS)
 @pytest.mark.parametrize('algo', [TC, TC2])
 def test_dense_tcgen05_every_rounding_mode(tok, algo):
