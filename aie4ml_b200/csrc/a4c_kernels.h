@@ -17,12 +17,12 @@ int a4c_launch_gemm_wide(const void* A, int a_bytes, long long a_rs, long long a
                          long long ldc, long long c_bs, long long batch, long long M, int K, int N, int shift,
                          int rounding, int relu, int out_dtype, int acc_bits, cudaStream_t stream);
 
-// Float-simulation path (float_ops.cu): bfloat16 (bf16 != 0) or float32 storage, float32 accumulation.
+// Float-simulation path (float_ops.cu): kind 0 bfloat16, 1 float32, 2 fp8 E4M3 storage; float32 accumulation.
 int a4c_launch_gemm_float(const void* A, long long a_rs, long long a_cs, long long a_bs, const void* B, long long b_ks,
                           long long b_ns, long long b_bs, const float* bias, void* C, long long ldc, long long c_bs,
-                          long long batch, long long M, int K, int N, int relu, int bf16, cudaStream_t stream);
+                          long long batch, long long M, int K, int N, int relu, int kind, cudaStream_t stream);
 int a4c_launch_add_float(const void* a, long long lda, const void* b, long long ldb, void* out, long long ldo,
-                         long long rows, long long cols, int bf16, cudaStream_t stream);
+                         long long rows, long long cols, int kind, cudaStream_t stream);
 
 // tcgen05 / TMA / TMEM int8 GEMM: A [M,K] K-contiguous, Wt [N,K] K-contiguous.
 // cta_pair = 0: one CTA per 128x256 tile; 1: a CTA pair (cta_group::2) per 256x256 tile.

@@ -154,6 +154,28 @@ int a4c_dense_i16(const int16_t* A, int64_t lda, const void* Wt, int w_dtype, in
     return finish();
 }
 
+int a4c_dense_ta(const void* A, int a_dtype, int64_t lda, int64_t stride_a, const void* Wt, int w_dtype, int64_t ldw,
+                 const int32_t* bias, void* Y, int64_t ldy, int64_t stride_y, int64_t batch, int M, int K, int N,
+                 int shift, int rounding, int relu, int out_dtype, void* stream) {
+    if (A == nullptr || Wt == nullptr || Y == nullptr) return A4C_ERR_INVALID_ARG;
+    if (batch < 0 || M <= 0 || K <= 0 || N <= 0 || lda < M || ldw < K || ldy < N) return A4C_ERR_INVALID_ARG;
+    if (!valid_round(rounding) || !valid_dtype(out_dtype) || shift < 0) return A4C_ERR_INVALID_ARG;
+    const bool a16 = a_dtype == A4C_I16, w16 = w_dtype == A4C_I16;
+    if (!(a_dtype == A4C_I8 || a_dtype == A4C_U8 || a16) || !(w_dtype == A4C_I8 || w16) || (w16 && !a16))
+        return A4C_ERR_INVALID_ARG;
+    if (shift > (w16 ? 62 : 31)) return A4C_ERR_INVALID_ARG;
+    int rc;
+    // stored [K, M]: the row (m) stride is 1 element, the k stride is the pitch
+    if (a16)
+        rc = a4c_launch_gemm_wide(A, 2, 1, lda, stride_a, Wt, w16 ? 2 : 1, 1, ldw, 0, bias, Y, ldy, stride_y, batch, M, K, N,
+                                  shift, rounding, relu, out_dtype, w16 ? 64 : 32, (cudaStream_t)stream);
+    else
+        rc = a4c_launch_gemm_simt(A, 1, lda, stride_a, Wt, 1, ldw, 0, bias, Y, ldy, stride_y, batch, M, K, N, shift,
+                                  rounding, relu, out_dtype, a_dtype == A4C_U8, (cudaStream_t)stream);
+    if (rc != A4C_OK) { if (rc == A4C_ERR_CUDA) note(cudaGetLastError()); return rc; }
+    return finish();
+}
+
 int a4c_bmm_i16(const int16_t* A, int64_t lda, int64_t stride_a, const void* B, int b_dtype, int64_t ldb,
                 int64_t stride_b, void* C, int64_t ldc, int64_t stride_c, int64_t batch, int M, int K, int N,
                 int trans_a, int trans_b, int shift, int rounding, int out_dtype, void* stream) {
@@ -175,8 +197,8 @@ int a4c_bmm_i16(const int16_t* A, int64_t lda, int64_t stride_a, const void* B, 
 int a4c_dense_f(const void* A, int fdtype, int64_t lda, const void* Wt, int64_t ldw, const float* bias, void* Y,
                 int64_t ldy, int64_t M, int K, int N, int relu, void* stream) {
     if (A == nullptr || Wt == nullptr || Y == nullptr) return A4C_ERR_INVALID_ARG;
-    if (M < 0 || K <= 0 || N <= 0 || lda < K || ldw < K || ldy < N || (fdtype != 0 && fdtype != 1)) return A4C_ERR_INVALID_ARG;
-    const int rc = a4c_launch_gemm_float(A, lda, 1, 0, Wt, 1, ldw, 0, bias, Y, ldy, 0, 1, M, K, N, relu, fdtype == 0,
+    if (M < 0 || K <= 0 || N <= 0 || lda < K || ldw < K || ldy < N || (fdtype < 0 || fdtype > 2)) return A4C_ERR_INVALID_ARG;
+    const int rc = a4c_launch_gemm_float(A, lda, 1, 0, Wt, 1, ldw, 0, bias, Y, ldy, 0, 1, M, K, N, relu, fdtype,
                                          (cudaStream_t)stream);
     if (rc != A4C_OK) { if (rc == A4C_ERR_CUDA) note(cudaGetLastError()); return rc; }
     return finish();
@@ -186,22 +208,22 @@ int a4c_bmm_f(const void* A, int fdtype, int64_t lda, int64_t stride_a, const vo
               void* C, int64_t ldc, int64_t stride_c, int64_t batch, int M, int K, int N, int trans_a, int trans_b,
               void* stream) {
     if (A == nullptr || B == nullptr || C == nullptr) return A4C_ERR_INVALID_ARG;
-    if (batch < 0 || M <= 0 || K <= 0 || N <= 0 || ldc < N || (fdtype != 0 && fdtype != 1)) return A4C_ERR_INVALID_ARG;
+    if (batch < 0 || M <= 0 || K <= 0 || N <= 0 || ldc < N || (fdtype < 0 || fdtype > 2)) return A4C_ERR_INVALID_ARG;
     if (lda < (trans_a ? M : K) || ldb < (trans_b ? K : N)) return A4C_ERR_INVALID_ARG;
     const long long a_rs = trans_a ? 1 : lda, a_cs = trans_a ? lda : 1;
     const long long b_ks = trans_b ? 1 : ldb, b_ns = trans_b ? ldb : 1;
     const int rc = a4c_launch_gemm_float(A, a_rs, a_cs, stride_a, B, b_ks, b_ns, stride_b, nullptr, C, ldc, stride_c, batch,
-                                         M, K, N, 0, fdtype == 0, (cudaStream_t)stream);
+                                         M, K, N, 0, fdtype, (cudaStream_t)stream);
     if (rc != A4C_OK) { if (rc == A4C_ERR_CUDA) note(cudaGetLastError()); return rc; }
     return finish();
 }
 
 int a4c_add_f(const void* a, int64_t lda, const void* b, int64_t ldb, void* out, int64_t ldo, int64_t rows, int64_t cols,
               int fdtype, void* stream) {
-    if (a == nullptr || b == nullptr || out == nullptr || rows < 0 || cols < 0 || (fdtype != 0 && fdtype != 1))
+    if (a == nullptr || b == nullptr || out == nullptr || rows < 0 || cols < 0 || (fdtype < 0 || fdtype > 2))
         return A4C_ERR_INVALID_ARG;
     if (lda < cols || ldb < cols || ldo < cols) return A4C_ERR_INVALID_ARG;
-    const int rc = a4c_launch_add_float(a, lda, b, ldb, out, ldo, rows, cols, fdtype == 0, (cudaStream_t)stream);
+    const int rc = a4c_launch_add_float(a, lda, b, ldb, out, ldo, rows, cols, fdtype, (cudaStream_t)stream);
     if (rc != A4C_OK) { if (rc == A4C_ERR_CUDA) note(cudaGetLastError()); return rc; }
     return finish();
 }

@@ -13,6 +13,11 @@ Mirrors the reference importer (``src/aie4ml/frontends/onnx/importer.py:30-130``
   ``Div`` (-> ``scale``), ``Softmax``, ``LayerNormalization``, ``Transpose``, ``Split``, ``Slice``, ``Concat``
   map one to one.
 
+A graph without Q/DQ nodes is a floating-point graph: a bare graph input of element type FLOAT / BFLOAT16 /
+FLOAT8E4M3FN and a float initializer used directly carry a ``FloatIntent`` (``context.py:19-24,127-144``,
+``utils.py:229-241``), and MatMul / Gemm / Add / LayerNormalization outputs inherit their left input's float intent
+(``handlers/matmul.py:51``, ``elementwise.py:61``), which selects the floating-point Dense / MatMul / Add kernels.
+
 The importer itself works on a small neutral description (``OnnxGraph``: nodes, initializers as NumPy arrays, input
 shapes), so it is testable without the ``onnx`` package; ``from_onnx`` needs ``onnx`` only to read a ``ModelProto``
 (or a path) into that description.  Output shapes are derived from the operators, not from ONNX shape inference.
@@ -27,7 +32,7 @@ from typing import Any, Dict, List, Optional, Sequence, Tuple
 import numpy as np
 
 from ..ir import BackendContext, TensorVar
-from ..qtypes import QuantIntent, RoundingMode, SaturationMode
+from ..qtypes import FloatFormat, FloatIntent, QuantIntent, RoundingMode, SaturationMode
 from .graph import GraphBuilder
 
 
@@ -44,9 +49,12 @@ class OnnxNode:
 class OnnxGraph:
     nodes: List[OnnxNode]
     initializers: Dict[str, np.ndarray]
-    inputs: Dict[str, Tuple[Tuple[int, ...], Any]]   # name -> (shape, numpy dtype of the declared element type)
+    inputs: Dict[str, Tuple[Tuple[int, ...], Any]]   # name -> (shape, numpy dtype of the declared element type, or
+                                                     #          'bfloat16' / 'float8_e4m3fn', which NumPy lacks)
     outputs: List[str]
     name: str = 'model'
+    # initializers stored as bfloat16 / float8_e4m3fn in the file: name -> that type's name (the array holds the values)
+    initializer_formats: Dict[str, str] = field(default_factory=dict)
 
 
 def require_onnx():
@@ -61,14 +69,32 @@ def require_onnx():
 
 
 _ONNX_ELEM_TO_NP = {1: np.float32, 2: np.uint8, 3: np.int8, 4: np.uint16, 5: np.int16, 6: np.int32, 7: np.int64,
-                    11: np.float64}
+                    11: np.float64, 16: 'bfloat16', 17: 'float8_e4m3fn'}
+
+
+def float_intent_of(tag) -> Optional[FloatIntent]:
+    """Element type (NumPy dtype or type name) -> FloatIntent, None when it is not one of the three float types."""
+    name = tag if isinstance(tag, str) else np.dtype(tag).name
+    if name == 'float32':
+        return FloatIntent(width=32, format=FloatFormat.FP32)
+    if name == 'bfloat16':
+        return FloatIntent(width=16, format=FloatFormat.BF16)
+    if name in ('float8_e4m3fn', 'fp8_e4m3'):
+        return FloatIntent(width=8, format=FloatFormat.FP8_E4M3)
+    return None
 
 
 def graph_from_proto(model_proto) -> OnnxGraph:
     """ModelProto -> OnnxGraph (needs the ``onnx`` package)."""
     _onnx, helper, numpy_helper = require_onnx()
     g = model_proto.graph
-    inits = {t.name: np.asarray(numpy_helper.to_array(t)) for t in g.initializer}
+    inits, init_formats = {}, {}
+    for t in g.initializer:
+        arr = np.asarray(numpy_helper.to_array(t))
+        if int(t.data_type) in (16, 17):
+            init_formats[t.name] = _ONNX_ELEM_TO_NP[int(t.data_type)]
+            arr = arr.astype(np.float32)
+        inits[t.name] = arr
     inputs: Dict[str, Tuple[Tuple[int, ...], Any]] = {}
     for vi in g.input:
         if vi.name in inits:
@@ -80,7 +106,7 @@ def graph_from_proto(model_proto) -> OnnxGraph:
     for i, n in enumerate(g.node):
         attrs = {a.name: helper.get_attribute_value(a) for a in n.attribute}
         nodes.append(OnnxNode(n.op_type, n.name or f'{n.op_type}_{i}', list(n.input), list(n.output), attrs))
-    return OnnxGraph(nodes, inits, inputs, [o.name for o in g.output], g.name or 'model')
+    return OnnxGraph(nodes, inits, inputs, [o.name for o in g.output], g.name or 'model', init_formats)
 
 
 def intent_from_qparams(inits: Dict[str, np.ndarray], scale_name: str, zero_name: str, qdtype, where: str) -> QuantIntent:
@@ -139,17 +165,35 @@ class _Importer:
     def source(self, onnx_name: str, where: str) -> TensorVar:
         if onnx_name in self.value:
             return self.value[onnx_name]
+        if onnx_name in self.g.inputs:
+            # a bare graph input (no Q/DQ in front): only the three float element types can be computed on as they are
+            shape, dt = self.g.inputs[onnx_name]
+            intent = float_intent_of(dt)
+            if intent is None:
+                raise ValueError(f'{where}: graph input "{onnx_name}" has unsupported element type {dt}. '
+                                 'Use QDQ wrapping for integer inputs.')
+            t = self.graph_input(onnx_name, shape, intent)
+            self.bind(onnx_name, t)
+            return t
         raise ValueError(f'{where}: input {onnx_name} is not a lowered tensor (a float graph input or initializer must '
                          'pass through QuantizeLinear / DequantizeLinear first).')
 
-    def param_source(self, onnx_name: str, where: str) -> TensorVar:
+    def param_source(self, onnx_name: str, where: str, like=None) -> TensorVar:
+        """A constant operand.  ``like``: precision of the activation it meets; next to a floating-point activation a
+        float initializer carries the float intent of its own stored type."""
         if onnx_name in self.value:
             return self.value[onnx_name]
         if onnx_name in self.g.initializers:
             arr = np.asarray(self.g.initializers[onnx_name])
             if not np.issubdtype(arr.dtype, np.floating):
                 raise ValueError(f'{where}: constant {onnx_name} must be float or pass through DequantizeLinear.')
-            return self.param(onnx_name, arr.astype(np.float64), None)
+            intent = None
+            if isinstance(like, FloatIntent):
+                intent = float_intent_of(self.g.initializer_formats.get(onnx_name, arr.dtype))
+                if intent is None:
+                    raise ValueError(f'{where}: direct initializer inputs must be float32/bfloat16/fp8_e4m3, or quantized '
+                                     f'via DequantizeLinear; got {arr.dtype}.')
+            return self.param(onnx_name, arr.astype(np.float64), intent)
         raise ValueError(f'{where}: constant input {onnx_name} not found.')
 
     def emit(self, op_type, name, inputs: Sequence[TensorVar], outputs, roles, metadata) -> None:
@@ -262,16 +306,17 @@ class _Importer:
             raise ValueError(f'{n.name}: activation input cannot be constant.')
         rhs_const = gemm or rhs_name in self.g.initializers or (rhs_name in self.value and self.value[rhs_name].is_parameter)
         out = n.outputs[0]
+        out_p = lhs.precision if isinstance(lhs.precision, FloatIntent) else None
         if not rhs_const:
             rhs = self.source(rhs_name, n.name)
             shape = tuple(lhs.shape[:-1]) + (int(rhs.shape[-1]),)
             if int(lhs.shape[-1]) != int(rhs.shape[-2]):
                 raise ValueError(f'{n.name}: MatMul operands do not contract ({lhs.shape} x {rhs.shape}).')
-            self.emit('matmul', n.name, [lhs, rhs], [(out, shape, None)], ['lhs', 'rhs'],
+            self.emit('matmul', n.name, [lhs, rhs], [(out, shape, out_p)], ['lhs', 'rhs'],
                       {'n_in': int(rhs.shape[-2]), 'n_out': int(rhs.shape[-1]), 'use_bias': False, 'layer_class': 'MatMul',
                        'source_class': 'MatMul', 'source_layer': n.name})
             return
-        rhs_t = self.param_source(rhs_name, n.name)
+        rhs_t = self.param_source(rhs_name, n.name, like=lhs.precision)
         if not rhs_t.is_parameter:
             raise ValueError(f'{n.name}: weight input must be a constant initializer.')
         W = np.asarray(rhs_t.data, dtype=np.float64)
@@ -287,40 +332,44 @@ class _Importer:
         meta = {'n_in': n_in, 'n_out': n_out, 'use_bias': False, 'layer_class': 'Dense', 'source_class': n.op_type,
                 'source_layer': n.name}
         if bias_name is None:
-            self.emit('dense', n.name, [lhs, w_param], [(out, shape, None)], ['lhs', 'rhs'], meta)
+            self.emit('dense', n.name, [lhs, w_param], [(out, shape, out_p)], ['lhs', 'rhs'], meta)
             return
         pre = f'{n.name}_prebias'
         self.mirrors.append((pre, out))
-        self.emit('dense', n.name, [lhs, w_param], [(pre, shape, None)], ['lhs', 'rhs'], meta)
-        bias_t = self.param_source(bias_name, n.name)
+        self.emit('dense', n.name, [lhs, w_param], [(pre, shape, out_p)], ['lhs', 'rhs'], meta)
+        bias_t = self.param_source(bias_name, n.name, like=lhs.precision)
         if not bias_t.is_parameter:
             raise ValueError(f'{n.name}: Gemm bias must be constant.')
         bias = np.asarray(bias_t.data, dtype=np.float64).reshape(-1)
         if bias.size != n_out:
             raise ValueError(f'{n.name}: Gemm bias must contain exactly {n_out} elements.')
         b_param = self.param(f'{n.name}_bias', bias, bias_t.precision)
-        self.emit('add', f'{n.name}_bias', [self.value[pre], b_param], [(out, shape, None)], ['lhs', 'rhs'],
+        self.emit('add', f'{n.name}_bias', [self.value[pre], b_param], [(out, shape, out_p)], ['lhs', 'rhs'],
                   {'layer_class': 'Add', 'source_class': 'Gemm', 'source_layer': n.name})
 
     def add(self, n: OnnxNode) -> None:
         if len(n.inputs) != 2:
             raise ValueError(f'{n.name}: Add must have exactly 2 inputs.')
+        acts = [self.source(name, n.name) for name in n.inputs if name in self.value or name in self.g.inputs]
+        like = acts[0].precision if acts else None
         ts = []
         for name in n.inputs:
-            ts.append(self.value[name] if name in self.value else self.param_source(name, n.name))
+            ts.append(self.value[name] if name in self.value else self.param_source(name, n.name, like=like))
         lhs, rhs = ts
         if lhs.is_parameter and not rhs.is_parameter:
             lhs, rhs = rhs, lhs
         if lhs.is_parameter == rhs.is_parameter and tuple(lhs.shape) != tuple(rhs.shape):
             raise ValueError(f'{n.name}: generic Add only supports exact-shape elementwise inputs; got {lhs.shape} and {rhs.shape}.')
-        self.emit('add', n.name, [lhs, rhs], [(n.outputs[0], tuple(lhs.shape), None)], ['lhs', 'rhs'],
+        out_p = lhs.precision if isinstance(lhs.precision, FloatIntent) else None
+        self.emit('add', n.name, [lhs, rhs], [(n.outputs[0], tuple(lhs.shape), out_p)], ['lhs', 'rhs'],
                   {'layer_class': 'Add', 'source_class': 'Add', 'source_layer': n.name})
 
     def relu(self, n: OnnxNode) -> None:
         if len(n.inputs) != 1:
             raise ValueError(f'{n.name}: Relu must have exactly 1 input.')
         src = self.source(n.inputs[0], n.name)
-        self.emit('activation', n.name, [src], [(n.outputs[0], tuple(src.shape), None)], ['lhs'],
+        out_p = src.precision if isinstance(src.precision, FloatIntent) else None
+        self.emit('activation', n.name, [src], [(n.outputs[0], tuple(src.shape), out_p)], ['lhs'],
                   {'activation': 'relu', 'layer_class': 'Activation', 'source_class': 'Relu', 'source_layer': n.name})
 
     def mul_div(self, n: OnnxNode) -> None:

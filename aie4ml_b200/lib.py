@@ -52,6 +52,8 @@ SIGNATURES = {
                                c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'a4c_dense_i16': (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int,
                               c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    'a4c_dense_ta': (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int64,
+                             c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'a4c_bmm_i16': (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int, c_int64, c_int64, c_void_p, c_int64, c_int64,
                             c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     'a4c_dense_f': (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int,

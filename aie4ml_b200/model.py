@@ -90,7 +90,8 @@ class CudaModel:
                                   for n in list(graph.input_tensor_names) + list(graph.output_tensor_names)):
             # iterations are chunks of one long batch: copy-in, launches and copy-out overlap across them
             pipe = self.pipeline()
-            host_in = {n: _host_tensor(a.reshape(-1, *a.shape[2:])).pin_memory() for n, a in prepared.items()}
+            host_in = {n: _host_tensor(a.reshape(-1, *a.shape[2:]), plan.tensor_of(n).dtype).pin_memory()
+                       for n, a in prepared.items()}
             host_out = {}
             for n in outs:
                 t = plan.tensor_of(n)
@@ -102,7 +103,8 @@ class CudaModel:
         else:
             for it in range(iterations):
                 for name, arr in prepared.items():
-                    plan.tensor_of(name).copy_(_host_tensor(arr[it]).to(plan.device, non_blocking=False))
+                    dst = plan.tensor_of(name)
+                    dst.copy_(_host_tensor(arr[it], dst.dtype).to(plan.device, non_blocking=False))
                 plan.run()
                 plan.check_status()
                 for name in outs:
@@ -186,13 +188,16 @@ class CudaModel:
         return out / 'cuda_pipeline.json'
 
 
-def _host_tensor(arr: np.ndarray):
-    """NumPy storage array -> torch CPU tensor of the plan's dtype (bfloat16 arrives as its 16 bits)."""
+def _host_tensor(arr: np.ndarray, dtype=None):
+    """NumPy storage array -> torch CPU tensor of the plan tensor's ``dtype`` (bfloat16 arrives as its 16 bits, fp8
+    as its 8 bits)."""
     import torch
 
     arr = np.ascontiguousarray(arr)
     if arr.dtype == np.uint16:
         return torch.from_numpy(arr.view(np.int16)).view(torch.bfloat16)
+    if dtype == torch.float8_e4m3fn:
+        return torch.from_numpy(arr).view(torch.float8_e4m3fn)
     return torch.from_numpy(arr)
 
 
@@ -200,7 +205,7 @@ def _host_array(t) -> np.ndarray:
     """torch CPU tensor -> int64 codes, or float32 values for the float-simulation path."""
     import torch
 
-    if t.dtype in (torch.bfloat16, torch.float32):
+    if t.dtype in (torch.bfloat16, torch.float32, torch.float8_e4m3fn):
         return t.float().numpy()
     return t.numpy().astype(np.int64)
 

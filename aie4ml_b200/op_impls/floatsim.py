@@ -18,7 +18,7 @@ import numpy as np
 
 from ..ir import ExecutionEntry, OpNode, input_tensor_for_role, optional_tensor_for_role
 from ..qtypes import FLOAT_FORMATS, AIEDataType, FloatIntent
-from ..quant_utils import to_storage_float
+from ..quant_utils import from_storage_float, pack_constant_float
 from .base import CUDA_GENERATIONS, OpImplVariant, register_variant
 from .matmul import _transposed
 from .precision import resolve_exact_storage_dtype
@@ -86,7 +86,8 @@ class CudaFloatDenseVariant(OpImplVariant):
         W = W.reshape(-1, W.shape[-2], W.shape[-1])[-1]
         K, N = int(W.shape[0]), int(W.shape[1])
         kp = (K + 15) // 16 * 16
-        stored, values = to_storage_float(W.T, fmt)          # [N, K] in storage form, and the values it holds
+        stored = pack_constant_float(W.T, fmt)               # [N, K] in storage form, by the reference's packer
+        values = from_storage_float(stored, fmt)             # ... and the float32 values that storage holds
         packed = np.zeros((N, kp), dtype=stored.dtype)
         packed[:, :K] = stored
         bias = optional_tensor_for_role(node, 'bias')

@@ -28,7 +28,7 @@ ROUNDING_CODE = {'floor': 0, 'ceil': 1, 'positive_inf': 2, 'negative_inf': 3, 's
 # Codes the C ABI takes for an element type.
 DTYPE_CODE = {'int8': 0, 'uint8': 1, 'int16': 2}
 # Codes the floating-point entry points take.
-FLOAT_CODE = {'bfloat16': 0, 'float32': 1}
+FLOAT_CODE = {'bfloat16': 0, 'float32': 1, 'fp8_e4m3': 2}
 
 
 def to_quant_intent(precision: Any) -> QuantIntent:

@@ -57,6 +57,7 @@ class QuantIntent:
 class FloatFormat(Enum):
     BF16 = 'bfloat16'
     FP32 = 'float32'
+    FP8_E4M3 = 'fp8_e4m3'
 
 
 @dataclass(frozen=True)
@@ -68,12 +69,13 @@ class FloatIntent:
     format: FloatFormat
 
 
-FLOAT_FORMATS = ('bfloat16', 'float32')
+FLOAT_FORMATS = ('bfloat16', 'float32', 'fp8_e4m3')
 
-# format -> (bits, signed, numpy dtype, C type); bfloat16 is stored as its 16 bits
+# format -> (bits, signed, numpy dtype, C type); bfloat16 is stored as its 16 bits, fp8 (E4M3, finite-only) as its 8
 _FORMATS = {
     'bfloat16': (16, True, np.uint16, 'uint16_t'),
     'float32': (32, True, np.float32, 'float'),
+    'fp8_e4m3': (8, True, np.uint8, 'uint8_t'),
     'int8': (8, True, np.int8, 'int8_t'),
     'uint8': (8, False, np.uint8, 'uint8_t'),
     'int16': (16, True, np.int16, 'int16_t'),

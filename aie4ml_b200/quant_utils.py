@@ -91,16 +91,81 @@ def from_bf16_bits(bits) -> np.ndarray:
     return (b.astype(np.uint32) << 16).view(np.float32).reshape(b.shape)
 
 
+def to_fp8_bits(values) -> np.ndarray:
+    """float -> FP8 E4M3 (finite-only "fn" variant: bias 7, largest finite 448, 0x7F = NaN) bit patterns, round to
+    nearest even, values beyond the largest finite saturate to it.  This is what the device's conversion does and
+    what activations entering or leaving the graph go through."""
+    f = np.ascontiguousarray(np.asarray(values, dtype=np.float32))
+    u = f.view(np.uint32)
+    sign = ((u >> 24) & 0x80).astype(np.uint8)
+    mag = u & 0x7FFFFFFF
+    a = mag.view(np.float32)
+    # normal range: keep 3 mantissa bits, ties to even; exponent field moves from bias 127 to bias 7
+    r = ((mag.astype(np.uint64) + 0x7FFFF + ((mag >> 20) & 1)) >> 20).astype(np.int64) - (120 << 3)
+    code = np.clip(r, 0, 0x7E)
+    # below 2^-6 the spacing is 2^-9: the rounded count is the encoding itself (8 = 2^-6 = the first normal)
+    with np.errstate(invalid='ignore'):
+        small = a < np.float32(2.0 ** -6)
+        code = np.where(small, np.rint(a.astype(np.float64) * 512.0).astype(np.int64), code)
+    code = np.where(np.isnan(a), 0x7F, code)
+    return (code.astype(np.uint8) | sign).reshape(f.shape)
+
+
+_FP8_VALUES = None
+
+
+def from_fp8_bits(bits) -> np.ndarray:
+    global _FP8_VALUES
+    if _FP8_VALUES is None:
+        c = np.arange(256)
+        e, m = (c >> 3) & 15, (c & 7).astype(np.float64)
+        mag = np.where(e == 0, m * 2.0 ** -9, (1.0 + m / 8.0) * np.exp2(e.astype(np.float64) - 7.0))
+        mag = np.where((c & 0x7F) == 0x7F, np.nan, mag)
+        _FP8_VALUES = np.where(c & 0x80, -mag, mag).astype(np.float32)
+    return _FP8_VALUES[np.asarray(bits, dtype=np.uint8)]
+
+
+def pack_constant_float(values, fmt: str) -> np.ndarray:
+    """Weights of a floating-point Dense in storage form, by the reference's constant packer
+    (``src/aie4ml/op_impls/families/matmul/common.py:253-284``): bfloat16 keeps the upper 16 bits of the float32
+    (truncation, not rounding); fp8_e4m3 adds half of the kept mantissa's last place to the float32 bit pattern and
+    truncates (ties away from zero), encodes magnitudes of 2^9 and above as 0x7F, and below 2^-10 as zero."""
+    f = np.ascontiguousarray(np.asarray(values, dtype=np.float32))
+    if fmt == 'float32':
+        return f
+    u = f.view(np.uint32)
+    if fmt == 'bfloat16':
+        return (u >> 16).astype(np.uint16).reshape(f.shape)
+    if fmt != 'fp8_e4m3':
+        raise ValueError(f'not a floating-point storage format: {fmt!r}')
+    h = (u.astype(np.uint64) + 0x80000) & 0xFFFFFFFF
+    e = ((h >> 23) & 0xFF).astype(np.int64)
+    m = (h & 0x7FFFFF).astype(np.int64)
+    sign = ((h >> 24) & 0x80).astype(np.int64)
+    normal = (((e - 120) << 3) & 0x78) | (m >> 20)
+    sub_shift = np.clip(140 - e, 0, 63)
+    subnormal = (((0x780000 + m) >> sub_shift) + 1) >> 1
+    mag = np.where(e > 135, 0x7F, np.where(e > 120, normal, np.where(e > 116, subnormal, 0)))
+    return ((sign | mag) & 0xFF).astype(np.uint8).reshape(f.shape)
+
+
 def to_storage_float(values, fmt: str):
-    """-> (array in storage form, float32 values that storage holds) for 'bfloat16' or 'float32'."""
+    """-> (array in storage form, float32 values that storage holds) for 'bfloat16', 'float32' or 'fp8_e4m3'."""
     if fmt == 'bfloat16':
         bits = to_bf16_bits(values)
         return bits, from_bf16_bits(bits)
     if fmt == 'float32':
         f = np.ascontiguousarray(np.asarray(values, dtype=np.float32))
         return f, f
+    if fmt == 'fp8_e4m3':
+        bits = to_fp8_bits(values)
+        return bits, from_fp8_bits(bits)
     raise ValueError(f'not a floating-point storage format: {fmt!r}')
 
 
 def from_storage_float(stored, fmt: str) -> np.ndarray:
-    return from_bf16_bits(stored) if fmt == 'bfloat16' else np.asarray(stored, dtype=np.float32)
+    if fmt == 'bfloat16':
+        return from_bf16_bits(stored)
+    if fmt == 'fp8_e4m3':
+        return from_fp8_bits(stored)
+    return np.asarray(stored, dtype=np.float32)

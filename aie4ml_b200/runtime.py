@@ -22,9 +22,9 @@ from . import lib as _lib
 from .ir import BackendContext, input_tensor_for_role
 from .op_impls.precision import DTYPE_CODE, FLOAT_CODE, ROUNDING_CODE, resolve_exact_storage_dtype
 
-ESZ = {'int8': 1, 'uint8': 1, 'int16': 2, 'int32': 4, 'bfloat16': 2, 'float32': 4}
+ESZ = {'int8': 1, 'uint8': 1, 'int16': 2, 'int32': 4, 'bfloat16': 2, 'float32': 4, 'fp8_e4m3': 1}
 NP_DT = {'int8': np.int8, 'uint8': np.uint8, 'int16': np.int16, 'int32': np.int32, 'bfloat16': np.uint16,
-         'float32': np.float32}
+         'float32': np.float32, 'fp8_e4m3': np.uint8}
 
 
 def _torch():
@@ -132,7 +132,7 @@ class Plan:
             if t.is_parameter:
                 continue
             self.fmt[name] = resolve_exact_storage_dtype(t.precision, namespace='tensor', layer_name=name).format
-            if self.fmt[name] not in ('int8', 'uint8', 'int16', 'bfloat16', 'float32'):
+            if self.fmt[name] not in ('int8', 'uint8', 'int16', 'bfloat16', 'float32', 'fp8_e4m3'):
                 raise NotImplementedError(f'{name}: activation format {self.fmt[name]!r} has no kernel.')
 
         # 2. aliases introduced by view placeholders
@@ -248,7 +248,7 @@ class Plan:
         torch = _torch()
         v = self._view(name)
         dt = {'int8': torch.int8, 'uint8': torch.uint8, 'int16': torch.int16, 'bfloat16': torch.bfloat16,
-              'float32': torch.float32}[v.fmt]
+              'float32': torch.float32, 'fp8_e4m3': torch.float8_e4m3fn}[v.fmt]
         base = self.buffers[v.root].view(dt)
         return base.as_strided(v.shape, v.strides, v.offset)
 
@@ -439,9 +439,20 @@ class Plan:
         kind, name = op['kind'], op['name']
         L = self.lib
         if kind == 'dense':
-            if op['transpose_lhs']:
-                raise NotImplementedError(f'{name}: dense over a transposed input view has no kernel yet.')
             a, y = self._view(op['lhs']), self._view(op['out'])
+            if op['transpose_lhs']:
+                # the stored input is a stack of [K, M] matrices; the output a stack of [M, N]
+                a_off, ba, Ks, Ms, lda, sa = collapse_batched(a, f'{name}: input')
+                y_off, by, My, N, ldy, sy = collapse_batched(y, f'{name}: output')
+                if (ba, Ms, Ks, N) != (by, My, op['K'], op['N']):
+                    raise ValueError(f'{name}: shape mismatch between views (input {a.shape}, output {y.shape}).')
+                w = self.params[op['weight']]
+                bias = self.params[op['bias']] if op['bias'] else None
+                args = (self.ptr(a, a_off), DTYPE_CODE[op['lhs_dtype']], lda, sa, w.data_ptr(), DTYPE_CODE[op['rhs_dtype']],
+                        int(w.shape[1]), bias.data_ptr() if bias is not None else None, self.ptr(y, y_off), ldy, sy, ba,
+                        Ms, Ks, N, op['shift'], ROUNDING_CODE[op['rounding']], int(op['relu']),
+                        DTYPE_CODE[op['out_dtype']])
+                return L.a4c_dense_ta, args
             a_off, M, K, lda = collapse_2d(a, f'{name}: input')
             y_off, My, N, ldy = collapse_2d(y, f'{name}: output')
             if (M, K, N) != (My, op['K'], op['N']):

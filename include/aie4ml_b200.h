@@ -165,11 +165,27 @@ A4C_API int a4c_bmm_i16(const int16_t* A, int64_t lda, int64_t stride_a, const v
                 int trans_a, int trans_b, int shift, int rounding, int out_dtype, void* stream);
 
 /*
+ * Dense whose input arrives through a view that swaps the last two axes: the reference's TRANSPOSE_INPUT flag
+ * (src/aie4ml/templates/firmware/variants/dense_bias_relu/parameters.h.jinja:12, read by
+ * dense_bias_relu.cpp:99,135; set from the input's io_view in op_impls/families/matmul/dense.py:130).
+ *   stored A_b: [K, M] a_dtype (int8 / uint8 / int16), pitch lda, batch stride stride_a   (logical input: A_b^T)
+ *   W^T [N, K] w_dtype (int8, or int16 with an int16 input), pitch ldw; bias int32 or NULL
+ *   Y_b: [M, N] out_dtype, pitch ldy, batch stride stride_y
+ * Arithmetic, accumulator width and SRS exactly as a4c_dense_i8 / a4c_dense_i16.  Pitches and strides in
+ * ELEMENTS.  Runs on the any-stride dp4a / wide kernels (the tensor-core kernels need a K-contiguous input).
+ */
+A4C_API int a4c_dense_ta(const void* A, int a_dtype, int64_t lda, int64_t stride_a, const void* Wt, int w_dtype,
+                 int64_t ldw, const int32_t* bias, void* Y, int64_t ldy, int64_t stride_y, int64_t batch, int M, int K,
+                 int N, int shift, int rounding, int relu, int out_dtype, void* stream);
+
+/*
  * Float-simulation path (reference AIEConfig.ComputeDtype = 'bfloat16' | 'float32',
  * src/aie4ml/passes/force_float_mode.py:22-46; float contract of the matmul family
  * src/aie4ml/op_impls/families/matmul/resolver.py:110-127): the same Dense / MatMul / Add operators computed in
- * floating point.  fdtype 0 = bfloat16 (tensors hold the 16 bits), 1 = float32; accumulation in float32, bias
- * float32, optional ReLU, results rounded to nearest-even into the storage type.  Pitches / strides in elements.
+ * floating point.  fdtype 0 = bfloat16 (tensors hold the 16 bits), 1 = float32, 2 = fp8 E4M3 (finite-only
+ * variant, the reference's 'fp8_e4m3' of src/aie4ml/aie_types.py:38, tensors hold the 8 bits; results beyond
+ * +-448 saturate); accumulation in float32, bias float32, optional ReLU, results rounded to nearest-even into the
+ * storage type.  Pitches / strides in elements.
  * Held to the reference's tolerances (tests/test_float_sim.py:87-93), not to bit equality.
  */
 A4C_API int a4c_dense_f(const void* A, int fdtype, int64_t lda, const void* Wt, int64_t ldw, const float* bias, void* Y,

@@ -138,6 +138,24 @@ def record_quantizer():
     return out
 
 
+def record_float_packer():
+    """The reference's constant packer for floating-point weights (pack_as_float) on float32 bit patterns that cover
+    every fp8 exponent, ties, the subnormal range, the saturation threshold and non-finite inputs."""
+    from aie4ml.aie_types import FloatFormat
+    from aie4ml.op_impls.families.matmul.common import pack_as_float
+
+    rng = np.random.default_rng(7)
+    vals = np.concatenate([
+        rng.normal(0, 1, 160), rng.normal(0, 60, 160), rng.normal(0, 0.004, 160),
+        np.ldexp(1.0 + np.arange(0, 16) / 16.0, -8), np.ldexp(1.0 + np.arange(0, 16) / 16.0, 3),
+        np.ldexp(np.arange(0, 33) / 2.0, -9),                       # every subnormal step and its midpoints
+        np.array([0.0, -0.0, 448.0, 463.9, 464.0, 480.0, 511.9, 512.0, 600.0, -600.0, 1e9, np.inf, -np.inf,
+                  2.0 ** -10, 2.0 ** -11, 3 * 2.0 ** -11, 1.0 + 2.0 ** -4, 1.0 + 3 * 2.0 ** -4])]).astype(np.float32)
+    return {'bits': vals.view(np.uint32).astype(int).tolist(),
+            'fp8_e4m3': np.asarray(pack_as_float(vals, FloatFormat.FP8_E4M3)).astype(int).tolist(),
+            'bfloat16': np.asarray(pack_as_float(vals, FloatFormat.BF16)).astype(int).tolist()}
+
+
 def main():
     from aie4ml.op_impls.utils.precision import ROUNDING_TOKEN_MAP
 
@@ -145,6 +163,7 @@ def main():
         'rounding_token_map': {k.name: v for k, v in ROUNDING_TOKEN_MAP.items()},
         'cases': {name: record_case(name) for name in CASES},
         'quantizer': record_quantizer(),
+        'float_packer': record_float_packer(),
     }
     path = HERE / 'reference_contracts.json'
     path.write_text(json.dumps(fixture, separators=(',', ':')))

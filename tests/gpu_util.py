@@ -196,6 +196,23 @@ def dense16(a, w_kn, bias, *, shift, tok, relu, out_dtype='int8'):
     return y[:, :N]
 
 
+def dense_ta(a_t, w_kn, bias, *, shift, tok, relu, out_dtype='int8'):
+    """Dense over a stack of stored [K, M] inputs (int8 / uint8 / int16); returns the stack of [M, N] outputs."""
+    L = a4c.load()
+    batch, K, M = a_t.shape
+    N = w_kn.shape[1]
+    a_code = {'int8': 0, 'uint8': 1, 'int16': 2}[a_t.dtype.name]
+    w_code = {'int8': 0, 'int16': 2}[w_kn.dtype.name]
+    a_d, wt = dev(np.ascontiguousarray(a_t)), dev(np.ascontiguousarray(w_kn.T))
+    b_d = dev(bias.astype(np.int32)) if bias is not None else None
+    y_d = torch.zeros((batch, M, N), dtype=TD[out_dtype], device='cuda')
+    rc = L.a4c_dense_ta(a_d.data_ptr(), a_code, M, K * M, wt.data_ptr(), w_code, K,
+                        b_d.data_ptr() if b_d is not None else None, y_d.data_ptr(), N, M * N, batch, M, K, N, shift,
+                        ROUNDING_CODE[tok], int(relu), DTYPE_CODE[out_dtype], stream())
+    a4c.check(rc, 'a4c_dense_ta')
+    return y_d.cpu().numpy()
+
+
 def bmm16(a, b, *, shift, tok, trans_a=False, trans_b=False, out_dtype='int16'):
     L = a4c.load()
     batch = a.shape[0]

@@ -83,3 +83,15 @@ def test_host_quantizer_matches_reference():
         orc = oracle.quantize(values, frac=c['frac'], width=c['width'], signed=c['signed'], rounding=c['rounding'],
                               saturation=c['saturation'])
         np.testing.assert_array_equal(orc, np.array(c['codes']), err_msg='oracle ' + str(c)[:80])
+
+
+def test_float_constant_packer_matches_reference():
+    """Weights of the floating-point Dense are packed by the reference's own rule (truncation for bfloat16, its
+    half-up-on-magnitude scheme for fp8_e4m3), pinned on 590 recorded float32 bit patterns."""
+    from aie4ml_b200.quant_utils import pack_constant_float
+
+    rec = FIXTURE['float_packer']
+    vals = np.array(rec['bits'], dtype=np.uint32).view(np.float32)
+    assert len(vals) > 500
+    for fmt in ('fp8_e4m3', 'bfloat16'):
+        np.testing.assert_array_equal(pack_constant_float(vals, fmt).astype(np.int64), np.array(rec[fmt]), err_msg=fmt)

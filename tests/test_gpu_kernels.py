@@ -482,6 +482,32 @@ def test_dense_16_bit_operands(wide, tok):
                                                     out_dtype='int16', acc_bits=acc_bits))
 
 
+@pytest.mark.parametrize('kind', ['int8', 'uint8', 'int16xint8', 'int16xint16'])
+def test_dense_over_a_transposed_stored_input(kind):
+    """TRANSPOSE_INPUT of the reference's Dense: the stored tensor is a stack of [K, M] matrices."""
+    import gpu_util as G
+
+    rng = np.random.default_rng(120)
+    batch, K, M, N = 3, 52, 37, 29
+    if kind == 'int8':
+        a_t, w = rng.integers(-128, 128, (batch, K, M)).astype(np.int8), rng.integers(-128, 128, (K, N)).astype(np.int8)
+    elif kind == 'uint8':
+        a_t, w = rng.integers(0, 256, (batch, K, M)).astype(np.uint8), rng.integers(-128, 128, (K, N)).astype(np.int8)
+    elif kind == 'int16xint8':
+        a_t, w = rng.integers(-32768, 32768, (batch, K, M)).astype(np.int16), rng.integers(-128, 128, (K, N)).astype(np.int8)
+    else:
+        a_t = rng.integers(-32768, 32768, (batch, K, M)).astype(np.int16)
+        w = rng.integers(-32768, 32768, (K, N)).astype(np.int16)
+    acc_bits = 64 if kind == 'int16xint16' else 32
+    base = {'int8': 7, 'uint8': 8, 'int16xint8': 15, 'int16xint16': 23}[kind]
+    bias = rng.integers(-(1 << 16), 1 << 16, N).astype(np.int32)
+    a = np.swapaxes(a_t, 1, 2)
+    for tok, relu, od, b in (('conv_even', True, 'int8', bias), ('positive_inf', False, 'uint8', bias), ('floor', False, 'int16', None)):
+        got = G.dense_ta(a_t, w, b, shift=base, tok=tok, relu=relu, out_dtype=od)
+        want = oracle.dense(a, w, b, shift=base, tok=tok, relu=relu, out_dtype=od, acc_bits=acc_bits)
+        np.testing.assert_array_equal(got, want)
+
+
 def test_bmm_16_bit_operands_with_transposes():
     import gpu_util as G
 

@@ -171,6 +171,23 @@ def test_report_times_every_launch_and_names_the_bound():
     assert 'sum of launches' in text and 'attention' in text
 
 
+def test_model_with_a_dense_over_a_transposed_input_view():
+    """Transpose -> Dense: the transpose folds into the Dense's input view (TRANSPOSE_INPUT in the reference) and
+    the kernel reads the stored [K, M] matrices; a second ordinary Dense follows."""
+    from aie4ml_b200.frontends.graph import GraphBuilder, intent
+
+    rng = np.random.default_rng(17)
+    b = GraphBuilder({'Part': 'cuda_b200'}, name='dense_ta')
+    x = b.input('x', (6, 48, 20), intent(8, 4))
+    xt = b.transpose('xt', x, [0, 2, 1])
+    h = b.dense('fc0', xt, rng.uniform(-1, 1, (48, 24)), intent(8, 6), intent(8, 3), bias=rng.uniform(-1, 1, 24),
+                bias_precision=intent(16, 8), relu=True)
+    y = b.dense('fc1', h, rng.uniform(-1, 1, (24, 16)), intent(8, 6), intent(8, 3))
+    b.output(y)
+    model = _check(b, {'x': rng.integers(-128, 128, (6, 48, 20)).astype(np.int8)})
+    assert model.plan.ops[0]['transpose_lhs'] and not model.plan.ops[1]['transpose_lhs']
+
+
 def test_model_with_16_bit_activations_and_weights():
     """A three-layer network whose first two layers keep 16-bit activations: int16 x int8 (acc32) into int16,
     int16 x int16 (acc64) into int8, then an ordinary int8 layer; against the oracle on the exported plan."""

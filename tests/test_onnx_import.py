@@ -109,7 +109,7 @@ def test_importer_rejections_name_the_node():
     g = OnnxGraph([OnnxNode('Gelu', 'g0', ['x'], ['y'])], {}, {'x': ((2, 16), np.float32)}, ['y'])
     with pytest.raises(NotImplementedError, match='g0: ONNX operator Gelu has no handler'):
         lower_onnx_graph(g, {'Part': 'cuda_b200'})
-    g = OnnxGraph([OnnxNode('Relu', 'r0', ['x'], ['y'])], {}, {'x': ((2, 16), np.float32)}, ['y'])
+    g = OnnxGraph([OnnxNode('Relu', 'r0', ['x'], ['y'])], {}, {'w': ((2, 16), np.float32)}, ['y'])
     with pytest.raises(ValueError, match='r0: input x is not a lowered tensor'):
         lower_onnx_graph(g, {'Part': 'cuda_b200'})
 
