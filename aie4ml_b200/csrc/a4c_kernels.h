@@ -75,16 +75,19 @@ int a4c_launch_mlp_small(const void* X, long long ldx, int x_unsigned, int n_lay
                          cudaStream_t stream);
 void a4c_mlp_set_path(int path);
 
-// Fused attention head (attention_tc.cu): scores, softmax and the value product in one kernel.
+// Fused attention heads (attention_tc.cu): scores, softmax and the value product in one kernel; `heads` heads per
+// batch entry, hstride_* bytes apart (ignored for heads == 1).
 int a4c_attention_tc_supported(const void* q, long long ldq, long long stride_q, const void* k, long long ldk,
                                long long stride_k, const void* v, long long ldv, long long stride_v, const void* out,
                                long long ldo, long long stride_o, long long batch, int sq, int sk, int dh, int qk_shift,
-                               int pv_shift, int sm_mode, int B, int S, int Dmax, int inv_shift);
+                               int pv_shift, int sm_mode, int B, int S, int Dmax, int inv_shift, int heads,
+                               long long hstride_q, long long hstride_k, long long hstride_v, long long hstride_o);
 int a4c_launch_attention_tc(const void* q, long long ldq, long long stride_q, const void* k, long long ldk,
                             long long stride_k, const void* v, long long ldv, long long stride_v, void* out,
                             long long ldo, long long stride_o, long long batch, int sq, int sk, int dh, int qk_shift,
                             int pv_shift, int rounding, int sm_mode, int B, int S, int Dmax, int inv_shift, int use_clb,
-                            int exp_kq, int* status_word, cudaStream_t stream);
+                            int exp_kq, int heads, long long hstride_q, long long hstride_k, long long hstride_v,
+                            long long hstride_o, int* status_word, cudaStream_t stream);
 
 // CTA-pair (cta_group::2) Dense: one 256 x 256 tile per two SMs (dense_tc2.cu); same argument rules as
 // a4c_launch_dense_tc.

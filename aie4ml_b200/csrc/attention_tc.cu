@@ -1,5 +1,5 @@
-// One attention head per launch, fused:  O_b = srs( softmax_u8( srs(Q_b . K_b^T) ) . V_b )  for every batch
-// entry b, with the scores and probabilities never leaving the SM.
+// Attention heads, fused:  O_bh = srs( softmax_u8( srs(Q_bh . K_bh^T) ) . V_bh )  for every batch entry b and head
+// h in one launch, with the scores and probabilities never leaving the SM.
 //
 // This is the chain  matmul_single::run (matmul.cpp:32-118, TRANSPOSE_B) -> softmax (softmax.cpp:20-88 HCCS,
 // :252-384 exp) -> matmul_single::run  of aie4ml, with every intermediate rounding and saturation kept:
@@ -9,7 +9,9 @@
 // The three kernels it replaces move the [rows, keys] score and probability matrices through HBM four times;
 // here HBM sees Q, K, V once and O once.
 //
-// Shape of the kernel (one CTA per SM, persistent over (batch entry, 128-query tile) items):
+// Shape of the kernel (one CTA per SM, persistent over (batch entry, 128-query tile, head) items, head fastest:
+// heads that are 64-byte column slices of one tensor share the 256-byte lines the TMA unit promotes to, so a line
+// is fetched from HBM once instead of once per head):
 //   warp 0      TMA producer: Q tile [128 x 64], K [128 keys x 64], V [128 keys x 64] per item, 64-byte swizzle,
 //               4-stage ring
 //   warp 1      MMA issuer: S = Q K^T (M128 N128 K64, both operands K-major) into one of two TMEM score
@@ -65,8 +67,9 @@ struct Tail {
 constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (size_t)GROUPS * P_BYTES + LUT_BYTES + sizeof(Tail);
 
 struct AttnArgs {
-    uint8_t* out; long long ldo, stride_o;
-    long long batch; int sq, m_tiles;
+    uint8_t* out; long long ldo, stride_o, hstride_o;
+    long long batch; int sq, m_tiles, heads;
+    int head_inner;   // tensor-map dimension order {64, heads, rows, batch} (heads are column slices) or {64, rows, heads, batch}
     // requantisation of the scores (1) and of the outputs (2)
     int shift1, shift2;
     uint32_t mask1, c01, mask2, c02;          // generic rounding constants
@@ -77,10 +80,11 @@ struct AttnArgs {
     int* status;
 };
 
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2,
+                                            int c3) {
     asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        :: "r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        :: "r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
 
 // K-major operand whose K extent is one 64-byte swizzle row: rows of 64 bytes, 8-row groups 512 bytes apart.
@@ -155,7 +159,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const long long num_items = g.batch * g.m_tiles;
+    // item = ((batch entry * query tiles) + query tile) * heads + head: the heads of one batch entry, which share
+    // their 256-byte-promoted L2 lines when they are column slices of one tensor, run at the same time
+    const long long num_items = g.batch * g.m_tiles * g.heads;
     // items of this CTA: blockIdx.x, + gridDim.x, ...; n is the CTA-local index
     const long long first = blockIdx.x;
     const int n_local = first < num_items ? (int)((num_items - first + gridDim.x - 1) / gridDim.x) : 0;
@@ -201,17 +207,25 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             bool ok = true;
             for (int n = 0; ok && n < n_local; ++n) {
                 const long long item = first + (long long)n * gridDim.x;
-                const int b = (int)(item / g.m_tiles);
-                const int m0 = (int)(item % g.m_tiles) * BM;
+                const int h = (int)(item % g.heads);
+                const long long t = item / g.heads;
+                const int b = (int)(t / g.m_tiles);
+                const int m0 = (int)(t % g.m_tiles) * BM;
                 const int stage = n % STAGES;
                 const uint32_t ph = (uint32_t)(n / STAGES) & 1u;
                 ok = mbar_wait(&tail->qkv_empty[stage], ph ^ 1u, abort_flag, g.status, 121);
                 if (!ok) break;
                 uint8_t* st = smem + (size_t)stage * STAGE_BYTES;
                 mbar_arrive_expect_tx(&tail->qkv_full[stage], STAGE_BYTES);
-                tma_load_3d(st, &tmap_q, &tail->qkv_full[stage], 0, m0, b);
-                tma_load_3d(st + TILE_BYTES, &tmap_k, &tail->qkv_full[stage], 0, 0, b);
-                tma_load_3d(st + 2 * TILE_BYTES, &tmap_v, &tail->qkv_full[stage], 0, 0, b);
+                if (g.head_inner) {
+                    tma_load_4d(st, &tmap_q, &tail->qkv_full[stage], 0, h, m0, b);
+                    tma_load_4d(st + TILE_BYTES, &tmap_k, &tail->qkv_full[stage], 0, h, 0, b);
+                    tma_load_4d(st + 2 * TILE_BYTES, &tmap_v, &tail->qkv_full[stage], 0, h, 0, b);
+                } else {
+                    tma_load_4d(st, &tmap_q, &tail->qkv_full[stage], 0, m0, h, b);
+                    tma_load_4d(st + TILE_BYTES, &tmap_k, &tail->qkv_full[stage], 0, 0, h, b);
+                    tma_load_4d(st + 2 * TILE_BYTES, &tmap_v, &tail->qkv_full[stage], 0, 0, h, b);
+                }
             }
         }
         __syncwarp();
@@ -273,8 +287,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         bool ok = true;
         for (int n = grp; ok && n < n_local; n += GROUPS) {
             const long long item = first + (long long)n * gridDim.x;
-            const long long b = item / g.m_tiles;
-            const int row = (int)(item % g.m_tiles) * BM + r;
+            const int h = (int)(item % g.heads);
+            const long long t = item / g.heads;
+            const long long b = t / g.m_tiles;
+            const int row = (int)(t % g.m_tiles) * BM + r;
             const uint32_t par = (uint32_t)(n >> 1) & 1u;
             ok = mbar_wait(&tail->s_full[grp], par, abort_flag, g.status, 124);
             if (!ok) break;
@@ -363,7 +379,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             tmem_ld_wait32(oa + 32);
             tc_fence_before();
             if (row < g.sq) {
-                uint8_t* orow = g.out + b * g.stride_o + (long long)row * g.ldo;
+                uint8_t* orow = g.out + b * g.stride_o + h * g.hstride_o + (long long)row * g.ldo;
 #pragma unroll
                 for (int c = 0; c < DH / 16; ++c) {
                     uint32_t w[4];
@@ -411,16 +427,23 @@ EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
-// 3-D uint8 map {64 bytes of head, rows, batch}; box {64, 128, 1}; 64-byte swizzle; rows past the end read as zero
-bool make_head_map(CUtensorMap* map, const void* base, long long rows, long long batch, long long ld, long long stride) {
+// 4-D uint8 map over the heads of a tensor, 64-byte swizzle, one box = 128 rows x 64 bytes of one head of one batch
+// entry; rows past the end read as zero.  Dimension order keeps the strides ascending: {64, heads, rows, batch} when
+// the heads are column slices of a row (head_inner), else {64, rows, heads, batch}.  Extents of one get a stride that
+// is merely valid.
+bool make_head_map(CUtensorMap* map, const void* base, long long rows, int heads, long long batch, long long ld,
+                   long long hstride, long long stride, bool head_inner) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) return false;
-    if (batch <= 1) stride = (rows > 0 ? rows : 1) * ld;
-    cuuint64_t dims[3] = {(cuuint64_t)DH, (cuuint64_t)rows, (cuuint64_t)(batch > 0 ? batch : 1)};
-    cuuint64_t strides[2] = {(cuuint64_t)ld, (cuuint64_t)stride};
-    cuuint32_t box[3] = {(cuuint32_t)DH, 128u, 1u};
-    cuuint32_t estr[3] = {1, 1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+    if (heads <= 1) hstride = head_inner ? 64 : (rows > 0 ? rows : 1) * ld;
+    if (batch <= 1) stride = (rows > 0 ? rows : 1) * ld * (head_inner || heads <= 1 ? 1 : heads);
+    const cuuint64_t nh = (cuuint64_t)(heads > 0 ? heads : 1), nb = (cuuint64_t)(batch > 0 ? batch : 1);
+    cuuint64_t dims[4] = {(cuuint64_t)DH, head_inner ? nh : (cuuint64_t)rows, head_inner ? (cuuint64_t)rows : nh, nb};
+    cuuint64_t strides[3] = {(cuuint64_t)(head_inner ? hstride : ld), (cuuint64_t)(head_inner ? ld : hstride),
+                             (cuuint64_t)stride};
+    cuuint32_t box[4] = {(cuuint32_t)DH, head_inner ? 1u : 128u, head_inner ? 128u : 1u, 1u};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -444,8 +467,11 @@ cudaError_t launch_mode(const CUtensorMap& mq, const CUtensorMap& mk, const CUte
 int a4c_attention_tc_supported(const void* q, long long ldq, long long stride_q, const void* k, long long ldk,
                                long long stride_k, const void* v, long long ldv, long long stride_v, const void* out,
                                long long ldo, long long stride_o, long long batch, int sq, int sk, int dh, int qk_shift,
-                               int pv_shift, int sm_mode, int B, int S, int Dmax, int inv_shift) {
-    if (sk != SK || dh != DH || sq < 1 || batch < 0) return A4C_ERR_UNSUPPORTED;
+                               int pv_shift, int sm_mode, int B, int S, int Dmax, int inv_shift, int heads,
+                               long long hstride_q, long long hstride_k, long long hstride_v, long long hstride_o) {
+    if (sk != SK || dh != DH || sq < 1 || batch < 0 || heads < 1) return A4C_ERR_UNSUPPORTED;
+    if (heads > 1 && (hstride_q % 16 || hstride_k % 16 || hstride_v % 16 || hstride_o % 16)) return A4C_ERR_ALIGNMENT;
+    if (heads > 1 && (hstride_q < 1 || hstride_k < 1 || hstride_v < 1 || hstride_o < 1)) return A4C_ERR_INVALID_ARG;
     if ((qk_shift == 0) != (pv_shift == 0)) return A4C_ERR_UNSUPPORTED;   // one rounding template serves both steps
     if (qk_shift < 0 || qk_shift > 31 || pv_shift < 0 || pv_shift > 31) return A4C_ERR_INVALID_ARG;
     if (sm_mode != 0 && sm_mode != 1) return A4C_ERR_INVALID_ARG;
@@ -455,8 +481,8 @@ int a4c_attention_tc_supported(const void* q, long long ldq, long long stride_q,
     if (batch > 1 && (stride_q % 16 || stride_k % 16 || stride_v % 16 || stride_o % 16)) return A4C_ERR_ALIGNMENT;
     if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15u) return A4C_ERR_ALIGNMENT;
     if (ldq < DH || ldk < DH || ldv < DH || ldo < DH) return A4C_ERR_INVALID_ARG;
-    const long long items = batch * ((sq + BM - 1) / BM);
-    if (batch > 2147483647LL || items > 2147483647LL) return A4C_ERR_TOO_LARGE;
+    const long long items = batch * ((sq + BM - 1) / BM) * heads;
+    if (batch > 2147483647LL || heads > 65535 || items > 2147483647LL) return A4C_ERR_TOO_LARGE;
     return A4C_OK;
 }
 
@@ -464,18 +490,24 @@ int a4c_launch_attention_tc(const void* q, long long ldq, long long stride_q, co
                             long long stride_k, const void* v, long long ldv, long long stride_v, void* out,
                             long long ldo, long long stride_o, long long batch, int sq, int sk, int dh, int qk_shift,
                             int pv_shift, int rounding, int sm_mode, int B, int S, int Dmax, int inv_shift, int use_clb,
-                            int exp_kq, int* status_word, cudaStream_t stream) {
+                            int exp_kq, int heads, long long hstride_q, long long hstride_k, long long hstride_v,
+                            long long hstride_o, int* status_word, cudaStream_t stream) {
     const int sup = a4c_attention_tc_supported(q, ldq, stride_q, k, ldk, stride_k, v, ldv, stride_v, out, ldo, stride_o,
-                                               batch, sq, sk, dh, qk_shift, pv_shift, sm_mode, B, S, Dmax, inv_shift);
+                                               batch, sq, sk, dh, qk_shift, pv_shift, sm_mode, B, S, Dmax, inv_shift,
+                                               heads, hstride_q, hstride_k, hstride_v, hstride_o);
     if (sup != A4C_OK) return sup;
     if (rounding < 0 || rounding >= A4C_RND_COUNT) return A4C_ERR_INVALID_ARG;
     if (batch == 0) return A4C_OK;
     CUtensorMap mq, mk, mv;
-    if (!make_head_map(&mq, q, sq, batch, ldq, stride_q) || !make_head_map(&mk, k, sk, batch, ldk, stride_k) ||
-        !make_head_map(&mv, v, sk, batch, ldv, stride_v))
+    // one dimension order for the three maps: heads innermost when every operand's heads are column slices of a row
+    const bool head_inner = heads > 1 && hstride_q < ldq && hstride_k < ldk && hstride_v < ldv;
+    if (!make_head_map(&mq, q, sq, heads, batch, ldq, hstride_q, stride_q, head_inner) ||
+        !make_head_map(&mk, k, sk, heads, batch, ldk, hstride_k, stride_k, head_inner) ||
+        !make_head_map(&mv, v, sk, heads, batch, ldv, hstride_v, stride_v, head_inner))
         return A4C_ERR_CUDA;
     AttnArgs g;
-    g.out = (uint8_t*)out; g.ldo = ldo; g.stride_o = stride_o; g.batch = batch; g.sq = sq;
+    g.out = (uint8_t*)out; g.ldo = ldo; g.stride_o = stride_o; g.hstride_o = heads > 1 ? hstride_o : 0; g.batch = batch;
+    g.sq = sq; g.heads = heads; g.head_inner = head_inner ? 1 : 0;
     g.m_tiles = (sq + BM - 1) / BM;
     g.shift1 = qk_shift; g.shift2 = pv_shift;
     const RoundParams r1 = make_round_params(qk_shift, rounding), r2 = make_round_params(pv_shift, rounding);
@@ -496,7 +528,7 @@ int a4c_launch_attention_tc(const void* q, long long ldq, long long stride_q, co
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const long long items = batch * g.m_tiles;
+    const long long items = batch * g.m_tiles * heads;
     const int grid = (int)(items < sms ? items : sms);
     cudaError_t err;
     if (qk_shift == 0) err = launch_mode<-1>(mq, mk, mv, g, grid, stream);

@@ -228,28 +228,50 @@ int a4c_add_f(const void* a, int64_t lda, const void* b, int64_t ldb, void* out,
     return finish();
 }
 
-int a4c_attention_i8_supported(const int8_t* q, int64_t ldq, int64_t stride_q, const int8_t* k, int64_t ldk,
-                               int64_t stride_k, const int8_t* v, int64_t ldv, int64_t stride_v, const int8_t* out,
-                               int64_t ldo, int64_t stride_o, int64_t batch, int sq, int sk, int dh, int qk_shift,
-                               int pv_shift, int sm_mode, int B, int S, int Dmax, int inv_shift) {
+int a4c_attention_heads_i8_supported(const int8_t* q, int64_t ldq, int64_t stride_q, int64_t hstride_q, const int8_t* k,
+                                     int64_t ldk, int64_t stride_k, int64_t hstride_k, const int8_t* v, int64_t ldv,
+                                     int64_t stride_v, int64_t hstride_v, const int8_t* out, int64_t ldo, int64_t stride_o,
+                                     int64_t hstride_o, int64_t batch, int heads, int sq, int sk, int dh, int qk_shift,
+                                     int pv_shift, int sm_mode, int B, int S, int Dmax, int inv_shift) {
     if (q == nullptr || k == nullptr || v == nullptr || out == nullptr) return A4C_ERR_INVALID_ARG;
     return a4c_attention_tc_supported(q, ldq, stride_q, k, ldk, stride_k, v, ldv, stride_v, out, ldo, stride_o, batch,
-                                      sq, sk, dh, qk_shift, pv_shift, sm_mode, B, S, Dmax, inv_shift);
+                                      sq, sk, dh, qk_shift, pv_shift, sm_mode, B, S, Dmax, inv_shift, heads, hstride_q,
+                                      hstride_k, hstride_v, hstride_o);
 }
 
-int a4c_attention_i8(const int8_t* q, int64_t ldq, int64_t stride_q, const int8_t* k, int64_t ldk, int64_t stride_k,
-                     const int8_t* v, int64_t ldv, int64_t stride_v, int8_t* out, int64_t ldo, int64_t stride_o,
-                     int64_t batch, int sq, int sk, int dh, int qk_shift, int pv_shift, int rounding, int sm_mode, int B,
-                     int S, int Dmax, int inv_shift, int use_clb, int exp_kq, void* stream) {
+int a4c_attention_heads_i8(const int8_t* q, int64_t ldq, int64_t stride_q, int64_t hstride_q, const int8_t* k, int64_t ldk,
+                           int64_t stride_k, int64_t hstride_k, const int8_t* v, int64_t ldv, int64_t stride_v,
+                           int64_t hstride_v, int8_t* out, int64_t ldo, int64_t stride_o, int64_t hstride_o, int64_t batch,
+                           int heads, int sq, int sk, int dh, int qk_shift, int pv_shift, int rounding, int sm_mode, int B,
+                           int S, int Dmax, int inv_shift, int use_clb, int exp_kq, void* stream) {
     if (q == nullptr || k == nullptr || v == nullptr || out == nullptr) return A4C_ERR_INVALID_ARG;
     if (!valid_round(rounding)) return A4C_ERR_INVALID_ARG;
     int* word = status_word();
     if (word == nullptr) return A4C_ERR_CUDA;
     const int rc = a4c_launch_attention_tc(q, ldq, stride_q, k, ldk, stride_k, v, ldv, stride_v, out, ldo, stride_o,
                                            batch, sq, sk, dh, qk_shift, pv_shift, rounding, sm_mode, B, S, Dmax,
-                                           inv_shift, use_clb, exp_kq, word, (cudaStream_t)stream);
+                                           inv_shift, use_clb, exp_kq, heads, hstride_q, hstride_k, hstride_v, hstride_o,
+                                           word, (cudaStream_t)stream);
     if (rc != A4C_OK) { if (rc == A4C_ERR_CUDA) note(cudaGetLastError()); return rc; }
     return finish();
+}
+
+int a4c_attention_i8_supported(const int8_t* q, int64_t ldq, int64_t stride_q, const int8_t* k, int64_t ldk,
+                               int64_t stride_k, const int8_t* v, int64_t ldv, int64_t stride_v, const int8_t* out,
+                               int64_t ldo, int64_t stride_o, int64_t batch, int sq, int sk, int dh, int qk_shift,
+                               int pv_shift, int sm_mode, int B, int S, int Dmax, int inv_shift) {
+    return a4c_attention_heads_i8_supported(q, ldq, stride_q, 0, k, ldk, stride_k, 0, v, ldv, stride_v, 0, out, ldo,
+                                            stride_o, 0, batch, 1, sq, sk, dh, qk_shift, pv_shift, sm_mode, B, S, Dmax,
+                                            inv_shift);
+}
+
+int a4c_attention_i8(const int8_t* q, int64_t ldq, int64_t stride_q, const int8_t* k, int64_t ldk, int64_t stride_k,
+                     const int8_t* v, int64_t ldv, int64_t stride_v, int8_t* out, int64_t ldo, int64_t stride_o,
+                     int64_t batch, int sq, int sk, int dh, int qk_shift, int pv_shift, int rounding, int sm_mode, int B,
+                     int S, int Dmax, int inv_shift, int use_clb, int exp_kq, void* stream) {
+    return a4c_attention_heads_i8(q, ldq, stride_q, 0, k, ldk, stride_k, 0, v, ldv, stride_v, 0, out, ldo, stride_o, 0,
+                                  batch, 1, sq, sk, dh, qk_shift, pv_shift, rounding, sm_mode, B, S, Dmax, inv_shift,
+                                  use_clb, exp_kq, stream);
 }
 
 int a4c_set_option(int option, int value) {

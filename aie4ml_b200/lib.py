@@ -69,6 +69,14 @@ SIGNATURES = {
     'a4c_attention_i8': (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64,
                                  c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    'a4c_attention_heads_i8_supported': (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
+                                                 c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
+                                                 c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                 c_int, c_int]),
+    'a4c_attention_heads_i8': (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p,
+                                       c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int,
+                                       c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                       c_void_p]),
     'a4c_add_sat': (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_int,
                             c_int, c_void_p]),
 }

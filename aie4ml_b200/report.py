@@ -55,7 +55,8 @@ def op_cost(plan, op: Dict[str, Any]) -> Dict[str, float]:
                 'ops': 2.0 * _numel(plan, op['out']) * K}
     if kind == 'attention':
         q, k = plan.views[op['q']], plan.views[op['k']]
-        nq, nk = _numel(plan, op['q']), _numel(plan, op['k'])
+        heads = int(op.get('heads', 1))
+        nq, nk = heads * _numel(plan, op['q']), heads * _numel(plan, op['k'])
         sk, dh = k.shape[-2], k.shape[-1]
         return {'bytes': 2 * nq + 2 * nk, 'ops': 2.0 * (nq // dh) * sk * dh * 2}
     if kind in ('layer_norm', 'softmax', 'add'):

@@ -111,7 +111,7 @@ class Plan:
 
     def __init__(self, ctx: BackendContext, device: Optional[str] = None, fuse_rowop_add: bool = True,
                  dense_algo: int = _lib.ALGO_AUTO, share_params: Optional['Plan'] = None, fuse_attention: bool = True,
-                 fuse_dense_chain: bool = True):
+                 fuse_dense_chain: bool = True, merge_attention_heads: bool = True):
         torch = _torch()
         self.ctx = ctx
         self.lib = _lib.load()
@@ -122,6 +122,7 @@ class Plan:
         self.dense_algo = int(dense_algo)
         self.fuse_rowop_add = bool(fuse_rowop_add)
         self.fuse_attention = bool(fuse_attention)
+        self.merge_attention_heads = bool(merge_attention_heads)
         self.fuse_dense_chain = bool(fuse_dense_chain)
         graph = ctx.ir.logical
         self.graph = graph
@@ -178,6 +179,8 @@ class Plan:
         self.buffers: Dict[str, Any] = {}
         if fuse_attention:
             self._fuse_attention()
+            if merge_attention_heads:
+                self._merge_attention_heads()
         self._keepalive: List[Any] = []
         if fuse_dense_chain:
             self._fuse_dense_chain()
@@ -190,6 +193,8 @@ class Plan:
             for key in ('lhs', 'rhs', 'out', 'addend', 'pre_addend', 'q', 'k', 'v'):
                 if op.get(key):
                     live.add(op[key])
+            for member in op.get('members', ()):
+                live.update(member.values())
         for name in sorted(live):
             self._view(name)
 
@@ -374,7 +379,8 @@ class Plan:
             self.ops = [op for i, op in enumerate(self.ops) if i not in drop]
 
     def _attention_args(self, op: Dict[str, Any]) -> tuple:
-        """Positional arguments of a4c_attention_i8 up to (not including) `rounding`, from the four views."""
+        """Positional arguments of a4c_attention_heads_i8 up to (not including) `rounding`, from the four views (of the
+        first head when the op covers several)."""
         name = op['name']
         q, k, v, o = (self._view(op[key]) for key in ('q', 'k', 'v', 'out'))
         q_off, bq, sq, dq, ldq, stq = collapse_batched(q, f'{name}: q')
@@ -383,8 +389,9 @@ class Plan:
         o_off, bo, so, do, ldo, sto = collapse_batched(o, f'{name}: output')
         if not (bq == bk == bv == bo and sk == sv and sq == so and dq == dk == dv == do):
             raise ValueError(f'{name}: q/k/v/output shapes do not form an attention head.')
-        return (self.ptr(q, q_off), ldq, stq, self.ptr(k, k_off), ldk, stk, self.ptr(v, v_off), ldv, stv,
-                self.ptr(o, o_off), ldo, sto, bq, sq, sk, dq, op['qk_shift'], op['pv_shift'])
+        hq, hk, hv, ho = op.get('head_strides', (0, 0, 0, 0))
+        return (self.ptr(q, q_off), ldq, stq, hq, self.ptr(k, k_off), ldk, stk, hk, self.ptr(v, v_off), ldv, stv, hv,
+                self.ptr(o, o_off), ldo, sto, ho, bq, op.get('heads', 1), sq, sk, dq, op['qk_shift'], op['pv_shift'])
 
     def _fuse_attention(self) -> None:
         """matmul(q, k^T) -> softmax (uint8) -> matmul(p, v) becomes one launch per head when the library has a
@@ -425,12 +432,58 @@ class Plan:
                 args = self._attention_args(op)
             except (NotImplementedError, ValueError):
                 continue
-            if self.lib.a4c_attention_i8_supported(*args, op['sm_mode'], op['B'], op['S'], op['Dmax'],
+            if self.lib.a4c_attention_heads_i8_supported(*args, op['sm_mode'], op['B'], op['S'], op['Dmax'],
                                                    op['inv_shift']) != 0:
                 continue
             replace[i] = op
             drop.update((h, j))
             self.fused.append(op['name'])
+        if replace:
+            self.ops = [replace.get(i, op) for i, op in enumerate(self.ops) if i not in drop]
+
+    def _merge_attention_heads(self) -> None:
+        """Fused attention ops that differ only in which column slice of the same four buffers they touch (the heads of
+        one layer) become one launch over (batch entry, head): a memory line that holds several heads is then fetched
+        once.  The merged op runs where the last head ran; nothing in between may touch the output buffer."""
+        same = ('qk_shift', 'pv_shift', 'rounding', 'sm_mode', 'B', 'S', 'Dmax', 'inv_shift', 'use_clb', 'exp_kq')
+        groups: Dict[tuple, List[int]] = {}
+        for i, op in enumerate(self.ops):
+            if op['kind'] != 'attention':
+                continue
+            vs = [self._view(op[key]) for key in ('q', 'k', 'v', 'out')]
+            key = tuple(op[k] for k in same) + tuple((v.root, v.shape, v.strides) for v in vs)
+            groups.setdefault(key, []).append(i)
+        drop, replace = set(), {}
+        for members in groups.values():
+            if len(members) < 2:
+                continue
+            offs = {i: [self._view(self.ops[i][key]).offset for key in ('q', 'k', 'v', 'out')] for i in members}
+            order = sorted(members, key=lambda i: offs[i][0])
+            first = offs[order[0]]
+            steps = [b - a for a, b in zip(first, offs[order[1]])]
+            if any(st <= 0 for st in steps):
+                continue
+            if any(offs[i][c] != first[c] + h * steps[c] for h, i in enumerate(order) for c in range(4)):
+                continue
+            out_root = self._view(self.ops[order[0]]['out']).root
+            lo, hi = min(members), max(members)
+            between = [self.ops[j] for j in range(lo, hi + 1) if j not in members]
+            if any(self._view(op[key]).root == out_root for op in between
+                   for key in ('lhs', 'rhs', 'out', 'addend', 'pre_addend', 'q', 'k', 'v') if op.get(key)):
+                continue
+            head0 = self.ops[order[0]]
+            merged = dict(head0, name='|'.join(self.ops[i]['name'] for i in order), heads=len(order), head_strides=tuple(steps),
+                          members=[{key: self.ops[i][key] for key in ('q', 'k', 'v', 'out')} for i in order])
+            try:
+                args = self._attention_args(merged)
+            except (NotImplementedError, ValueError):
+                continue
+            if self.lib.a4c_attention_heads_i8_supported(*args, merged['sm_mode'], merged['B'], merged['S'], merged['Dmax'],
+                                                         merged['inv_shift']) != 0:
+                continue
+            replace[hi] = merged
+            drop.update(i for i in members if i != hi)
+            self.fused.append(merged['name'])
         if replace:
             self.ops = [replace.get(i, op) for i, op in enumerate(self.ops) if i not in drop]
 
@@ -553,7 +606,7 @@ class Plan:
         if kind == 'attention':
             args = self._attention_args(op) + (ROUNDING_CODE[op['rounding']], op['sm_mode'], op['B'], op['S'],
                                                op['Dmax'], op['inv_shift'], op['use_clb'], op['exp_kq'])
-            return L.a4c_attention_i8, args
+            return L.a4c_attention_heads_i8, args
         if kind in ('layer_norm', 'softmax', 'add'):
             x, y = self._view(op['lhs']), self._view(op['out'])
             x_off, rows, cols, ldx = collapse_2d(x, f'{name}: input')

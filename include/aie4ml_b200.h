@@ -224,6 +224,25 @@ A4C_API int a4c_attention_i8(const int8_t* q, int64_t ldq, int64_t stride_q, con
                      void* stream);
 
 /*
+ * The same for `heads` heads per batch entry in one launch: head h of batch entry b starts at
+ * base + b * stride_* + h * hstride_* (bytes, multiples of 16) in each of q, k, v and out.  For the usual layout,
+ * heads as 64-byte column slices of [rows, heads * 64] tensors (what the reference's Split / Concat placeholders
+ * around the per-head MatMuls describe, src/aie4ml/passes/fold_views.py), hstride = 64 and the heads of one row share
+ * their memory lines, which then leave HBM once instead of once per head.  Results are those of `heads` calls of
+ * a4c_attention_i8.
+ */
+A4C_API int a4c_attention_heads_i8_supported(const int8_t* q, int64_t ldq, int64_t stride_q, int64_t hstride_q,
+                                     const int8_t* k, int64_t ldk, int64_t stride_k, int64_t hstride_k, const int8_t* v,
+                                     int64_t ldv, int64_t stride_v, int64_t hstride_v, const int8_t* out, int64_t ldo,
+                                     int64_t stride_o, int64_t hstride_o, int64_t batch, int heads, int sq, int sk, int dh,
+                                     int qk_shift, int pv_shift, int sm_mode, int B, int S, int Dmax, int inv_shift);
+A4C_API int a4c_attention_heads_i8(const int8_t* q, int64_t ldq, int64_t stride_q, int64_t hstride_q, const int8_t* k,
+                           int64_t ldk, int64_t stride_k, int64_t hstride_k, const int8_t* v, int64_t ldv, int64_t stride_v,
+                           int64_t hstride_v, int8_t* out, int64_t ldo, int64_t stride_o, int64_t hstride_o, int64_t batch,
+                           int heads, int sq, int sk, int dh, int qk_shift, int pv_shift, int rounding, int sm_mode, int B,
+                           int S, int Dmax, int inv_shift, int use_clb, int exp_kq, void* stream);
+
+/*
  * Elementwise out = saturate( round_shift( a + b, shift ) ) over [rows, cols] tensors of one dtype.
  * Replaces elementwise_add_kernel::run
  * (src/aie4ml/templates/nnet_utils/elementwise_add/elementwise_add.cpp:12-37; SHIFT, ROUNDING from

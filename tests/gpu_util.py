@@ -176,6 +176,34 @@ def attention(qkv, heads_at, *, qk_shift, pv_shift, tok, mode, B=0, S=0, Dmax=0,
     return out.cpu().numpy()
 
 
+def attention_heads(q, k, v, heads, *, qk_shift, pv_shift, tok, mode, B=0, S=0, Dmax=0, inv_shift=15, use_clb=False,
+                    exp_kq=0, layout='cols'):
+    """All heads of a layer in one launch: q [batch, sq, heads*64], k and v [batch, 128, heads*64] int8, head h in
+    columns [64h, 64h + 64).  Returns the [batch, sq, heads*64] output.  layout 'cols' hands the tensors over as they
+    are (heads = column slices, 64 bytes apart); 'blocks' stores every head as its own [rows, 64] matrix
+    ([batch, heads, rows, 64]) and converts the result back."""
+    L = a4c.load()
+    batch, sq, width = q.shape
+    sk = k.shape[1]
+    if layout == 'blocks':
+        blocks = lambda t: np.ascontiguousarray(t.reshape(batch, t.shape[1], heads, 64).transpose(0, 2, 1, 3))
+        qd, kd, vd = dev(blocks(q)), dev(blocks(k)), dev(blocks(v))
+        out = torch.full((batch, heads, sq, 64), 0x5A, dtype=torch.int8, device='cuda')
+        geo = lambda rows: (64, heads * rows * 64, rows * 64)
+    else:
+        qd, kd, vd = dev(q), dev(k), dev(v)
+        out = torch.full((batch, sq, width), 0x5A, dtype=torch.int8, device='cuda')
+        geo = lambda rows: (width, rows * width, 64)
+    args = (qd.data_ptr(), *geo(sq), kd.data_ptr(), *geo(sk), vd.data_ptr(), *geo(sk), out.data_ptr(), *geo(sq), batch, heads,
+            sq, sk, 64, qk_shift, pv_shift)
+    sm = (0 if mode == 'hccs' else 1, B, S, Dmax, inv_shift)
+    a4c.check(L.a4c_attention_heads_i8_supported(*args, *sm), 'a4c_attention_heads_i8_supported')
+    a4c.check(L.a4c_attention_heads_i8(*args, ROUNDING_CODE[tok], *sm, int(use_clb), exp_kq, stream()), 'a4c_attention_heads_i8')
+    a4c.device_status(stream())
+    res = out.cpu().numpy()
+    return res.transpose(0, 2, 1, 3).reshape(batch, sq, width) if layout == 'blocks' else res
+
+
 def dense16(a, w_kn, bias, *, shift, tok, relu, out_dtype='int8'):
     """int16 activations against int8 (32-bit wrapping accumulator) or int16 (64-bit accumulator) weights."""
     L = a4c.load()

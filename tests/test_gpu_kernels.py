@@ -433,6 +433,28 @@ def test_fused_attention_head_equals_matmul_softmax_matmul(tok, mode):
     assert (untouched == 0x5A).all()
 
 
+@pytest.mark.parametrize('heads,sq,layout', [(4, 128, 'cols'), (3, 200, 'cols'), (1, 77, 'cols'), (4, 128, 'blocks'),
+                                             (2, 150, 'blocks')])
+@pytest.mark.parametrize('mode', ['exp', 'hccs'])
+def test_fused_attention_all_heads_of_a_layer_in_one_launch(heads, sq, layout, mode):
+    """(batch entry, head) items with the head index fastest; query counts that are not a multiple of the 128-row tile;
+    every head against the oracle's three-step chain; unused width stays untouched."""
+    import gpu_util as G
+
+    rng = np.random.default_rng(40 + heads)
+    batch, width = 150, heads * 64
+    q = np.clip(np.rint(rng.normal(0, 45, (batch, sq, width))), -128, 127).astype(np.int8)
+    k = np.clip(np.rint(rng.normal(0, 45, (batch, 128, width))), -128, 127).astype(np.int8)
+    v = rng.integers(-128, 128, (batch, 128, width)).astype(np.int8)
+    sm = dict(exp_kq=23) if mode == 'exp' else dict(B=200, S=3, Dmax=66)
+    got = G.attention_heads(q, k, v, heads, qk_shift=9, pv_shift=8, tok='positive_inf', mode=mode, layout=layout, **sm)
+    for h in range(heads):
+        cols = slice(64 * h, 64 * h + 64)
+        want = _attention_oracle(q[..., cols], k[..., cols], v[..., cols], qk_shift=9, pv_shift=8, tok='positive_inf',
+                                 mode=mode, **sm)
+        np.testing.assert_array_equal(got[..., cols], want, err_msg=f'head {h}')
+
+
 def test_fused_attention_other_softmax_parameters_and_rejections():
     import gpu_util as G
     from aie4ml_b200 import lib as a4c

@@ -41,8 +41,11 @@ def test_cfg2_dense(shape):
 def test_cfg3_encoder_block(softmax, rounding):
     model = _check(*W.encoder_cfg3(3, softmax=softmax, rounding=rounding))
     kinds = [op['kind'] for op in model.plan.ops]
-    # every head's QK^T -> softmax -> AV chain runs as one fused launch; scores and probabilities have no buffer
-    assert kinds.count('attention') == 4 and kinds.count('matmul') == 0 and kinds.count('softmax') == 0
+    # every head's QK^T -> softmax -> AV chain is fused and the four heads share one launch; scores and
+    # probabilities have no buffer
+    assert kinds.count('attention') == 1 and kinds.count('matmul') == 0 and kinds.count('softmax') == 0
+    att = next(op for op in model.plan.ops if op['kind'] == 'attention')
+    assert att['heads'] == 4 and att['head_strides'] == (64, 64, 64, 64) and len(model.plan.ops) == 9
     assert kinds.count('layer_norm') == 2 and not any(n.startswith(('qk', 'sm')) for n in model.plan.buffers)
     # both residual Adds ride inside their LayerNorm launches
     assert kinds.count('add') == 0 and sum(1 for op in model.plan.ops if op.get('pre_addend')) == 2
