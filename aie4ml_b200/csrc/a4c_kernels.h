@@ -58,6 +58,7 @@ int a4c_launch_softmax_fast(const int8_t* x, long long ldx, const void* addend, 
 
 // Tuning overrides of rowops_fast.cu (0 = automatic, negative leaves a value unchanged).
 void a4c_rowops_fast_tuning(int chunks_per_lane, int min_stages);
+void a4c_rowops_fast_contig(int on);
 
 // tcgen05 batched MatMul (bmm_tc.cu).  B stored [N,K] when trans_b (K-major operand) or [K,N] (MN-major operand).
 int a4c_bmm_tc_supported(const void* A, long long lda, long long stride_a, const void* B, long long ldb,

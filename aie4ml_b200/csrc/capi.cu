@@ -299,6 +299,10 @@ int a4c_set_option(int option, int value) {
         a4c_rowops_fast_tuning(-1, value);
         return A4C_OK;
     }
+    if (option == A4C_OPT_ROWOP_CONTIG_COPY && (value == 0 || value == 1)) {
+        a4c_rowops_fast_contig(value);
+        return A4C_OK;
+    }
     return A4C_ERR_INVALID_ARG;
 }
 

@@ -97,6 +97,20 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
     return d;
 }
+// Sum / maximum over the G = 2^k adjacent lanes that share a row.  A whole warp (G = 32) uses the warp-wide reduce
+// instruction.  Given several member masks in one warp that instruction is replayed once per mask (eight times for
+// G = 4: 1.3x the run time of a whole LayerNorm at 256 columns), so smaller groups use an xor butterfly, which costs
+// log2(G) shuffles for every group at once.
+__device__ __forceinline__ int group_sum(int v, int G) {
+    if (G == 32) return __reduce_add_sync(0xffffffffu, v);
+    for (int d = G >> 1; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+    return v;
+}
+__device__ __forceinline__ int group_max(int v, int G) {
+    if (G == 32) return (int)__reduce_max_sync(0xffffffffu, v);
+    for (int d = G >> 1; d > 0; d >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, d));
+    return v;
+}
 // float 2^23 + byte K of w (bytes taken as unsigned)
 template <int K>
 __device__ __forceinline__ float byte_to_f23(uint32_t w) {
@@ -109,6 +123,7 @@ __device__ __forceinline__ float byte_to_f23(uint32_t w) {
 // puts those rows on different banks.
 struct RowGeom {
     int nchunks, G, R, pitch;
+    int contig;   // the R rows of an item are adjacent in memory and in the slot: one copy brings all of them
 };
 
 // One warp's ring.  A slot holds R input rows and, with a fused Add, R addend rows behind them.
@@ -123,6 +138,7 @@ struct Ring {
     uint32_t row_bytes;   // bytes copied per row
     uint32_t pitch;       // distance between rows inside a slot (row_bytes + bank-spreading pad)
     int R;
+    int contig;           // rows are adjacent in global memory and pitch == row_bytes: one copy per item and operand
 };
 
 // Whole warp: lane 0 arms the barrier, lane r (and r + 32, ...) issues the copies of row r, so the R rows of
@@ -134,6 +150,15 @@ __device__ __forceinline__ void ring_issue(const Ring& c, long long item, int st
     if (nrows > c.R) nrows = c.R;
     const uint32_t bar = c.bars + stage * 8;
     const uint32_t dst = c.slots + stage * c.slot_bytes;
+    if (c.contig) {
+        if (lane == 0) {
+            const uint32_t bytes = (uint32_t)nrows * c.row_bytes;
+            mbar_expect_tx(bar, bytes * (c.addend ? 2u : 1u));
+            bulk_load(dst, c.x + row0 * c.ldx, bytes, bar);
+            if (c.addend) bulk_load(dst + c.add_off, c.addend + row0 * c.ldadd, bytes, bar);
+        }
+        return;
+    }
     if (lane == 0) mbar_expect_tx(bar, (uint32_t)nrows * c.row_bytes * (c.addend ? 2u : 1u));
     if (lane < (int)nrows) {
         bulk_load(dst + lane * c.pitch, c.x + (row0 + lane) * c.ldx, c.row_bytes, bar);
@@ -232,7 +257,7 @@ __global__ void __launch_bounds__(kThreads) layernorm_fast_kernel(LnFastArgs a) 
         reinterpret_cast<float*>(smem)[kParamFloats + pos] = ((float)a.beta[c] + a.c0_out) * TWO_M64;
     }
     Ring rc;
-    rc.R = R;
+    rc.R = R; rc.contig = a.geom.contig;
     rc.row_bytes = (uint32_t)cols; rc.pitch = (uint32_t)a.geom.pitch;
     rc.add_off = (uint32_t)(R * a.geom.pitch);
     rc.slot_bytes = (uint32_t)(R * a.geom.pitch) * (RING_ADD ? 2u : 1u);
@@ -257,7 +282,6 @@ __global__ void __launch_bounds__(kThreads) layernorm_fast_kernel(LnFastArgs a) 
 
     const float out_mul = __int_as_float((127 - (a.s_out + 85)) << 23);  // 2^-(s_out + 85)
     const float c0g = (float)a.c0_gamma;
-    const uint32_t group_mask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (sub * G));
     const int clamp_threshold = (32767 * 128) / a.gamma_absmax;  // inv_std above this may overflow int16
     const bool nearest = a.rounding == A4C_RND_CONV_EVEN || a.rounding == A4C_RND_POSITIVE_INF ||
                          a.rounding == A4C_RND_NEGATIVE_INF;
@@ -311,8 +335,8 @@ __global__ void __launch_bounds__(kThreads) layernorm_fast_kernel(LnFastArgs a) 
             sx0 = dp4a_ss(xv[j].z, 0x01010101u, sx0); sq0 = dp4a_ss(xv[j].z, xv[j].z, sq0);
             sx1 = dp4a_ss(xv[j].w, 0x01010101u, sx1); sq1 = dp4a_ss(xv[j].w, xv[j].w, sq1);
         }
-        const int sum_x = __reduce_add_sync(group_mask, sx0 + sx1);
-        const int sum_sq = __reduce_add_sync(group_mask, sq0 + sq1);
+        const int sum_x = group_sum(sx0 + sx1, G);
+        const int sum_sq = group_sum(sq0 + sq1, G);
         // layer_norm.cpp:23-31
         const int mu = (sum_x + (cols >> 1)) >> a.log2c;
         const int centered = (int)((uint32_t)sum_sq - 2u * (uint32_t)mu * (uint32_t)sum_x +
@@ -451,7 +475,7 @@ __global__ void __launch_bounds__(kThreads) softmax_fast_kernel(SmFastArgs a) {
         __syncthreads();
     }
     Ring rc;
-    rc.R = R;
+    rc.R = R; rc.contig = a.geom.contig;
     rc.row_bytes = (uint32_t)cols; rc.pitch = (uint32_t)a.geom.pitch;
     rc.add_off = (uint32_t)(R * a.geom.pitch);
     rc.slot_bytes = (uint32_t)(R * a.geom.pitch) * (HAS_ADD ? 2u : 1u);
@@ -476,7 +500,6 @@ __global__ void __launch_bounds__(kThreads) softmax_fast_kernel(SmFastArgs a) {
     const int numer = 255 << a.inv_shift;  // inv_shift <= 22 on this path
     const float numer_f = (float)numer;     // exact: 255 * 2^k
     const float out_mul = __int_as_float((127 - (a.inv_shift + 85)) << 23);  // 2^-(inv_shift + 85)
-    const uint32_t group_mask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (sub * G));
     const uint32_t lane_in_slot = (uint32_t)(sub * a.geom.pitch + gl * 16);
     const long long step_rows = total_warps * R;
     long long row = warp_global * R + sub;
@@ -517,7 +540,7 @@ __global__ void __launch_bounds__(kThreads) softmax_fast_kernel(SmFastArgs a) {
 #pragma unroll
             for (int w = 0; w < 4; ++w) mx = __vimax3_u16x2(mx, prmt(w4[w], 0, 0x4240), prmt(w4[w], 0, 0x4341));
         }
-        const int m = (int)__reduce_max_sync(group_mask, max(mx & 0xFFFFu, mx >> 16));
+        const int m = group_max((int)max(mx & 0xFFFFu, mx >> 16), G);
         const uint32_t m4 = (uint32_t)m * 0x01010101u;
 
         // scores (kept in registers for the normalisation pass) and their sum
@@ -540,7 +563,7 @@ __global__ void __launch_bounds__(kThreads) softmax_fast_kernel(SmFastArgs a) {
             }
         }
         // exact: a lane adds at most 32 scores <= 32767 (scaled by 2^-64)
-        const int sum = __reduce_add_sync(group_mask, __float2int_rn((fs0 + fs1) * TWO_P64));
+        const int sum = group_sum(__float2int_rn((fs0 + fs1) * TWO_P64), G);
         const int s = sum > 0 ? sum : 1;
         int inv;
         if (CLB) {
@@ -595,7 +618,9 @@ __global__ void __launch_bounds__(kThreads) softmax_fast_kernel(SmFastArgs a) {
 int g_min_stages = 0;
 int g_chunks_per_lane = 0;
 
-RowGeom make_geom(int cols, int preferred_nch) {
+int g_contig = 1;   // A4C_OPT_ROWOP_CONTIG_COPY
+
+RowGeom make_geom(int cols, int preferred_nch, bool rows_adjacent) {
     RowGeom g;
     g.nchunks = cols / 16;
     const int target = g_chunks_per_lane > 0 ? g_chunks_per_lane : preferred_nch;
@@ -603,7 +628,8 @@ RowGeom make_geom(int cols, int preferred_nch) {
     while (G * target < g.nchunks && G < 32) G <<= 1;
     g.G = G;
     g.R = 32 / G;
-    g.pitch = cols + ((G < 8 && cols % 128 == 0) ? G * 16 : 0);
+    g.contig = (g_contig && rows_adjacent && g.R > 1) ? 1 : 0;
+    g.pitch = cols + ((!g.contig && G < 8 && cols % 128 == 0) ? G * 16 : 0);
     return g;
 }
 
@@ -635,6 +661,8 @@ void plan_launch(size_t fixed, size_t slot, long long n_items, int* stages, size
 
 }  // namespace
 
+void a4c_rowops_fast_contig(int on) { g_contig = on ? 1 : 0; }
+
 void a4c_rowops_fast_tuning(int chunks_per_lane, int min_stages) {
     if (chunks_per_lane >= 0) g_chunks_per_lane = chunks_per_lane;
     if (min_stages >= 0) g_min_stages = min_stages;
@@ -665,7 +693,7 @@ int a4c_launch_layernorm_fast(const int8_t* x, long long ldx, const int16_t* gam
         default: break;
     }
     a.c0_out += (float)(128 << s_out);  // outputs are produced biased by +128
-    a.geom = make_geom(cols, 4);   // measured best at every row length from 128 to 2048
+    a.geom = make_geom(cols, 4, ldx == cols && (!addend || ldadd == cols));   // 4: measured best from 128 to 2048 columns
     const int nch = (a.geom.nchunks + a.geom.G - 1) / a.geom.G;
     if (nch != 1 && nch != 2 && nch != 4) return A4C_ERR_UNSUPPORTED;
     const size_t fixed = (size_t)nch * 4 * 32 * 4 * 4 * 2;
@@ -707,7 +735,7 @@ int a4c_launch_softmax_fast(const int8_t* x, long long ldx, const void* addend, 
     a.rows = rows; a.cols = cols; a.mode = mode; a.B = B; a.S = S; a.Dmax = Dmax; a.inv_shift = inv_shift;
     a.use_clb = use_clb; a.exp_kq = exp_kq; a.status = status;
     // four chunks per lane keep 64 scores in registers: worth it only with the fused Add on long rows
-    a.geom = make_geom(cols, (addend && cols >= 512) ? 4 : 2);
+    a.geom = make_geom(cols, (addend && cols >= 512) ? 4 : 2, ldx == cols && (!addend || ldadd == cols));
     const int nch = (a.geom.nchunks + a.geom.G - 1) / a.geom.G;
     if (nch != 1 && nch != 2 && nch != 4) return A4C_ERR_UNSUPPORTED;
     const size_t slot = (size_t)a.geom.R * a.geom.pitch * (addend ? 2 : 1);

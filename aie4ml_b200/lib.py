@@ -27,6 +27,7 @@ OPT_ROWOP_PATH = 0
 OPT_BMM_PATH = 1
 OPT_ROWOP_CHUNKS_PER_LANE = 2
 OPT_ROWOP_MIN_STAGES = 3
+OPT_ROWOP_CONTIG_COPY = 6
 OPT_MLP_PATH = 4
 OPT_DENSE_RESIDENT_W = 5
 

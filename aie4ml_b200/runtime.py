@@ -483,7 +483,8 @@ class Plan:
                 continue
             replace[hi] = merged
             drop.update(i for i in members if i != hi)
-            self.fused.append(merged['name'])
+            singles = {self.ops[i]['name'] for i in members}
+            self.fused = [f for f in self.fused if f not in singles] + [merged['name']]
         if replace:
             self.ops = [replace.get(i, op) for i, op in enumerate(self.ops) if i not in drop]
 

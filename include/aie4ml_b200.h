@@ -58,6 +58,7 @@ extern "C" {
 /* Tuning of the bandwidth-oriented row kernels (results do not depend on either): */
 #define A4C_OPT_ROWOP_CHUNKS_PER_LANE 2 /* 0 = automatic (default), else 1, 2 or 4: 16-element chunks of one row per lane */
 #define A4C_OPT_ROWOP_MIN_STAGES 3      /* 0 = automatic (default), else 2..4: least depth of the per-warp copy ring */
+#define A4C_OPT_ROWOP_CONTIG_COPY 6     /* rows adjacent in memory and several rows per warp item: 1 = one bulk copy per item, 0 = one per row */
 
 /* Library version (major*10000 + minor*100 + patch). */
 A4C_API int a4c_version(void);

@@ -204,11 +204,12 @@ def test_bmm_attention_shapes(bmm_path):
                                   oracle.matmul(a, b, shift=4, tok='floor', transpose_a=True, out_dtype='int16'))
 
 
-@pytest.fixture(params=['auto', 'generic', 'chunks1', 'chunks2', 'chunks4'])
+@pytest.fixture(params=['auto', 'generic', 'chunks1', 'chunks2', 'chunks4', 'row_copies'])
 def rowop_path(request):
     """Runs a row-op test with automatic kernel selection (bandwidth-oriented kernels where they
-    apply), with the generic integer kernels forced, and with every work split of the
-    bandwidth-oriented kernels forced (16-element chunks per lane; shortest copy ring)."""
+    apply), with the generic integer kernels forced, with every work split of the
+    bandwidth-oriented kernels forced (16-element chunks per lane; shortest copy ring), and with one
+    bulk copy per row instead of one per group of adjacent rows."""
     from aie4ml_b200 import lib as a4c
 
     L = a4c.load()
@@ -216,7 +217,10 @@ def rowop_path(request):
     if request.param.startswith('chunks'):
         assert L.a4c_set_option(a4c.OPT_ROWOP_CHUNKS_PER_LANE, int(request.param[-1])) == 0
         assert L.a4c_set_option(a4c.OPT_ROWOP_MIN_STAGES, 2) == 0
+    if request.param == 'row_copies':
+        assert L.a4c_set_option(a4c.OPT_ROWOP_CONTIG_COPY, 0) == 0
     yield request.param
+    assert L.a4c_set_option(a4c.OPT_ROWOP_CONTIG_COPY, 1) == 0
     assert L.a4c_set_option(a4c.OPT_ROWOP_PATH, 0) == 0
     assert L.a4c_set_option(a4c.OPT_ROWOP_CHUNKS_PER_LANE, 0) == 0
     assert L.a4c_set_option(a4c.OPT_ROWOP_MIN_STAGES, 0) == 0
