@@ -69,6 +69,7 @@ class CudaModel:
             self.plan = Plan(self._ctx, fuse_rowop_add=bool(fusion.get('rowop_add', True)),
                              fuse_attention=bool(fusion.get('attention', True)),
                              merge_attention_heads=bool(fusion.get('attention_heads', True)),
+                             merge_parallel_dense=bool(fusion.get('parallel_dense', True)),
                              fuse_dense_chain=bool(fusion.get('dense_chain', True)),
                              dense_algo=int(self._ctx.aie_config.get('DenseAlgo', 0)))
         return 0

@@ -111,7 +111,7 @@ class Plan:
 
     def __init__(self, ctx: BackendContext, device: Optional[str] = None, fuse_rowop_add: bool = True,
                  dense_algo: int = _lib.ALGO_AUTO, share_params: Optional['Plan'] = None, fuse_attention: bool = True,
-                 fuse_dense_chain: bool = True, merge_attention_heads: bool = True):
+                 fuse_dense_chain: bool = True, merge_attention_heads: bool = True, merge_parallel_dense: bool = True):
         torch = _torch()
         self.ctx = ctx
         self.lib = _lib.load()
@@ -123,6 +123,7 @@ class Plan:
         self.fuse_rowop_add = bool(fuse_rowop_add)
         self.fuse_attention = bool(fuse_attention)
         self.merge_attention_heads = bool(merge_attention_heads)
+        self.merge_parallel_dense = bool(merge_parallel_dense)
         self.fuse_dense_chain = bool(fuse_dense_chain)
         graph = ctx.ir.logical
         self.graph = graph
@@ -177,6 +178,9 @@ class Plan:
         self.fused: List[str] = []
         self.views: Dict[str, View] = {}
         self.buffers: Dict[str, Any] = {}
+        self.synthetic: Dict[str, Tuple[int, ...]] = {}     # tensors the plan adds (name -> shape): merged outputs
+        if merge_parallel_dense:
+            self._merge_parallel_dense()
         if fuse_attention:
             self._fuse_attention()
             if merge_attention_heads:
@@ -226,9 +230,8 @@ class Plan:
         if name in self.views:
             return self.views[name]
         torch = _torch()
-        t = self.graph.tensors[name]
         fmt = self.fmt[name]
-        shape = tuple(int(s) for s in t.shape)
+        shape = self.synthetic[name] if name in self.synthetic else tuple(int(s) for s in self.graph.tensors[name].shape)
         if name in self.alias:
             parent, axis, start = self.alias[name]
             pv = self._view(parent)
@@ -293,6 +296,52 @@ class Plan:
                 if op.get('fused_out'):
                     op['out'] = op.pop('fused_out')
             self.ops = [op for i, op in enumerate(self.ops) if i not in drop]
+
+    def _merge_parallel_dense(self) -> None:
+        """Dense layers that read the same tensor with the same requantisation (the Q / K / V projections of an
+        attention layer) become ONE Dense over the concatenated weights: the input is read once, and the outputs
+        become column slices of one wider tensor.  Each output must own its storage so far (not a view, not a
+        graph output) and be a whole number of 16-byte pieces wide."""
+        graph = self.graph
+        groups: Dict[tuple, List[int]] = {}
+        for i, op in enumerate(self.ops):
+            if (op['kind'] != 'dense' or op['transpose_lhs'] or op['lhs_dtype'] not in ('int8', 'uint8')
+                    or op.get('rhs_dtype', 'int8') != 'int8' or op['out_dtype'] not in ('int8', 'uint8')):
+                continue
+            out = op['out']
+            if out in self.alias or out in graph.output_tensor_names or op['N'] % 16:
+                continue
+            lead = tuple(int(d) for d in graph.tensors[out].shape[:-1])
+            key = (op['lhs'], op['K'], op['shift'], op['rounding'], op['relu'], op['out_dtype'], op['lhs_dtype'], lead)
+            groups.setdefault(key, []).append(i)
+        replace, drop = {}, set()
+        for key, members in groups.items():
+            if len(members) < 2:
+                continue
+            layers = [self.ops[i] for i in members]
+            lead = key[-1]
+            total = sum(l['N'] for l in layers)
+            name = '|'.join(l['out'] for l in layers)
+            self.synthetic[name] = lead + (total,)
+            self.fmt[name] = self.fmt[layers[0]['out']]
+            start = 0
+            for l in layers:
+                self._add_alias(l['out'], name, len(lead), start, l['name'])
+                start += l['N']
+            merged_name = '|'.join(l['name'] for l in layers)
+            weight = f'{merged_name}/weights'
+            self.params_np[weight] = np.concatenate([self.params_np.pop(l['weight']) for l in layers], axis=0)
+            bias = None
+            if any(l['bias'] for l in layers):
+                bias = f'{merged_name}/bias'
+                self.params_np[bias] = np.concatenate(
+                    [self.params_np.pop(l['bias']) if l['bias'] else np.zeros(l['N'], dtype=np.int32) for l in layers])
+            # at the first member's place: the shared input exists there, and no output is needed any earlier
+            replace[members[0]] = dict(layers[0], name=merged_name, out=name, N=total, weight=weight, bias=bias)
+            drop.update(members[1:])
+            self.fused.append(merged_name)
+        if replace:
+            self.ops = [replace.get(i, op) for i, op in enumerate(self.ops) if i not in drop]
 
     def _fuse_dense_chain(self) -> None:
         """Consecutive Dense layers whose intermediates feed nothing else become one `mlp` op when the library

@@ -91,6 +91,7 @@ class HostPipeline:
         for _ in range(depth - 1):
             self.plans.append(Plan(ctx, device=str(first.device), fuse_rowop_add=first.fuse_rowop_add,
                                    fuse_attention=first.fuse_attention, merge_attention_heads=first.merge_attention_heads,
+                                   merge_parallel_dense=first.merge_parallel_dense,
                                    fuse_dense_chain=first.fuse_dense_chain,
                                    dense_algo=first.dense_algo,
                                    share_params=first))

@@ -45,7 +45,11 @@ def test_cfg3_encoder_block(softmax, rounding):
     # probabilities have no buffer
     assert kinds.count('attention') == 1 and kinds.count('matmul') == 0 and kinds.count('softmax') == 0
     att = next(op for op in model.plan.ops if op['kind'] == 'attention')
-    assert att['heads'] == 4 and att['head_strides'] == (64, 64, 64, 64) and len(model.plan.ops) == 9
+    assert att['heads'] == 4 and att['head_strides'] == (64, 64, 64, 64)
+    # the Q / K / V projections read the same tensor with the same requantisation: one Dense over 768 outputs
+    assert len(model.plan.ops) == 7 and model.plan.ops[0]['kind'] == 'dense' and model.plan.ops[0]['N'] == 768
+    separate = _check(*W.encoder_cfg3(3, softmax=softmax, rounding=rounding), FusionPolicy={'parallel_dense': False})
+    assert len(separate.plan.ops) == 9 and separate.plan.ops[0]['N'] == 256
     assert kinds.count('layer_norm') == 2 and not any(n.startswith(('qk', 'sm')) for n in model.plan.buffers)
     # both residual Adds ride inside their LayerNorm launches
     assert kinds.count('add') == 0 and sum(1 for op in model.plan.ops if op.get('pre_addend')) == 2
@@ -66,8 +70,10 @@ def test_cfg4_rowop_plus_add_fused_and_unfused(op):
 
 def test_cfg5_wide_mlp_with_fanout_and_concat():
     model = _check(*W.wide_mlp_cfg5(300))
-    # both branch tails write straight into the concat buffer: no copy kernel, 10 dense launches
-    assert len(model.plan.launches) == 10
+    # both branch tails write straight into the concat buffer: no copy kernel; the two first layers read the same
+    # input and run as one Dense over 2048 outputs: 9 dense launches
+    assert len(model.plan.launches) == 9 and model.plan.ops[0]['N'] == 2048
+    assert len(_check(*W.wide_mlp_cfg5(300), FusionPolicy={'parallel_dense': False}).plan.launches) == 10
     assert model.plan.views['b0_fc3_out'].root == model.plan.views['b1_fc3_out'].root == 'cat_out'
 
 
