@@ -30,10 +30,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait.  Returns false when the CTA is aborting (this wait or another one gave up).
-static __device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                       int code) {
-    if (mbar_try_wait(bar, parity)) return true;
+// Bounded wait.  Returns false when the CTA is aborting (this wait or another one gave up).  The first probe is
+// inline: an out-of-line call costs several hundred cycles in these kernels even when the barrier has long
+// completed (measured with clock stamps: 21 cycles for the probe, ~470 for the call), and the MMA issuer pays that
+// on every operand stage.
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                            int code) {
     const uint64_t t0 = a4c_globaltimer();
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -48,6 +50,15 @@ static __device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, vo
     }
 }
 
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+    // a probe that finds the phase incomplete suspends the thread for a while by itself: a few of them cover the
+    // ordinary waits without leaving the caller
+#pragma unroll 1
+    for (int i = 0; i < 8; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, status, code);
+}
+
 // Same contract, but polls with the non-suspending test_wait: for a single-thread role whose wake-up latency
 // sits on the critical path (the MMA issuer waiting for an accumulator buffer).
 __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
@@ -59,9 +70,8 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-static __device__ __noinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                            int code) {
-    if (mbar_test_wait(bar, parity)) return true;
+static __device__ __noinline__ bool mbar_wait_spin_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                 int* status, int code) {
     const uint64_t t0 = a4c_globaltimer();
     for (uint32_t it = 1;; ++it) {
         if (mbar_test_wait(bar, parity)) return true;
@@ -74,6 +84,13 @@ static __device__ __noinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parit
             }
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                               int code) {
+#pragma unroll 1
+    for (int i = 0; i < 512; ++i)
+        if (mbar_test_wait(bar, parity)) return true;
+    return mbar_wait_spin_slow(bar, parity, abort_flag, status, code);
 }
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
