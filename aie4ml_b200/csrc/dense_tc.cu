@@ -12,9 +12,9 @@
 //              stage; tcgen05.commit releases the stage; accumulators live in TMEM, two of them
 //              (2 x 256 columns) so the epilogue of tile i overlaps the main loop of tile i+1
 //   warps 2-9  epilogue, two groups of four warps on alternate tiles (group g owns accumulator g): tcgen05.ld
-//              of 64 columns at a time (lane = row) with the next 64 in flight, bias from a resident
-//              shared-memory copy, requantise, pack four int8 per word into the warp's swizzled 32 x 64-byte
-//              staging patch, TMA store; the accumulator goes back to the issuer at half-tile
+//              of 64 columns at a time (lane = row), bias from a resident shared-memory copy, requantise, pack
+//              four int8 per word into the warp's swizzled 32 x 64-byte staging patch, TMA store; the accumulator
+//              goes back to the issuer once its last 64 columns are in registers
 // Tile order: normally CTA c takes global tiles c, c + grid, ... (column tile fastest) and every stage carries an
 // A tile and a W tile.  For K <= 512 with enough row tiles, a CTA instead keeps the whole K extent of ONE weight
 // tile resident in shared memory (loaded once) and the ring holds A tiles only, up to eight of them, so several
@@ -337,33 +337,26 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             if (!ok) continue;
             tc_fence_after();
             const int row_base = m0 + quad * 32;
-            // four 64-column groups per warp; the next group's TMEM loads fly while this one is converted
-            uint32_t ra[64], rb[64];
-            const bool have[4] = {n0 < g.N, n0 + 64 < g.N, n0 + 128 < g.N, n0 + 192 < g.N};   // warp-uniform
-            if (have[0]) {
-                tmem_ld32_async(taddr, ra);
-                tmem_ld32_async(taddr + 32u, ra + 32);
-                tmem_ld_wait32(ra);
-                tmem_ld_wait32(ra + 32);
+            // Four 64-column groups per warp through ONE register buffer.  Loading the next group while this one is
+            // converted (a second buffer of 64 registers) measured 2-6 % slower: at the kernel's register ceiling the
+            // conversion code schedules better with the registers than the TMEM load latency costs.  The accumulator
+            // goes back to the MMA issuer as soon as its last columns are in registers, before they are converted.
+            uint32_t ra[64];
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                const bool have = n0 + c * 64 < g.N;   // warp-uniform
+                if (have) {
+                    tmem_ld32_async(taddr + (uint32_t)(c * 64), ra);
+                    tmem_ld32_async(taddr + (uint32_t)(c * 64 + 32), ra + 32);
+                    tmem_ld_wait32(ra);
+                    tmem_ld_wait32(ra + 32);
+                }
+                if (c == 3) {
+                    tc_fence_before();
+                    mbar_arrive(&tail->tmem_empty[grp]);
+                }
+                if (have) epilogue_pair<MODE>(ra, tile_bias + c * 64, my_stage, lane, g, &tmap_y, row_base, n0 + c * 64);
             }
-            if (have[1]) { tmem_ld32_async(taddr + 64u, rb); tmem_ld32_async(taddr + 96u, rb + 32); }
-            if (have[0]) epilogue_pair<MODE>(ra, tile_bias, my_stage, lane, g, &tmap_y, row_base, n0);
-            if (have[1]) { tmem_ld_wait32(rb); tmem_ld_wait32(rb + 32); }
-            if (have[2]) { tmem_ld32_async(taddr + 128u, ra); tmem_ld32_async(taddr + 160u, ra + 32); }
-            if (have[1]) epilogue_pair<MODE>(rb, tile_bias + 64, my_stage, lane, g, &tmap_y, row_base, n0 + 64);
-            if (have[2]) { tmem_ld_wait32(ra); tmem_ld_wait32(ra + 32); }
-            if (have[3]) {
-                tmem_ld32_async(taddr + 192u, rb);
-                tmem_ld32_async(taddr + 224u, rb + 32);
-                tmem_ld_wait32(rb);
-                tmem_ld_wait32(rb + 32);
-            }
-            // Half-way through the tile every accumulator column is in registers or already converted: hand the
-            // buffer back now, so the MMAs of this group's next tile run under the remaining two conversions.
-            tc_fence_before();
-            mbar_arrive(&tail->tmem_empty[grp]);
-            if (have[2]) epilogue_pair<MODE>(ra, tile_bias + 128, my_stage, lane, g, &tmap_y, row_base, n0 + 128);
-            if (have[3]) epilogue_pair<MODE>(rb, tile_bias + 192, my_stage, lane, g, &tmap_y, row_base, n0 + 192);
         }
         // the stores this warp issued must be complete (not merely read) before the CTA retires
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
