@@ -184,3 +184,31 @@ def test_float_matmul_add_and_larger_shapes(compute_dtype):
     want = (s_ref @ w + np.maximum(s_ref @ (w * 0.5), 0.0)).reshape(got.shape)
     tol = dict(rtol=2e-2, atol=2e-1) if compute_dtype == 'bfloat16' else TOL['float32']   # three bf16 roundings in a row
     np.testing.assert_allclose(got, want, **tol)
+
+
+@pytest.mark.gpu
+def test_onnx_fp8_dynamic_matmul_with_a_transposed_operand():
+    """Two fp8_e4m3 graph inputs, Transpose -> MatMul (a dynamic, batched product with a transposed right operand)
+    followed by an Add with a third input; against the oracle on the exported plan, within one fp8 step."""
+    from aie4ml_b200 import from_onnx
+    from aie4ml_b200.frontends.onnx_import import OnnxGraph, OnnxNode
+
+    rng = np.random.default_rng(31)
+    g = OnnxGraph(
+        nodes=[OnnxNode('Transpose', 'kt', ['k'], ['k_t'], {'perm': [0, 2, 1]}), OnnxNode('MatMul', 'qk', ['q', 'k_t'], ['s']),
+               OnnxNode('Add', 'res', ['s', 'z'], ['y'])],
+        initializers={}, inputs={'q': ((3, 40, 32), 'float8_e4m3fn'), 'k': ((3, 24, 32), 'float8_e4m3fn'),
+                                 'z': ((3, 40, 24), 'float8_e4m3fn')}, outputs=['y'], name='f8mm')
+    model = from_onnx(g, {'Part': 'cuda_b200'})
+    model.compile()
+    plan = model.export_plan()
+    assert [(op['kind'], op['dtype']) for op in plan['ops']] == [('matmul_f', 'fp8_e4m3'), ('add_f', 'fp8_e4m3')]
+    assert plan['ops'][0]['transpose_rhs'] and not plan['ops'][0]['transpose_lhs']
+    x = {'q': rng.normal(0, 1, (3, 40, 32)).astype(np.float32), 'k': rng.normal(0, 1, (3, 24, 32)).astype(np.float32),
+         'z': rng.normal(0, 4, (3, 40, 24)).astype(np.float32)}
+    got = np.asarray(model.predict(x))
+    stored = {n: oracle.round_float(v, 'fp8_e4m3') for n, v in x.items()}
+    (_, want), = oracle.run_plan(plan, stored).items()
+    np.testing.assert_array_equal(got, oracle.round_float(got, 'fp8_e4m3'))
+    np.testing.assert_allclose(got, want.reshape(got.shape), rtol=2.0 ** -3 * 1.01, atol=2.0 ** -9)
+    assert (got == want.reshape(got.shape)).mean() > 0.97

@@ -197,6 +197,37 @@ def test_model_with_a_dense_over_a_transposed_input_view():
     assert model.plan.ops[0]['transpose_lhs'] and not model.plan.ops[1]['transpose_lhs']
 
 
+def test_parallel_dense_merge_with_and_without_bias_and_unequal_widths():
+    """Three Dense layers read the same tensor with the same requantisation (one has no bias, widths 32 / 48 / 16):
+    they run as one Dense over 96 outputs whose column slices are the three results; a fourth with a ReLU
+    and a fifth whose width is not a multiple of 16 stay separate.  Every consumer reads its slice."""
+    from aie4ml_b200.frontends.graph import GraphBuilder, intent
+
+    rng = np.random.default_rng(23)
+    b = GraphBuilder({'Part': 'cuda_b200'}, name='fanout')
+    x = b.input('x', (70, 64), intent(8, 4))
+    a0 = b.dense('a0', x, rng.uniform(-1, 1, (64, 32)), intent(8, 6), intent(8, 3), bias=rng.uniform(-1, 1, 32),
+                 bias_precision=intent(16, 8))
+    a1 = b.dense('a1', x, rng.uniform(-1, 1, (64, 48)), intent(8, 6), intent(8, 3))
+    a2 = b.dense('a2', x, rng.uniform(-1, 1, (64, 16)), intent(8, 6), intent(8, 3), bias=rng.uniform(-1, 1, 16),
+                 bias_precision=intent(16, 8))
+    other = b.dense('other', x, rng.uniform(-1, 1, (64, 32)), intent(8, 6), intent(8, 3), relu=True)   # another epilogue
+    odd = b.dense('odd', x, rng.uniform(-1, 1, (64, 24)), intent(8, 6), intent(8, 3))          # 24 is not 16-aligned
+    s0 = b.add('s0', a0, other, intent(8, 3))
+    y0 = b.dense('y0', s0, rng.uniform(-1, 1, (32, 16)), intent(8, 6), intent(8, 3))
+    y1 = b.dense('y1', a1, rng.uniform(-1, 1, (48, 16)), intent(8, 6), intent(8, 3))
+    y2 = b.dense('y2', odd, rng.uniform(-1, 1, (24, 16)), intent(8, 6), intent(8, 3))
+    t = b.add('t0', y0, y1, intent(8, 3))
+    t = b.add('t1', t, y2, intent(8, 3))
+    b.output(b.add('t2', t, a2, intent(8, 3)))
+    model = _check(b, {'x': rng.integers(-128, 128, (70, 64)).astype(np.int8)})
+    merged = [op for op in model.plan.ops if op['kind'] == 'dense' and op['N'] == 96]
+    assert len(merged) == 1 and merged[0]['name'] == 'a0|a1|a2' and merged[0]['bias']
+    assert model.plan.views['a1_out'].root == model.plan.views['a0_out'].root == model.plan.views['a2_out'].root
+    assert model.plan.views['a1_out'].offset == 32 and model.plan.views['a2_out'].offset == 80
+    assert {op['name'] for op in model.plan.ops if op['kind'] == 'dense'} >= {'other', 'odd', 'y0', 'y1', 'y2'}
+
+
 def test_model_with_16_bit_activations_and_weights():
     """A three-layer network whose first two layers keep 16-bit activations: int16 x int8 (acc32) into int16,
     int16 x int16 (acc64) into int8, then an ordinary int8 layer; against the oracle on the exported plan."""
