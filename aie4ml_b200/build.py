@@ -11,6 +11,7 @@ import os
 import shutil
 import subprocess
 import sys
+from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
 PKG_DIR = Path(__file__).resolve().parent
@@ -42,7 +43,7 @@ def build_library(verbose: bool = False, ptxas_info: bool = False) -> Path:
     nvcc = _nvcc()
     BUILD_DIR.mkdir(parents=True, exist_ok=True)
     headers = sorted(CSRC.glob('*.cuh')) + sorted(CSRC.glob('*.h')) + [PKG_DIR.parent / 'include' / 'aie4ml_b200.h']
-    objects = []
+    objects, jobs = [], []
     for src in sorted(CSRC.glob('*.cu')):
         obj = BUILD_DIR / (src.stem + '.o')
         objects.append(obj)
@@ -50,9 +51,16 @@ def build_library(verbose: bool = False, ptxas_info: bool = False) -> Path:
             cmd = [nvcc, *NVCC_FLAGS, '-ccbin', '/usr/bin/g++', '-c', str(src), '-o', str(obj)]
             if ptxas_info:
                 cmd[1:1] = ['-Xptxas', '-v']
-            if verbose:
-                print(' '.join(cmd), flush=True)
-            subprocess.run(cmd, check=True)
+            jobs.append(cmd)
+
+    def compile_one(cmd):
+        if verbose:
+            print(' '.join(cmd), flush=True)
+        subprocess.run(cmd, check=True)
+
+    # the translation units are independent: compile the stale ones side by side
+    with ThreadPoolExecutor(max_workers=max(1, min(len(jobs), os.cpu_count() or 1))) as pool:
+        list(pool.map(compile_one, jobs))
     if _stale(LIB_PATH, objects):
         cmd = [nvcc, '-shared', '-gencode', 'arch=compute_100a,code=sm_100a', '-ccbin', '/usr/bin/g++',
                '--cudart', 'static', '-o', str(LIB_PATH), *map(str, objects)]

@@ -95,3 +95,11 @@ int a4c_launch_attention_tc(const void* q, long long ldq, long long stride_q, co
 int a4c_launch_dense_tc2(const void* A, long long lda, const void* Wt, long long ldw, const int32_t* bias,
                          void* Y, long long ldy, long long M, int K, int N, int shift, int rounding, int relu,
                          int out_dtype, int a_unsigned, int* status_word, cudaStream_t stream);
+
+// Records a failed CUDA call for a4c_last_cuda_error() (thread-local, capi.cu); returns true when e is cudaSuccess.
+bool a4c_note_cuda(cudaError_t e);
+
+// The status word inside the fixed scratch array of a4c_mlp_i8_static (mlp_chain.cu): copies it to *out and
+// clears it when non-zero.  *out = 0 and A4C_OK when the array has not been set up on the current device.  The
+// caller has synchronised whatever work could still write the word.  Allocates nothing.
+int a4c_mlp_static_status_take(int* out);

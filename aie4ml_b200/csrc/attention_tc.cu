@@ -451,12 +451,8 @@ bool make_head_map(CUtensorMap* map, const void* base, long long rows, int heads
 template <int MODE>
 cudaError_t launch_mode(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& g, int grid,
                         cudaStream_t s) {
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(attention_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)SMEM_BYTES);
-    });
+    static tc::SmemOptIn opt_in;
+    const cudaError_t attr_err = opt_in.ensure(attention_tc_kernel<MODE>, SMEM_BYTES);
     if (attr_err != cudaSuccess) return attr_err;
     attention_tc_kernel<MODE><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(mq, mk, mv, g);
     return cudaGetLastError();
@@ -476,7 +472,11 @@ int a4c_attention_tc_supported(const void* q, long long ldq, long long stride_q,
     if (qk_shift < 0 || qk_shift > 31 || pv_shift < 0 || pv_shift > 31) return A4C_ERR_INVALID_ARG;
     if (sm_mode != 0 && sm_mode != 1) return A4C_ERR_INVALID_ARG;
     if (inv_shift < 0 || inv_shift > 22) return A4C_ERR_UNSUPPORTED;
-    if (sm_mode == 0 && B - S * (Dmax < 255 ? Dmax : 255) < 0) return A4C_ERR_UNSUPPORTED;   // negative scores
+    // HCCS: every score must lie in [0, 32767] (the kernel normalises through the bit pattern of a non-negative
+    // value); these are the reference resolver's bounds (softmax/common.py:59-89), anything else goes to the
+    // separate kernels
+    if (sm_mode == 0 && (S < 0 || Dmax < 0 || B < 0 || B > 32767 || B - S * (Dmax < 255 ? Dmax : 255) < 0))
+        return A4C_ERR_UNSUPPORTED;
     if (ldq % 16 || ldk % 16 || ldv % 16 || ldo % 16) return A4C_ERR_ALIGNMENT;
     if (batch > 1 && (stride_q % 16 || stride_k % 16 || stride_v % 16 || stride_o % 16)) return A4C_ERR_ALIGNMENT;
     if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15u) return A4C_ERR_ALIGNMENT;

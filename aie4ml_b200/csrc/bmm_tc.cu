@@ -263,12 +263,8 @@ bool make_map3(CUtensorMap* map, const void* base, long long inner, long long ro
 template <int BN, bool B_MN, int MODE>
 cudaError_t launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const BmmArgs& g, int grid, cudaStream_t s) {
     constexpr size_t smem = 1024 + (size_t)STAGES * Cfg<BN>::STAGE_BYTES + sizeof(Tail);
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(bmm_tc_kernel<BN, B_MN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)smem);
-    });
+    static tc::SmemOptIn opt_in;
+    const cudaError_t attr_err = opt_in.ensure(bmm_tc_kernel<BN, B_MN, MODE>, smem);
     if (attr_err != cudaSuccess) return attr_err;
     bmm_tc_kernel<BN, B_MN, MODE><<<grid, NUM_THREADS, smem, s>>>(ma, mb, g);
     return cudaGetLastError();

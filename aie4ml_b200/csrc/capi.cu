@@ -47,6 +47,8 @@ int finish() {
 
 }  // namespace
 
+bool a4c_note_cuda(cudaError_t e) { return note(e); }
+
 extern "C" {
 
 int a4c_version(void) { return 100; }
@@ -77,7 +79,11 @@ int a4c_device_status(int* status, void* stream) {
         cudaMemset(word, 0, sizeof(int));
         return A4C_ERR_DEVICE_TIMEOUT;
     }
-    return A4C_OK;
+    // a4c_mlp_i8_static reports into a word of its own (inside its fixed array): a caller that passed no
+    // status_out there learns of a timeout here
+    const int src = a4c_mlp_static_status_take(status);
+    if (src != A4C_OK) return src;
+    return *status != 0 ? A4C_ERR_DEVICE_TIMEOUT : A4C_OK;
 }
 
 int a4c_dense_i8(const void* A, int64_t lda, const int8_t* Wt, int64_t ldw, const int32_t* bias, void* Y,

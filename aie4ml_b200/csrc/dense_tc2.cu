@@ -297,12 +297,8 @@ bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols
 
 template <int MODE>
 cudaError_t launch_mode(const CUtensorMap& ma, const CUtensorMap& mb, const Tc2Args& g, int grid, cudaStream_t s) {
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(dense_tc2_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)SMEM_BYTES);
-    });
+    static tc::SmemOptIn opt_in;
+    const cudaError_t attr_err = opt_in.ensure(dense_tc2_kernel<MODE>, SMEM_BYTES);
     if (attr_err != cudaSuccess) return attr_err;
     dense_tc2_kernel<MODE><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(ma, mb, g);
     return cudaGetLastError();

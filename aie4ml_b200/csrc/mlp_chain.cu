@@ -151,12 +151,12 @@ unsigned char* g_static_ptr[kMaxDevices] = {nullptr};
 // per device with that device current.
 int static_scratch(cudaStream_t stream, unsigned char** out) {
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return A4C_ERR_CUDA;
+    if (!a4c_note_cuda(cudaGetDevice(&dev)) || dev < 0 || dev >= kMaxDevices) return A4C_ERR_CUDA;
     std::lock_guard<std::mutex> lock(g_static_mutex);
     if (g_static_ptr[dev] == nullptr) {
         unsigned char* p = nullptr;
-        if (cudaGetSymbolAddress((void**)&p, g_mlp_static_scratch) != cudaSuccess || p == nullptr) return A4C_ERR_CUDA;
-        if (cudaMemsetAsync(p, 0, 256, stream) != cudaSuccess) return A4C_ERR_CUDA;
+        if (!a4c_note_cuda(cudaGetSymbolAddress((void**)&p, g_mlp_static_scratch)) || p == nullptr) return A4C_ERR_CUDA;
+        if (!a4c_note_cuda(cudaMemsetAsync(p, 0, 256, stream))) return A4C_ERR_CUDA;
         g_static_ptr[dev] = p;
     }
     *out = g_static_ptr[dev];
@@ -175,6 +175,21 @@ int dense_no_alloc(const void* A, long long lda, const int8_t* Wt, long long ldw
 }
 
 }  // namespace
+
+int a4c_mlp_static_status_take(int* out) {
+    *out = 0;
+    int dev = 0;
+    if (!a4c_note_cuda(cudaGetDevice(&dev)) || dev < 0 || dev >= kMaxDevices) return A4C_ERR_CUDA;
+    unsigned char* base;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        base = g_static_ptr[dev];
+    }
+    if (base == nullptr) return A4C_OK;   // never set up on this device: nothing can have reported into it
+    if (!a4c_note_cuda(cudaMemcpy(out, base, sizeof(int), cudaMemcpyDeviceToHost))) return A4C_ERR_CUDA;
+    if (*out != 0 && !a4c_note_cuda(cudaMemset(base, 0, sizeof(int)))) return A4C_ERR_CUDA;
+    return A4C_OK;
+}
 
 extern "C" int a4c_mlp_i8_static(const void* X, int64_t ldx, int x_unsigned, int n_layers, const int* dims,
                                  const int8_t* const* Wt, const int64_t* ldw, const int32_t* const* bias,
@@ -201,16 +216,19 @@ extern "C" int a4c_mlp_i8_static(const void* X, int64_t ldx, int x_unsigned, int
             const int rc = dense_no_alloc(in, ld_in, Wt[l], ldw[l], bias ? bias[l] : nullptr, out, ld_out, M, dims[l],
                                           dims[l + 1], shift[l], rounding, relu[l], last ? out_dtype : A4C_I8, in_unsigned,
                                           status, s);
-            if (rc != A4C_OK) return rc;
+            if (rc != A4C_OK) {
+                if (rc == A4C_ERR_CUDA) a4c_note_cuda(cudaGetLastError());
+                return rc;
+            }
             in = out;
             ld_in = ld_out;
             in_unsigned = 0;
         }
-        if (cudaPeekAtLastError() != cudaSuccess) return A4C_ERR_CUDA;
+        if (!a4c_note_cuda(cudaPeekAtLastError())) return A4C_ERR_CUDA;
     }
     if (status_out != nullptr) {
-        if (cudaMemcpyAsync(status_out, status, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess) return A4C_ERR_CUDA;
-        if (cudaStreamSynchronize(s) != cudaSuccess) return A4C_ERR_CUDA;
+        if (!a4c_note_cuda(cudaMemcpyAsync(status_out, status, sizeof(int), cudaMemcpyDeviceToHost, s))) return A4C_ERR_CUDA;
+        if (!a4c_note_cuda(cudaStreamSynchronize(s))) return A4C_ERR_CUDA;
         if (*status_out != 0) {
             cudaMemsetAsync(status, 0, sizeof(int), s);
             return A4C_ERR_DEVICE_TIMEOUT;

@@ -4,9 +4,29 @@
 #include <cuda.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "a4c_common.cuh"
 
 namespace tc {
+
+// The opt-in to more than 48 KB of dynamic shared memory belongs to one (kernel, device) pair, so it is
+// remembered per device ordinal: a process that drives several GPUs sets it on each of them before its first
+// launch there.  One object per kernel instantiation (a function-local static of the launcher).
+struct SmemOptIn {
+    std::atomic<unsigned long long> done{0};   // bit d: set on device d
+    template <typename Kernel>
+    cudaError_t ensure(Kernel kernel, size_t bytes) {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        const bool tracked = dev >= 0 && dev < 64;
+        if (tracked && ((done.load(std::memory_order_acquire) >> dev) & 1ull)) return cudaSuccess;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e == cudaSuccess && tracked) done.fetch_or(1ull << dev, std::memory_order_release);
+        return e;
+    }
+};
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

@@ -119,6 +119,15 @@ class Plan:
             raise RuntimeError('aie4ml_b200 executes on a CUDA device only; no GPU is visible and there is no '
                                'CPU execution path.')
         self.device = torch.device(device or f'cuda:{torch.cuda.current_device()}')
+        # The C ABI works on the CURRENT device (status word, SM count, scratch, shared-memory opt-in), so every
+        # entry into it from this plan runs with the plan's device current, whatever the caller had selected.
+        with torch.cuda.device(self.device):
+            self._build(ctx, fuse_rowop_add, dense_algo, share_params, fuse_attention, fuse_dense_chain,
+                        merge_attention_heads, merge_parallel_dense)
+
+    def _build(self, ctx, fuse_rowop_add, dense_algo, share_params, fuse_attention, fuse_dense_chain,
+               merge_attention_heads, merge_parallel_dense) -> None:
+        torch = _torch()
         self.dense_algo = int(dense_algo)
         self.fuse_rowop_add = bool(fuse_rowop_add)
         self.fuse_attention = bool(fuse_attention)
@@ -702,24 +711,27 @@ class Plan:
     def run(self, use_graph: bool = True) -> None:
         """Execute every launch on the current stream (replaying a captured CUDA graph once one exists)."""
         torch = _torch()
-        if use_graph and self.graph_exec is not None:
-            self.graph_exec.replay()
-            return
-        self.launch_all(torch.cuda.current_stream(self.device).cuda_stream)
+        with torch.cuda.device(self.device):
+            if use_graph and self.graph_exec is not None:
+                self.graph_exec.replay()
+                return
+            self.launch_all(torch.cuda.current_stream(self.device).cuda_stream)
 
     def capture(self) -> None:
         """Capture the launch list into a CUDA graph (after one eager warm-up run)."""
         torch = _torch()
-        self.run(use_graph=False)
-        torch.cuda.synchronize(self.device)
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            self.launch_all(torch.cuda.current_stream(self.device).cuda_stream)
-        self.graph_exec = g
+        with torch.cuda.device(self.device):
+            self.run(use_graph=False)
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.launch_all(torch.cuda.current_stream(self.device).cuda_stream)
+            self.graph_exec = g
 
     def check_status(self) -> None:
         torch = _torch()
-        _lib.device_status(torch.cuda.current_stream(self.device).cuda_stream)
+        with torch.cuda.device(self.device):
+            _lib.device_status(torch.cuda.current_stream(self.device).cuda_stream)
 
     # ---- export --------------------------------------------------------------------------------
     def export(self) -> Dict[str, Any]:

@@ -297,7 +297,9 @@ A4C_API int a4c_mlp_i8_single_kernel(int n_layers, const int* dims, int out_dtyp
  *
  * status_out (host pointer, or NULL): when given, the call waits for `stream`, stores the kernels' status word
  * there (0 = every bounded device-side wait completed) and returns A4C_ERR_DEVICE_TIMEOUT if it is not 0;
- * with NULL the call stays asynchronous.
+ * with NULL the call stays asynchronous, and a later a4c_device_status() on the same device (which waits for
+ * its stream, allocates its own status word on first use, and is therefore for the set-up or shut-down side of
+ * such a caller) reports and clears a timeout that a NULL-status call left behind.
  */
 #define A4C_MLP_STATIC_BYTES (4u << 20)
 A4C_API int a4c_mlp_i8_static(const void* X, int64_t ldx, int x_unsigned, int n_layers, const int* dims,

@@ -145,10 +145,13 @@ def mlp_chain(x, layers, *, tok, out_dtype='int8', fn_name='a4c_mlp_i8'):
     esz = np.dtype(NP[out_dtype]).itemsize
     ldy = (N * esz + 15) // 16 * 16 // esz
     y_d = torch.zeros((M, ldy), dtype=TD[out_dtype], device='cuda')
-    rc = fn(x_d.data_ptr(), lda, int(x.dtype == np.uint8), n, ctypes.cast(dims, ctypes.c_void_p),
+    args = [x_d.data_ptr(), lda, int(x.dtype == np.uint8), n, ctypes.cast(dims, ctypes.c_void_p),
             ctypes.cast(wt_ptrs, ctypes.c_void_p), ctypes.cast(ldw, ctypes.c_void_p), ctypes.cast(b_ptrs, ctypes.c_void_p),
             ctypes.cast(shifts, ctypes.c_void_p), ctypes.cast(relus, ctypes.c_void_p), ROUNDING_CODE[tok], y_d.data_ptr(),
-            ldy, DTYPE_CODE[out_dtype], M, stream())
+            ldy, DTYPE_CODE[out_dtype], M]
+    if fn_name == 'a4c_mlp_i8_static':
+        args.append(None)    # status_out: stay asynchronous, a4c_device_status below reads the word
+    rc = fn(*args, stream())
     a4c.check(rc, fn_name)
     a4c.device_status(stream())
     return y_d.cpu().numpy()[:, :N]

@@ -483,6 +483,13 @@ def test_fused_attention_other_softmax_parameters_and_rejections():
     assert L.a4c_attention_i8_supported(*misaligned) == a4c.A4C_ERR_ALIGNMENT
     one_zero_shift = list(ok); one_zero_shift[16] = 0
     assert L.a4c_attention_i8_supported(*one_zero_shift) == a4c.A4C_ERR_UNSUPPORTED
+    # surrogate parameters outside the reference's bounds (softmax/common.py:59-89) are left to the separate kernels:
+    # a negative slope makes scores grow past 32767, where the fused kernel's normalisation is not defined
+    for B, S, Dmax in ((200, -3, 60), (40000, 1, 10), (-1, 0, 0), (10, 1, 20), (10, 1, -1)):
+        bad = list(ok); bad[18:22] = [0, B, S, Dmax]
+        assert L.a4c_attention_i8_supported(*bad) == a4c.A4C_ERR_UNSUPPORTED, (B, S, Dmax)
+    fine = list(ok); fine[18:22] = [0, 200, 3, 66]
+    assert L.a4c_attention_i8_supported(*fine) == 0
 
 
 @pytest.mark.parametrize('wide', [False, True])

@@ -4,7 +4,10 @@ Some embedders of this library run a model from code that may not call cudaMallo
 runtime's stream, a process whose device memory belongs to its own pool, a loop that must never wait on the CUDA
 allocator's lock.  For them the chain's scratch is a fixed array inside the library image.  This test calls that
 entry point through the C ABI twice in a row and checks both results, bit for bit, against the ordinary
-`a4c_mlp_i8` (whose scratch is allocated); it also checks that a problem larger than the fixed array is refused.
+`a4c_mlp_i8` (whose scratch is allocated) and against the CPU oracle; it checks that the device's free memory
+does not move across calls, that chains which take the other kernel branches (a first layer too short for the
+tensor-core kernel, unsigned input and output, a single layer) agree with the oracle too, and that a problem
+larger than the fixed array is refused.
 
 The file name sorts last on purpose: a run that stops at the first failure has then already run everything else.
 """
@@ -100,3 +103,72 @@ def test_static_chain_refuses_what_does_not_fit():
     y2 = torch.zeros((4096, 16), dtype=torch.int8, device='cuda')
     assert _call('a4c_mlp_i8_static', x_d, 64, n, dims, wt_ptrs, ldw, b_ptrs, shifts, relus, y2, 16, 4096, None) == 0
     torch.cuda.synchronize()
+
+
+def _oracle_chain(x, layers, tok, out_dtype):
+    from oracle import oracle
+
+    cur = x
+    for i, (w, b, shift, relu) in enumerate(layers):
+        last = i == len(layers) - 1
+        cur = oracle.dense(cur, w, b, shift=shift, tok=tok, relu=relu, out_dtype=out_dtype if last else 'int8')
+    return cur
+
+
+def _layers(rng, dims, shift, bias=True):
+    n = len(dims) - 1
+    return [(rng.integers(-127, 128, (dims[i], dims[i + 1])).astype(np.int8),
+             rng.integers(-(1 << 12), 1 << 12, dims[i + 1]).astype(np.int32) if bias else None, shift, i < n - 1)
+            for i in range(n)]
+
+
+def test_static_chain_against_the_oracle_on_every_kernel_branch_without_allocating():
+    import torch
+
+    import gpu_util as G
+
+    rng = np.random.default_rng(77)
+    cases = [
+        # (dims, rows, input type, output type, rounding token)
+        ((16, 64, 32, 32, 5), 1024, np.int8, 'int8', 'positive_inf'),    # tensor-core kernel in every layer
+        ((8, 48, 10), 300, np.int8, 'int8', 'conv_even'),                # K = 8 < 16: the dp4a kernel takes layer 0
+        ((32, 64, 24), 257, np.uint8, 'uint8', 'symmetric_inf'),         # unsigned input and output
+        ((64, 40), 129, np.int8, 'int8', 'floor'),                       # a single layer: no scratch is touched
+    ]
+    # one warm-up call sets the array up on this device; after it the free memory must not move
+    d0, r0 = cases[0][0], cases[0][1]
+    G.mlp_chain(rng.integers(-128, 128, (r0, d0[0])).astype(np.int8), _layers(rng, d0, 7), tok='positive_inf',
+                fn_name='a4c_mlp_i8_static')
+    prepared = []
+    for dims, rows, in_t, out_t, tok in cases:
+        lo, hi = (0, 256) if in_t is np.uint8 else (-128, 128)
+        prepared.append((rng.integers(lo, hi, (rows, dims[0])).astype(in_t), _layers(rng, dims, 7), tok, out_t))
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    for x, layers, tok, out_t in prepared:
+        want = _oracle_chain(x, layers, tok, out_t)
+        for attempt in range(2):
+            got = G.mlp_chain(x, layers, tok=tok, out_dtype=out_t, fn_name='a4c_mlp_i8_static')
+            np.testing.assert_array_equal(got.astype(np.int64), want.astype(np.int64),
+                                          err_msg=f'dims {[w.shape for w, *_ in layers]} call {attempt}')
+    # the calls themselves: same buffers, several sizes, free device memory read before and after
+    import ctypes
+
+    x, layers, tok, out_t = prepared[0]
+    n = len(layers)
+    wts = [G.dev(G.pack_wt(w)) for w, *_ in layers]
+    b_d = [G.dev(b) for _, b, _, _ in layers]
+    dims = (ctypes.c_int * (n + 1))(x.shape[1], *[w.shape[1] for w, *_ in layers])
+    wt_ptrs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in wts])
+    ldw = (ctypes.c_int64 * n)(*[t.shape[1] for t in wts])
+    b_ptrs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in b_d])
+    shifts = (ctypes.c_int * n)(*([7] * n))
+    relus = (ctypes.c_int * n)(*([1] * (n - 1) + [0]))
+    x_d = G.dev(x)
+    y_d = torch.zeros((x.shape[0], 16), dtype=torch.int8, device='cuda')
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    for rows in (1024, 1, 517, 1024):
+        assert _call('a4c_mlp_i8_static', x_d, 16, n, dims, wt_ptrs, ldw, b_ptrs, shifts, relus, y_d, 16, rows, None) == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before, 'the allocation-free entry point changed the free device memory'
