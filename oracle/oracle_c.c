@@ -64,6 +64,200 @@ static inline int64_t srs_out(int64_t v, int shift, int tok, int dtype) {
     return saturate(round_shift64(v, shift, tok), dtype);
 }
 
+/* ---- integer GEMM core ---------------------------------------------------------------------
+ * Both matrix products below are blocked over rows and columns with the K loop innermost on 32-bit
+ * accumulators that wrap (the AIE acc32 lanes do: every partial sum is taken modulo 2^32, so any
+ * order of accumulation gives the same bits).  Two code paths compute the same sums:
+ *   - AVX-512 VNNI (when the compiler targets it): vpdpbusd multiplies unsigned bytes by signed
+ *     bytes, so a signed A is offset by +128 (a ^ 0x80) and 128 * (column sum of W) is taken back
+ *     out of the accumulator's initial value; the non-saturating form wraps like the plain sum.
+ *   - portable C: operands widened to int16, dot products the compiler turns into multiply-add
+ *     instructions of whatever width the target has.
+ */
+#if defined(__AVX512VNNI__) && defined(__AVX512BW__) && defined(__AVX512F__)
+#include <immintrin.h>
+#define ORC_VNNI 1
+#else
+#define ORC_VNNI 0
+#endif
+
+ORC_API int orc_gemm_path(void) { return ORC_VNNI; }   /* 1 = AVX-512 VNNI, 0 = portable C */
+
+#if ORC_VNNI
+enum { VN_NR = 64, VN_MR = 6 };
+
+/* W [K,N] (row pitch ldw, element (k,n) at W[k*w_ks + n*w_ns]) -> panels [N/64][K4][64 n][4 k], zero padded;
+ * colsum[n] = sum_k W[k,n]. */
+static int8_t* vn_pack_w(const int8_t* W, int64_t w_ks, int64_t w_ns, int K, int N, int32_t* colsum) {
+    const int K4 = (K + 3) / 4, NP = (N + VN_NR - 1) / VN_NR;
+    int8_t* P = (int8_t*)aligned_alloc(64, (size_t)NP * K4 * VN_NR * 4);
+    if (!P) return NULL;
+#pragma omp parallel for schedule(static)
+    for (int np = 0; np < NP; ++np) {
+        int8_t* dst = P + (size_t)np * K4 * VN_NR * 4;
+        int32_t cs[VN_NR] = {0};
+        const int nb = N - np * VN_NR < VN_NR ? N - np * VN_NR : VN_NR;
+        for (int k4 = 0; k4 < K4; ++k4)
+            for (int kk = 0; kk < 4; ++kk) {
+                const int k = k4 * 4 + kk;
+                int8_t* d = dst + (size_t)k4 * VN_NR * 4 + kk;
+                if (k < K) {
+                    const int8_t* src = W + (int64_t)k * w_ks + (int64_t)np * VN_NR * w_ns;   /* 64 columns of row k */
+                    for (int j = 0; j < nb; ++j) { const int8_t v = src[(int64_t)j * w_ns]; d[j * 4] = v; cs[j] += v; }
+                    for (int j = nb; j < VN_NR; ++j) d[j * 4] = 0;
+                } else {
+                    for (int j = 0; j < VN_NR; ++j) d[j * 4] = 0;
+                }
+            }
+        for (int j = 0; j < nb; ++j) colsum[np * VN_NR + j] = cs[j];
+    }
+    return P;
+}
+
+/* acc[i][n] (i < mr <= 6, 64 columns) = init[n] + sum_k Au[i][k] * Wp[k][n] over K4 groups of four k.
+ * Au: mr rows of unsigned bytes, row pitch a_ld (a multiple of 4, zero or anything in the K padding:
+ * the packed W is zero there). */
+static void vn_micro(const uint8_t* Au, int64_t a_ld, int mr, const int8_t* Wp, int K4, const int32_t* init,
+                     int32_t* out /* [mr][64] */) {
+    __m512i acc[VN_MR][4];
+    for (int i = 0; i < VN_MR; ++i)
+        for (int c = 0; c < 4; ++c) acc[i][c] = _mm512_loadu_si512((const void*)(init + 16 * c));
+    const uint8_t* rows[VN_MR];
+    for (int i = 0; i < VN_MR; ++i) rows[i] = Au + (int64_t)(i < mr ? i : 0) * a_ld;
+    for (int k4 = 0; k4 < K4; ++k4) {
+        const __m512i w0 = _mm512_load_si512((const void*)(Wp + (size_t)k4 * 256));
+        const __m512i w1 = _mm512_load_si512((const void*)(Wp + (size_t)k4 * 256 + 64));
+        const __m512i w2 = _mm512_load_si512((const void*)(Wp + (size_t)k4 * 256 + 128));
+        const __m512i w3 = _mm512_load_si512((const void*)(Wp + (size_t)k4 * 256 + 192));
+#pragma GCC unroll 6
+        for (int i = 0; i < VN_MR; ++i) {
+            int32_t a4;
+            memcpy(&a4, rows[i] + (size_t)k4 * 4, 4);
+            const __m512i a = _mm512_set1_epi32(a4);
+            acc[i][0] = _mm512_dpbusd_epi32(acc[i][0], a, w0);
+            acc[i][1] = _mm512_dpbusd_epi32(acc[i][1], a, w1);
+            acc[i][2] = _mm512_dpbusd_epi32(acc[i][2], a, w2);
+            acc[i][3] = _mm512_dpbusd_epi32(acc[i][3], a, w3);
+        }
+    }
+    for (int i = 0; i < mr; ++i)
+        for (int c = 0; c < 4; ++c) _mm512_storeu_si512((void*)(out + i * 64 + 16 * c), acc[i][c]);
+}
+#endif
+
+/* One [M,K] x [K,N] product with the shared epilogue.  A element (m,k) at A[m*a_rs + k*a_cs] (bytes),
+ * W element (k,n) at W[k*w_ks + n*w_ns].  `parallel` = split the rows over OpenMP threads (the batched
+ * caller parallelises over the batch instead). */
+static int gemm_i8(const void* A, int64_t a_rs, int64_t a_cs, int a_unsigned, const int8_t* W, int64_t w_ks, int64_t w_ns,
+                   const int32_t* bias, void* Y, int64_t ldy, int64_t M, int K, int N, int shift, int rounding, int relu,
+                   int out_dtype, int parallel) {
+#if ORC_VNNI
+    const int K4 = (K + 3) / 4, Kp = K4 * 4, NP = (N + VN_NR - 1) / VN_NR;
+    int32_t* colsum = (int32_t*)calloc((size_t)NP * VN_NR, sizeof(int32_t));
+    int32_t* init = (int32_t*)calloc((size_t)NP * VN_NR, sizeof(int32_t));
+    int8_t* Wp = colsum && init ? vn_pack_w(W, w_ks, w_ns, K, N, colsum) : NULL;
+    if (!Wp) { free(colsum); free(init); return -2; }
+    for (int n = 0; n < N; ++n)
+        init[n] = (int32_t)((uint32_t)(bias ? bias[n] : 0) - (a_unsigned ? 0u : 128u * (uint32_t)colsum[n]));
+    enum { MBLK = 48 };   /* rows converted at a time: 8 micro-kernel row groups share each streamed W panel */
+    int fail = 0;
+#pragma omp parallel if (parallel)
+    {
+        uint8_t* Au = (uint8_t*)aligned_alloc(64, ((size_t)MBLK * Kp + 63) / 64 * 64);
+        int32_t tile[VN_MR * 64];
+        if (!Au) {
+#pragma omp atomic write
+            fail = 1;
+        }
+#pragma omp for schedule(dynamic, 1)
+        for (int64_t m0 = 0; m0 < M; m0 += MBLK) {
+            if (!Au) continue;
+            const int mb = (int)(M - m0 < MBLK ? M - m0 : MBLK);
+            for (int i = 0; i < mb; ++i) {
+                const uint8_t* src = (const uint8_t*)A + (m0 + i) * a_rs;
+                uint8_t* dst = Au + (size_t)i * Kp;
+                const uint8_t flip = a_unsigned ? 0 : 0x80;
+                for (int k = 0; k < K; ++k) dst[k] = src[(int64_t)k * a_cs] ^ flip;
+                for (int k = K; k < Kp; ++k) dst[k] = 0;
+            }
+            for (int np = 0; np < NP; ++np) {
+                const int8_t* wp = Wp + (size_t)np * K4 * 256;
+                const int nb = N - np * 64 < 64 ? N - np * 64 : 64;
+                for (int i0 = 0; i0 < mb; i0 += VN_MR) {
+                    const int mr = mb - i0 < VN_MR ? mb - i0 : VN_MR;
+                    vn_micro(Au + (size_t)i0 * Kp, Kp, mr, wp, K4, init + np * 64, tile);
+                    for (int i = 0; i < mr; ++i)
+                        for (int j = 0; j < nb; ++j) {
+                            int64_t y = srs_out(tile[i * 64 + j], shift, rounding, out_dtype);
+                            if (relu && y < 0) y = 0;
+                            store_out(Y, (m0 + i0 + i) * ldy + np * 64 + j, y, out_dtype);
+                        }
+                }
+            }
+        }
+        free(Au);
+    }
+    free(Wp); free(colsum); free(init);
+    return fail ? -2 : 0;
+#else
+    /* portable: W^T and a block of A rows widened to int16 with K contiguous; 4 x 4 register tiles of dot products */
+    const int Kp = (K + 31) / 32 * 32;
+    int16_t* Wt = (int16_t*)aligned_alloc(64, (size_t)N * Kp * sizeof(int16_t));
+    if (!Wt) return -2;
+#pragma omp parallel for schedule(static) if (parallel)
+    for (int n = 0; n < N; ++n) {
+        int16_t* dst = Wt + (size_t)n * Kp;
+        for (int k = 0; k < K; ++k) dst[k] = W[(int64_t)k * w_ks + (int64_t)n * w_ns];
+        for (int k = K; k < Kp; ++k) dst[k] = 0;
+    }
+    enum { MBLK = 32 };
+    int fail = 0;
+#pragma omp parallel if (parallel)
+    {
+        int16_t* Ab = (int16_t*)aligned_alloc(64, (size_t)MBLK * Kp * sizeof(int16_t));
+        if (!Ab) {
+#pragma omp atomic write
+            fail = 1;
+        }
+#pragma omp for schedule(dynamic, 1)
+        for (int64_t m0 = 0; m0 < M; m0 += MBLK) {
+            if (!Ab) continue;
+            const int mb = (int)(M - m0 < MBLK ? M - m0 : MBLK);
+            for (int i = 0; i < mb; ++i) {
+                const uint8_t* su = (const uint8_t*)A + (m0 + i) * a_rs;
+                const int8_t* ss = (const int8_t*)su;
+                int16_t* dst = Ab + (size_t)i * Kp;
+                for (int k = 0; k < K; ++k) dst[k] = a_unsigned ? (int16_t)su[(int64_t)k * a_cs] : (int16_t)ss[(int64_t)k * a_cs];
+                for (int k = K; k < Kp; ++k) dst[k] = 0;
+            }
+            for (int n0 = 0; n0 < N; n0 += 4)
+                for (int i0 = 0; i0 < mb; i0 += 4) {
+                    int32_t acc[4][4] = {{0}};
+                    const int16_t* a[4];
+                    const int16_t* w[4];
+                    for (int t = 0; t < 4; ++t) {
+                        a[t] = Ab + (size_t)(i0 + t < mb ? i0 + t : i0) * Kp;
+                        w[t] = Wt + (size_t)(n0 + t < N ? n0 + t : n0) * Kp;
+                    }
+                    for (int k = 0; k < Kp; ++k)   /* signed wrap is defined here: the file is built with -fwrapv */
+                        for (int i = 0; i < 4; ++i)
+                            for (int j = 0; j < 4; ++j) acc[i][j] += (int32_t)a[i][k] * (int32_t)w[j][k];
+                    for (int i = 0; i < 4 && i0 + i < mb; ++i)
+                        for (int j = 0; j < 4 && n0 + j < N; ++j) {
+                            const int32_t v = (int32_t)((uint32_t)acc[i][j] + (uint32_t)(bias ? bias[n0 + j] : 0));
+                            int64_t y = srs_out(v, shift, rounding, out_dtype);
+                            if (relu && y < 0) y = 0;
+                            store_out(Y, (m0 + i0 + i) * ldy + n0 + j, y, out_dtype);
+                        }
+                }
+        }
+        free(Ab);
+    }
+    free(Wt);
+    return fail ? -2 : 0;
+#endif
+}
+
 /* Dense: relu?(srs(A.W + bias)).  dense_single::run,
  * templates/nnet_utils/dense_bias_relu/dense_bias_relu.cpp:67-166 (bias as accumulator init
  * :114-124, acc32 MACs :132-151, ReLU after saturation :153-157).
@@ -71,29 +265,8 @@ static inline int64_t srs_out(int64_t v, int shift, int tok, int dtype) {
 ORC_API int orc_dense_i8(const void* A, int64_t lda, const int8_t* W, const int32_t* bias, void* Y, int64_t ldy,
                          int64_t M, int K, int N, int shift, int rounding, int relu, int out_dtype, int a_unsigned) {
     if (M < 0 || K <= 0 || N <= 0 || shift < 0 || shift > 62) return -1;
-#pragma omp parallel
-    {
-        int32_t* acc = (int32_t*)malloc(sizeof(int32_t) * (size_t)N);
-#pragma omp for schedule(static)
-        for (int64_t m = 0; m < M; ++m) {
-            for (int n = 0; n < N; ++n) acc[n] = bias ? bias[n] : 0;
-            const int8_t* as = (const int8_t*)A + m * lda;
-            const uint8_t* au = (const uint8_t*)A + m * lda;
-            for (int k = 0; k < K; ++k) {
-                const int32_t a = a_unsigned ? (int32_t)au[k] : (int32_t)as[k];
-                const int8_t* w = W + (int64_t)k * N;
-                /* unsigned arithmetic: acc32 lanes wrap */
-                for (int n = 0; n < N; ++n) acc[n] = (int32_t)((uint32_t)acc[n] + (uint32_t)(a * (int32_t)w[n]));
-            }
-            for (int n = 0; n < N; ++n) {
-                int64_t y = srs_out(acc[n], shift, rounding, out_dtype);
-                if (relu && y < 0) y = 0;
-                store_out(Y, m * ldy + n, y, out_dtype);
-            }
-        }
-        free(acc);
-    }
-    return 0;
+    if (M == 0) return 0;
+    return gemm_i8(A, lda, 1, a_unsigned, W, N, 1, bias, Y, ldy, M, K, N, shift, rounding, relu, out_dtype, 1);
 }
 
 /* Batched dynamic MatMul: C_b = srs(op(A_b).op(B_b)).  matmul_single::run,
@@ -104,26 +277,19 @@ ORC_API int orc_bmm_i8(const void* A, int64_t lda, int64_t stride_a, const int8_
                        void* C, int64_t ldc, int64_t stride_c, int64_t batch, int M, int K, int N, int trans_a,
                        int trans_b, int shift, int rounding, int out_dtype, int a_unsigned) {
     if (batch < 0 || M <= 0 || K <= 0 || N <= 0 || shift < 0 || shift > 62) return -1;
+    const int esz = out_dtype == 2 ? 2 : 1;
+    int fail = 0;
 #pragma omp parallel for schedule(static)
     for (int64_t b = 0; b < batch; ++b) {
-        const int8_t* as = (const int8_t*)A + b * stride_a;
-        const uint8_t* au = (const uint8_t*)A + b * stride_a;
-        const int8_t* bs = B + b * stride_b;
-        for (int m = 0; m < M; ++m) {
-            for (int n = 0; n < N; ++n) {
-                uint32_t acc = 0;
-                for (int k = 0; k < K; ++k) {
-                    const int64_t ai = trans_a ? (int64_t)k * lda + m : (int64_t)m * lda + k;
-                    const int64_t bi = trans_b ? (int64_t)n * ldb + k : (int64_t)k * ldb + n;
-                    const int32_t a = a_unsigned ? (int32_t)au[ai] : (int32_t)as[ai];
-                    acc += (uint32_t)(a * (int32_t)bs[bi]);
-                }
-                const int64_t y = srs_out((int32_t)acc, shift, rounding, out_dtype);
-                store_out(C, b * stride_c + (int64_t)m * ldc + n, y, out_dtype);
-            }
+        const int rc = gemm_i8((const uint8_t*)A + b * stride_a, trans_a ? 1 : lda, trans_a ? lda : 1, a_unsigned,
+                               B + b * stride_b, trans_b ? 1 : ldb, trans_b ? ldb : 1, NULL,
+                               (uint8_t*)C + b * stride_c * esz, ldc, M, K, N, shift, rounding, 0, out_dtype, 0);
+        if (rc != 0) {
+#pragma omp atomic write
+            fail = rc;
         }
     }
-    return 0;
+    return fail;
 }
 
 /* Elementwise srs(a + b): elementwise_add_kernel::run,

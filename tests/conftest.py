@@ -40,3 +40,16 @@ def oracle_c():
     if not so.exists() or so.stat().st_mtime < src.stat().st_mtime:
         subprocess.run(['make', '-C', str(ROOT / 'oracle')], check=True, capture_output=True)
     return ctypes.CDLL(str(so))
+
+
+@pytest.fixture(scope='session')
+def oracle_c_native(tmp_path_factory):
+    """The C oracle built for THIS host's CPU (-march=native), the build the benchmark times: on a CPU with
+    AVX-512 VNNI its matrix products take the vpdpbusd path, which the portable build never compiles."""
+    import ctypes
+    import subprocess
+
+    out = tmp_path_factory.mktemp('oracle_native') / 'liboracle_native.so'
+    subprocess.run(['make', '-C', str(ROOT / 'oracle'), f'OUT={out}', 'ARCH=-march=native'], check=True,
+                   capture_output=True)
+    return ctypes.CDLL(str(out))

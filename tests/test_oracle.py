@@ -215,3 +215,35 @@ def test_c_edition_matches_numpy_rowops(oracle_c, tok):
                                       oracle.softmax_hccs(x, B=120, S=2, Dmax=59, out_dtype=od))
     np.testing.assert_array_equal(C.softmax(oracle_c, x, mode='hccs', B=120, S=2, Dmax=59, inv_shift=14, use_clb=True),
                                   oracle.softmax_hccs(x, B=120, S=2, Dmax=59, inv_shift=14, use_clb=True))
+
+
+@pytest.mark.parametrize('build', ['portable', 'native'])
+def test_c_edition_blocked_products_wrap_like_the_numpy_oracle(oracle_c, oracle_c_native, build):
+    """The blocked matrix products of the C edition (portable int16 dot products; AVX-512 VNNI with the +128 offset and
+    column-sum correction when the host CPU has it) against the NumPy oracle: ragged shapes around the block sizes,
+    unsigned A, full-range biases that make the 32-bit accumulator wrap, strided and transposed MatMul operands."""
+    lib = oracle_c if build == 'portable' else oracle_c_native
+    rng = np.random.default_rng(60)
+    for M, K, N in ((1, 1, 1), (7, 5, 3), (49, 130, 65), (97, 1031, 129), (6, 4100, 64)):
+        for unsigned in (False, True):
+            a = rng.integers(0 if unsigned else -128, 256 if unsigned else 128, (M, K)).astype(np.uint8 if unsigned else np.int8)
+            w = rng.integers(-128, 128, (K, N)).astype(np.int8)
+            bias = rng.integers(-(1 << 31), 1 << 31, N).astype(np.int32)
+            for tok, shift, od in (('positive_inf', 10, 'int8'), ('conv_even', 3, 'int16'), ('floor', 0, 'uint8')):
+                np.testing.assert_array_equal(C.dense(lib, a, w, bias, shift=shift, tok=tok, relu=True, out_dtype=od),
+                                              oracle.dense(a, w, bias, shift=shift, tok=tok, relu=True, out_dtype=od))
+    # extreme operands: every product at its largest magnitude
+    a = np.full((3, 8192), -128, dtype=np.int8)
+    w = np.full((8192, 5), -128, dtype=np.int8)
+    np.testing.assert_array_equal(C.dense(lib, a, w, None, shift=20, tok='floor', relu=False, out_dtype='int16'),
+                                  oracle.dense(a, w, None, shift=20, tok='floor', relu=False, out_dtype='int16'))
+    q = rng.integers(-128, 128, (4, 128, 64)).astype(np.int8)
+    k = rng.integers(-128, 128, (4, 128, 64)).astype(np.int8)
+    p_u8 = rng.integers(0, 256, (4, 128, 128)).astype(np.uint8)
+    np.testing.assert_array_equal(C.bmm(lib, q, k, shift=9, tok='positive_inf', trans_b=True),
+                                  oracle.matmul(q, k, shift=9, tok='positive_inf', transpose_b=True))
+    np.testing.assert_array_equal(C.bmm(lib, p_u8, k, shift=8, tok='conv_even', out_dtype='int16'),
+                                  oracle.matmul(p_u8, k, shift=8, tok='conv_even', out_dtype='int16'))
+    qt = np.ascontiguousarray(q.transpose(0, 2, 1))
+    np.testing.assert_array_equal(C.bmm(lib, qt, k, shift=9, tok='symmetric_inf', trans_a=True, trans_b=True),
+                                  oracle.matmul(qt, k, shift=9, tok='symmetric_inf', transpose_a=True, transpose_b=True))
