@@ -32,16 +32,20 @@ def shard_inputs(inputs: dict, rank: int, world: int) -> dict:
 
 
 def gather_outputs(local, total_rows: int, group=None):
-    """All-gather row shards of unequal size into the full tensor on every rank.
+    """All-gather row shards into the full tensor on every rank.
 
-    ``local`` is a torch tensor ``[rows_r, ...]``.  Shards are padded to the largest shard so one
-    ``all_gather_into_tensor`` suffices, then trimmed."""
+    ``local`` is a torch tensor ``[rows_r, ...]`` (any strides).  Equal shards gather straight into the result with one
+    ``all_gather_into_tensor``; unequal ones are padded to the largest shard first and trimmed afterwards."""
     import torch
     import torch.distributed as dist
 
     world = dist.get_world_size(group)
     sizes = [shard_rows(total_rows, r, world) for r in range(world)]
     biggest = max(e - s for s, e in sizes)
+    if all(e - s == biggest for s, e in sizes):
+        out = torch.empty((total_rows, *local.shape[1:]), dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(out, local.contiguous(), group=group)
+        return out
     padded = torch.zeros((biggest, *local.shape[1:]), dtype=local.dtype, device=local.device)
     padded[: local.shape[0]] = local
     out = torch.empty((world * biggest, *local.shape[1:]), dtype=local.dtype, device=local.device)

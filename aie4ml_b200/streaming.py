@@ -50,19 +50,61 @@ def gpu_local_cpus(device_index: int) -> Optional[List[int]]:
         return None
 
 
+def gpu_numa_node(device_index: int) -> Optional[int]:
+    """NUMA node the GPU's PCIe slot hangs off (sysfs), or None when the platform does not say."""
+    try:
+        import torch
+
+        props = torch.cuda.get_device_properties(device_index)
+        bdf = f'{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0'
+        with open(f'/sys/bus/pci/devices/{bdf}/numa_node') as fh:
+            node = int(fh.read().strip())
+        return node if node >= 0 else None
+    except Exception:
+        return None
+
+
+_SYS_SET_MEMPOLICY = 238      # x86-64
+_MPOL_DEFAULT, _MPOL_PREFERRED = 0, 1
+
+
+def _set_mempolicy(mode: int, node: Optional[int]) -> bool:
+    """set_mempolicy(2) for the calling thread through the raw system call (no libnuma here).  False when the
+    kernel refuses (another architecture, a cpuset without that node, a sandbox)."""
+    import ctypes
+    import platform
+
+    if platform.machine() != 'x86_64':
+        return False
+    try:
+        libc = ctypes.CDLL(None, use_errno=True)
+        if node is None:
+            return libc.syscall(_SYS_SET_MEMPOLICY, mode, None, 0) == 0
+        mask = (ctypes.c_ulong * 16)()
+        mask[node // 64] = 1 << (node % 64)
+        return libc.syscall(_SYS_SET_MEMPOLICY, mode, mask, 16 * 64 + 1) == 0
+    except Exception:
+        return False
+
+
 class near_gpu:
-    """Context manager: run the calling thread on the CPUs nearest to a GPU, so that host buffers allocated and
-    pinned inside the block land in that NUMA node's memory (first touch); the previous affinity is restored on
-    exit.  Copies between such buffers and the GPU do not cross the socket interconnect.  A no-op when the
-    topology cannot be read."""
+    """Context manager: host buffers allocated and pinned inside the block land in the memory of the NUMA node the
+    GPU is attached to, so copies between them and the GPU do not cross the socket interconnect.  Two means, both
+    undone on exit: the calling thread prefers that node's memory (set_mempolicy, which works even when this
+    process may not run on that node's CPUs), and it runs on the node's CPUs where it is allowed to (first
+    touch).  A no-op when the topology cannot be read."""
 
     def __init__(self, device_index: int):
         self.cpus = gpu_local_cpus(device_index)
+        self.node = gpu_numa_node(device_index)
         self.saved = None
+        self.policy_set = False
 
     def __enter__(self):
         import os
 
+        if self.node is not None:
+            self.policy_set = _set_mempolicy(_MPOL_PREFERRED, self.node)
         if self.cpus and hasattr(os, 'sched_setaffinity'):
             self.saved = os.sched_getaffinity(0)
             os.sched_setaffinity(0, self.cpus)
@@ -73,7 +115,13 @@ class near_gpu:
 
         if self.saved is not None:
             os.sched_setaffinity(0, self.saved)
+        if self.policy_set:
+            _set_mempolicy(_MPOL_DEFAULT, None)
         return False
+
+    def describe(self) -> dict:
+        return {'requested': True, 'gpu_numa_node': self.node, 'memory_policy_preferred_node': bool(self.policy_set),
+                'ran_on_node_cpus': len(self.cpus) if self.cpus else 0}
 
 
 class HostPipeline:
@@ -118,13 +166,15 @@ class HostPipeline:
     def chunks_for(self, rows: int) -> int:
         return (int(rows) + self.chunk_rows - 1) // self.chunk_rows
 
-    def run(self, host_in: Dict[str, 'object'], host_out: Dict[str, 'object']) -> int:
+    def run(self, host_in: Dict[str, 'object'], host_out: Dict[str, 'object'], launches: bool = True) -> int:
         """Stream ``host_in[name][r]`` for every row r through the model into ``host_out``.
 
         Host tensors are torch CPU tensors (pinned for asynchronous copies) shaped ``[rows, ...]``
         with the graph tensor's trailing extents; ``rows`` need not be a multiple of the chunk.  A
         short last chunk runs at full chunk size over whatever the slot's buffers hold beyond the
         copied rows (operators never mix rows), and only its valid rows are copied back.
+        ``launches=False`` leaves the kernels out and keeps every copy and every event: what the host's memory and
+        the PCIe link allow for this chunking (a measurement aid).
         Returns the number of chunks.  The call only enqueues: the caller's current stream is made to
         wait for all three pipeline streams, so synchronise it (or use ``run_and_wait``) before
         reading ``host_out``.
@@ -159,7 +209,8 @@ class HostPipeline:
                 self.s_run.wait_event(self.ev_in[slot])
                 if c >= depth:
                     self.s_run.wait_event(self.ev_out[slot])    # the slot's outputs have been read back
-                plan.run()
+                if launches:
+                    plan.run()
                 self.ev_run[slot].record(self.s_run)
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(self.ev_run[slot])

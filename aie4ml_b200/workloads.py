@@ -24,13 +24,27 @@ def _codes(rng, lo: int, hi: int, shape, dtype=np.int64) -> np.ndarray:
     return rng.integers(lo, hi + 1, size=shape, dtype=dtype)
 
 
+def _gauss_table(sigma: float) -> np.ndarray:
+    """65536-entry inverse-CDF table of clip(round(N(0, sigma^2)), -128, 127): entry u is the value whose
+    cumulative probability interval contains (u + 0.5) / 65536."""
+    import math
+
+    cdf = np.array([0.5 * (1.0 + math.erf((v + 0.5) / (sigma * math.sqrt(2.0)))) for v in range(-128, 127)])
+    q = (np.arange(65536, dtype=np.float64) + 0.5) / 65536.0
+    return (np.searchsorted(cdf, q, side='right') - 128).astype(np.int8)
+
+
 def _gauss_i8(rng, sigma: float, shape) -> np.ndarray:
+    """int8 codes with a Gaussian profile (rounded, clipped to [-128, 127]): uniform 16-bit draws mapped through the
+    inverse CDF of the discretised distribution.  A 2^30-element tensor takes seconds this way; drawing float
+    normals and rounding them takes a minute."""
+    table = _gauss_table(float(sigma))
     out = np.empty(shape, dtype=np.int8)
     flat = out.reshape(-1)
-    step = 1 << 24  # draw in slabs: a 2^30-element float64 normal array would need 8 GiB
+    step = 1 << 26
     for i in range(0, flat.size, step):
         n = min(step, flat.size - i)
-        flat[i:i + n] = np.clip(np.rint(rng.standard_normal(n, dtype=np.float32) * np.float32(sigma)), -128, 127)
+        np.take(table, rng.integers(0, 65536, size=n, dtype=np.uint16), out=flat[i:i + n])
     return out
 
 

@@ -1,4 +1,4 @@
-"""ctypes helpers for the C edition of the oracle (test infrastructure)."""
+"""ctypes binding of the C edition of the oracle (test infrastructure: tests, the benchmark's checker and CPU arm)."""
 
 import ctypes
 from ctypes import c_int, c_int64, c_void_p

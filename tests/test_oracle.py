@@ -4,7 +4,7 @@ recipes must satisfy, float sanity bounds, and agreement between its NumPy and C
 import numpy as np
 import pytest
 
-import oracle_c_api as C
+from oracle import c_api as C
 from oracle import oracle
 
 TOKENS = oracle.ROUNDING_TOKENS
