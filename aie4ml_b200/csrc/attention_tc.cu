@@ -18,11 +18,15 @@
 //               buffers; later O = P V (M128 N64 K128, P K-major from shared memory, V MN-major) into one of
 //               two TMEM output buffers.  The next item's S is issued before this item's O, so the tensor
 //               pipe works on scores while the softmax warps are busy.
-//   warps 2-5   softmax group 0 (even items), warps 6-9 group 1 (odd items).  A thread owns one query row
-//               (its TMEM lane): tcgen05.ld of 128 accumulators, requantise, row maximum, score table lookup
-//               (per-lane replicated table in shared memory: no bank conflicts), sum, reciprocal, normalise,
-//               and the uint8 probabilities go to shared memory in the 128-byte-swizzled K-major layout the
-//               second MMA reads.  Then the same thread converts its O row and stores it.
+//   warps 2-17  softmax: group 0 (even items) and group 1 (odd items) of eight warps each.  TWO threads share a
+//               query row (a TMEM lane): each takes 64 of the 128 score columns -- tcgen05.ld of 64 accumulators,
+//               requantise, maximum, score table lookup (per-lane replicated table in shared memory: no bank
+//               conflicts), sum -- and the two exchange the row maximum and the row sum through shared memory
+//               (a 64-thread named barrier per warp pair).  Each then normalises its half and writes it as uint8
+//               into the 128-byte-swizzled K-major tile the second MMA reads, and later converts and stores 32 of
+//               the row's 64 output columns.  Sixteen such warps give every scheduler four of them to interleave
+//               (with eight, one thread per row, the integer pipe sat 58 % busy behind load latencies); the
+//               register budget is 96 per thread (five of the eighteen warps share one scheduler's 16 K registers).
 // Every wait is bounded (tc::mbar_wait): on a timeout the CTA sets the status word and drains.
 #include <cuda.h>
 
@@ -46,10 +50,18 @@ constexpr int STAGE_BYTES = 3 * TILE_BYTES;
 constexpr int P_BYTES = BM * SK;                  // 16 KB per softmax group
 constexpr int LUT_BYTES = 256 * 32 * 4;
 constexpr int GROUPS = 2;
-constexpr int GROUP_THREADS = 128;
+constexpr int HALVES = 2;                         // threads per query row
+constexpr int HALF_COLS = SK / HALVES;            // score columns per thread
+constexpr int GROUP_THREADS = 128 * HALVES;
 constexpr int NUM_THREADS = 64 + GROUPS * GROUP_THREADS;
+constexpr int MAX_REGS = 96;                      // 18 warps: five share one scheduler's 16384 registers
 constexpr int TMEM_COLS = 512;                    // scores at columns g*128, outputs at 256 + g*64
 constexpr int MODE_HALF_UP_CLAMP = 100;           // positive_inf, both shifts in [1, 22]: saturate before the shift
+// The same with both shifts <= 13 and the shift itself moved to the multiply-add pipe: the clamped value n, |n| < 2^22,
+// is produced as the bit pattern of the float 1.5*2^23 + n, and one round-down FMA by 2^-s leaves
+// 1.5*2^23 + floor(n / 2^s), whose low byte is the result.
+constexpr int MODE_HALF_UP_FLOAT = 102;
+constexpr int MAGIC_BITS = 0x4B400000;            // 1.5 * 2^23
 
 constexpr float TWO_M64 = 5.421010862427522e-20f;  // 2^-64
 constexpr float TWO_P64 = 18446744073709551616.0f; // 2^64
@@ -60,8 +72,11 @@ struct Tail {
     uint64_t s_full[GROUPS];
     uint64_t p_full[GROUPS];
     uint64_t o_full[GROUPS];
+    uint64_t pair[GROUPS][4];     // the two warps that share a group's 32 query rows meet here (one arrival per warp)
     uint32_t tmem_base;
     volatile int abort_flag;
+    // row maximum (slot 0) and row sum (slot 1) of each half row, read by the thread that holds the other half
+    uint32_t xch[GROUPS][2][HALVES][BM];
 };
 
 constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (size_t)GROUPS * P_BYTES + LUT_BYTES + sizeof(Tail);
@@ -73,8 +88,9 @@ struct AttnArgs {
     // requantisation of the scores (1) and of the outputs (2)
     int shift1, shift2;
     uint32_t mask1, c01, mask2, c02;          // generic rounding constants
-    int xhi1, addb1, xlob1;                   // MODE_HALF_UP_CLAMP, biased by +128: see requant_biased
+    int xhi1, addb1, xlob1;                   // MODE_HALF_UP_CLAMP / _FLOAT, biased by +128: see score_code
     int xhi2, half2, xlo2;
+    float fmul1, fadd1, fmul2, fadd2;         // MODE_HALF_UP_FLOAT: 2^-s and 1.5*2^23 * (1 - 2^-s) per step
     // softmax
     int mode, B, S, Dmax, inv_shift, use_clb, exp_kq;
     int* status;
@@ -105,13 +121,16 @@ __device__ __forceinline__ float lds32f(uint32_t a) {
     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
     return v;
 }
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ void sts32(uint32_t a, uint32_t v) {
+    asm volatile("st.shared.u32 [%0], %1;" :: "r"(a), "r"(v) : "memory");
+}
 __device__ __forceinline__ void sts128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" :: "r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
-}
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-    uint32_t d;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-    return d;
 }
 
 // exp_score16, softmax.cpp:252-273
@@ -125,9 +144,14 @@ __device__ __forceinline__ int exp_score16(int d, int kq) {
     return zint >= 16 ? 0 : (e >> (zint & 15));
 }
 
-// Score accumulator -> int8 score + 128 (an unsigned byte whose order is the signed order).
+// Score accumulator -> int8 score + 128 (an unsigned byte whose order is the signed order), plus the constant
+// code_bias<MODE>() in the upper bits: differences and maxima of two codes are those of the scores.
 template <int MODE>
-__device__ __forceinline__ int requant_biased(int acc, const AttnArgs& g) {
+__device__ __forceinline__ int score_code(int acc, const AttnArgs& g) {
+    if (MODE == MODE_HALF_UP_FLOAT) {
+        const int u = __viaddmax_s32(min(acc, g.xhi1), g.addb1 + MAGIC_BITS, g.xlob1 + MAGIC_BITS);
+        return __float_as_int(__fmaf_rd(__int_as_float(u), g.fmul1, g.fadd1));
+    }
     if (MODE == MODE_HALF_UP_CLAMP) {
         // min(acc, 127 * 2^s), then + 2^(s-1) + 128 * 2^s with the lower clamp folded in, then the shift
         return __viaddmax_s32(min(acc, g.xhi1), g.addb1, g.xlob1) >> g.shift1;
@@ -138,8 +162,13 @@ __device__ __forceinline__ int requant_biased(int acc, const AttnArgs& g) {
     return min(max(v, -128), 127) + 128;
 }
 
+// Output accumulator -> a word whose low byte is the int8 result.
 template <int MODE>
 __device__ __forceinline__ int requant_out(int acc, const AttnArgs& g) {
+    if (MODE == MODE_HALF_UP_FLOAT) {
+        const int u = __viaddmax_s32(min(acc, g.xhi2), g.half2 + MAGIC_BITS, g.xlo2 + MAGIC_BITS);
+        return __float_as_int(__fmaf_rd(__int_as_float(u), g.fmul2, g.fadd2));
+    }
     if (MODE == MODE_HALF_UP_CLAMP) return __viaddmax_s32(min(acc, g.xhi2), g.half2, g.xlo2) >> g.shift2;
     int v = acc;
     if (MODE == A4C_RND_FLOOR) v = acc >> g.shift2;
@@ -148,7 +177,7 @@ __device__ __forceinline__ int requant_out(int acc, const AttnArgs& g) {
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __maxnreg__(MAX_REGS)
 attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, AttnArgs g) {
     extern __shared__ uint8_t smem_raw[];
@@ -172,6 +201,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             mbar_init(&tail->s_full[s], 1);
             mbar_init(&tail->p_full[s], GROUP_THREADS);
             mbar_init(&tail->o_full[s], 1);
+            for (int q = 0; q < 4; ++q) mbar_init(&tail->pair[s][q], HALVES);
         }
         tail->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -271,15 +301,30 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         }
         __syncwarp();
     } else {
-        // ---------------- softmax + output (two groups of four warps) ----------------
-        const int grp = (warp - 2) >> 2;
+        // ---------------- softmax + output (two groups of eight warps, two threads per query row) ----------------
         const int quad = warp & 3;                   // TMEM lane quadrant of this warp
+        const int grp = (warp - 2) >> 3;             // warps 2-9: even items, warps 10-17: odd items
+        const int hf = ((warp - 2) >> 2) & 1;        // which 64 score columns (and which 32 output columns)
         const int r = quad * 32 + lane;              // query row inside the tile
+        uint64_t* pair_bar = &tail->pair[grp][quad];   // where the two warps that share these rows meet (bounded wait)
+        uint32_t pair_phase = 0;
+        // Both warps have written their shared-memory words; returns once the other warp's are readable.
+        auto pair_sync = [&]() -> bool {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(pair_bar);
+            const bool met = mbar_wait(pair_bar, pair_phase, abort_flag, g.status, 126);
+            pair_phase ^= 1u;
+            return met;
+        };
         const uint32_t lut_lane = smem_u32(lut) + (uint32_t)lane * 4u;
         const uint32_t p_row = smem_u32(p_smem + (size_t)grp * P_BYTES) + (uint32_t)r * 128u;
         const uint32_t sw = (uint32_t)(r & 7);
-        const uint32_t taddr_s = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(grp * SK);
-        const uint32_t taddr_o = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(2 * SK + grp * DH);
+        const uint32_t taddr_s = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(grp * SK + hf * HALF_COLS);
+        const uint32_t taddr_o = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(2 * SK + grp * DH + hf * (DH / HALVES));
+        // exchange words as shared-space addresses: slot 0 (maximum) here, slot 1 (sum) XCH_SLOT bytes further
+        const uint32_t xch_mine = smem_u32(&tail->xch[grp][0][hf][r]);
+        const uint32_t xch_other = smem_u32(&tail->xch[grp][0][hf ^ 1][r]);
+        constexpr uint32_t XCH_SLOT = HALVES * BM * 4;
         const int numer = 255 << g.inv_shift;
         const float numer_f = (float)numer;
         const float out_mul = __int_as_float((127 - (g.inv_shift + 85)) << 23);  // 2^-(inv_shift + 85)
@@ -296,39 +341,41 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             if (!ok) break;
             tc_fence_after();
 
-            // scores: 128 accumulators -> biased bytes, and the row maximum
-            uint32_t pw[SK / 4];
-            int m = 0;
-            {
-                uint32_t acc[SK];
+            // this thread's 64 scores: accumulators -> codes (score + 128, plus a constant in the upper bits)
+            uint32_t v[HALF_COLS];
+            tmem_ld32_async(taddr_s, v);
+            tmem_ld32_async(taddr_s + 32u, v + 32);
+            tmem_ld_wait32(v);
+            tmem_ld_wait32(v + 32);
+            int m = (int)0x80000000;
 #pragma unroll
-                for (int c = 0; c < SK / 32; ++c) tmem_ld32_async(taddr_s + (uint32_t)(c * 32), acc + c * 32);
-#pragma unroll
-                for (int c = 0; c < SK / 32; ++c) tmem_ld_wait32(acc + c * 32);
-#pragma unroll
-                for (int i = 0; i < SK / 4; ++i) {
-                    const int u0 = requant_biased<MODE>((int)acc[4 * i + 0], g), u1 = requant_biased<MODE>((int)acc[4 * i + 1], g);
-                    const int u2 = requant_biased<MODE>((int)acc[4 * i + 2], g), u3 = requant_biased<MODE>((int)acc[4 * i + 3], g);
-                    m = __vimax3_s32(m, u0, u1);
-                    m = __vimax3_s32(m, u2, u3);
-                    pw[i] = pack4_i8(u0, u1, u2, u3);
-                }
+            for (int i = 0; i < HALF_COLS; i += 2) {
+                const int c0 = score_code<MODE>((int)v[i], g), c1 = score_code<MODE>((int)v[i + 1], g);
+                v[i] = (uint32_t)c0;
+                v[i + 1] = (uint32_t)c1;
+                m = __vimax3_s32(m, c0, c1);
             }
-            const uint32_t m4 = (uint32_t)m * 0x01010101u;
-            float e[SK];
+            sts32(xch_mine, (uint32_t)m);
+            ok = pair_sync();
+            if (!ok) break;
+            m = max(m, (int)lds32(xch_other));
+            // table address of score code c: lut_lane + (m - c) * 128, as one multiply-add
+            const uint32_t row_base = lut_lane + (uint32_t)m * 128u;
             float fs0 = 0.0f, fs1 = 0.0f;
 #pragma unroll
-            for (int i = 0; i < SK / 4; ++i) {
-                const uint32_t dw = m4 - pw[i];   // per byte: maximum - score, no borrows
-                e[4 * i + 0] = lds32f(prmt(dw, 0, 0x4440) * 128u + lut_lane);
-                e[4 * i + 1] = lds32f(prmt(dw, 0, 0x4441) * 128u + lut_lane);
-                e[4 * i + 2] = lds32f(prmt(dw, 0, 0x4442) * 128u + lut_lane);
-                e[4 * i + 3] = lds32f(prmt(dw, 0, 0x4443) * 128u + lut_lane);
-                fs0 += e[4 * i + 0] + e[4 * i + 2];
-                fs1 += e[4 * i + 1] + e[4 * i + 3];
+            for (int i = 0; i < HALF_COLS; i += 2) {   // each code is replaced by (the bits of) its table entry
+                const float e0 = lds32f(row_base - v[i] * 128u), e1 = lds32f(row_base - v[i + 1] * 128u);
+                v[i] = __float_as_uint(e0);
+                v[i + 1] = __float_as_uint(e1);
+                fs0 += e0;
+                fs1 += e1;
             }
-            // exact: at most 128 scores <= 32767 (scaled by 2^-64)
-            const int sum = __float2int_rn((fs0 + fs1) * TWO_P64);
+            // exact: at most 128 scores <= 32767 (scaled by 2^-64), whatever the order of the additions
+            const float fs = fs0 + fs1;
+            sts32(xch_mine + XCH_SLOT, __float_as_uint(fs));
+            ok = pair_sync();
+            if (!ok) break;
+            const int sum = __float2int_rn((fs + __uint_as_float(lds32(xch_other + XCH_SLOT))) * TWO_P64);
             const int s = sum > 0 ? sum : 1;
             int inv;
             if (clb) {
@@ -346,7 +393,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             inv = min(max(inv, 0), 32767);
             const float invs = (float)inv * out_mul;
 #pragma unroll
-            for (int c = 0; c < SK / 16; ++c) {
+            for (int c = 0; c < HALF_COLS / 16; ++c) {
                 uint32_t w[4];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
@@ -354,34 +401,32 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                     // floor(score * inv / 2^shift) in the low bits of a subnormal (scores are non-negative)
                     // with inv = floor(255 * 2^shift / sum) a score <= sum cannot exceed 255; only the power-of-two
                     // reciprocal (use_clb) needs the saturation
-                    int o0 = __float_as_int(__fmaf_rd(e[i + 0], invs, 0.0f));
-                    int o1 = __float_as_int(__fmaf_rd(e[i + 1], invs, 0.0f));
-                    int o2 = __float_as_int(__fmaf_rd(e[i + 2], invs, 0.0f));
-                    int o3 = __float_as_int(__fmaf_rd(e[i + 3], invs, 0.0f));
+                    int o0 = __float_as_int(__fmaf_rd(__uint_as_float(v[i + 0]), invs, 0.0f));
+                    int o1 = __float_as_int(__fmaf_rd(__uint_as_float(v[i + 1]), invs, 0.0f));
+                    int o2 = __float_as_int(__fmaf_rd(__uint_as_float(v[i + 2]), invs, 0.0f));
+                    int o3 = __float_as_int(__fmaf_rd(__uint_as_float(v[i + 3]), invs, 0.0f));
                     if (clb) { o0 = min(o0, 255); o1 = min(o1, 255); o2 = min(o2, 255); o3 = min(o3, 255); }
                     w[q] = pack4_i8(o0, o1, o2, o3);
                 }
-                // K-major, 128-byte swizzle: 16-byte piece c of row r sits at piece c ^ (r & 7)
-                sts128(p_row + (((uint32_t)c ^ sw) << 4), w[0], w[1], w[2], w[3]);
+                // K-major, 128-byte swizzle: 16-byte piece p of row r sits at piece p ^ (r & 7)
+                sts128(p_row + ((((uint32_t)(hf * (HALF_COLS / 16) + c)) ^ sw) << 4), w[0], w[1], w[2], w[3]);
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> tensor-core reads
             tc_fence_before();
             mbar_arrive(&tail->p_full[grp]);
 
-            // output row
+            // this thread's 32 columns of the output row
             ok = mbar_wait(&tail->o_full[grp], par, abort_flag, g.status, 125);
             if (!ok) break;
             tc_fence_after();
-            uint32_t oa[DH];
+            uint32_t oa[DH / HALVES];
             tmem_ld32_async(taddr_o, oa);
-            tmem_ld32_async(taddr_o + 32u, oa + 32);
             tmem_ld_wait32(oa);
-            tmem_ld_wait32(oa + 32);
             tc_fence_before();
             if (row < g.sq) {
-                uint8_t* orow = g.out + b * g.stride_o + h * g.hstride_o + (long long)row * g.ldo;
+                uint8_t* orow = g.out + b * g.stride_o + h * g.hstride_o + (long long)row * g.ldo + hf * (DH / HALVES);
 #pragma unroll
-                for (int c = 0; c < DH / 16; ++c) {
+                for (int c = 0; c < DH / HALVES / 16; ++c) {
                     uint32_t w[4];
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
@@ -515,6 +560,14 @@ int a4c_launch_attention_tc(const void* q, long long ldq, long long stride_q, co
     const bool pre_clamp = rounding == A4C_RND_POSITIVE_INF && qk_shift >= 1 && qk_shift <= 22 && pv_shift >= 1 &&
                            pv_shift <= 22;
     g.xhi1 = g.addb1 = g.xlob1 = g.xhi2 = g.half2 = g.xlo2 = 0;
+    g.fmul1 = g.fadd1 = g.fmul2 = g.fadd2 = 0.0f;
+    const bool float_shift = pre_clamp && qk_shift <= 13 && pv_shift <= 13;
+    if (float_shift) {
+        g.fmul1 = 1.0f / (float)(1 << qk_shift);
+        g.fadd1 = 12582912.0f - 12582912.0f * g.fmul1;
+        g.fmul2 = 1.0f / (float)(1 << pv_shift);
+        g.fadd2 = 12582912.0f - 12582912.0f * g.fmul2;
+    }
     if (pre_clamp) {
         g.xhi1 = 127 * (1 << qk_shift);
         g.addb1 = (1 << (qk_shift - 1)) + 128 * (1 << qk_shift);
@@ -532,6 +585,7 @@ int a4c_launch_attention_tc(const void* q, long long ldq, long long stride_q, co
     const int grid = (int)(items < sms ? items : sms);
     cudaError_t err;
     if (qk_shift == 0) err = launch_mode<-1>(mq, mk, mv, g, grid, stream);
+    else if (float_shift) err = launch_mode<MODE_HALF_UP_FLOAT>(mq, mk, mv, g, grid, stream);
     else if (pre_clamp) err = launch_mode<MODE_HALF_UP_CLAMP>(mq, mk, mv, g, grid, stream);
     else switch (rounding) {
         case A4C_RND_FLOOR: err = launch_mode<A4C_RND_FLOOR>(mq, mk, mv, g, grid, stream); break;

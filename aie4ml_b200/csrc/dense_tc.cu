@@ -126,7 +126,7 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int
 
 // One epilogue warp turns 32 rows x 64 accumulator columns (two TMEM loads, `r`) into int8 in its shared-memory
 // patch and hands the patch to a TMA store (which clips rows >= M and columns >= N).
-template <int MODE>
+template <int MODE, bool HAS_BIAS>
 __device__ __forceinline__ void epilogue_pair(const uint32_t* r, const int32_t* bias64, uint8_t* my_stage, int lane,
                                               const TcArgs& g, const CUtensorMap* tmap_y, int row0, int col0) {
     // the previous store out of this patch must have read it before it is overwritten
@@ -134,16 +134,18 @@ __device__ __forceinline__ void epilogue_pair(const uint32_t* r, const int32_t* 
     __syncwarp();
     const int sw_w = (lane >> 1) & 3;   // 64-byte swizzle: 16-byte piece p of row l sits at piece p ^ ((l >> 1) & 3)
     // the 64 bias values are the same for every lane (a lane is a row): broadcast loads, issued one 16-column
-    // piece ahead of their use so that their latency hides under the previous piece's arithmetic
+    // piece ahead of their use so that their latency hides under the previous piece's arithmetic.  A layer without
+    // a bias (HAS_BIAS false) issues none of them: shared-memory reads queue behind the operand fetch of the MMAs,
+    // and with the tensor pipe busy these loads alone doubled the time of a group.
     int4 bnext[4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) bnext[q] = *reinterpret_cast<const int4*>(bias64 + q * 4);
+    for (int q = 0; q < 4; ++q) bnext[q] = HAS_BIAS ? *reinterpret_cast<const int4*>(bias64 + q * 4) : make_int4(0, 0, 0, 0);
 #pragma unroll
     for (int piece = 0; piece < 4; ++piece) {
         int4 b[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) b[q] = bnext[q];
-        if (piece < 3) {
+        if (HAS_BIAS && piece < 3) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) bnext[q] = *reinterpret_cast<const int4*>(bias64 + (piece + 1) * 16 + q * 4);
         }
@@ -174,8 +176,8 @@ __device__ __forceinline__ void epilogue_pair(const uint32_t* r, const int32_t* 
     }
 }
 
-// MODE = rounding token, or -1 when shift == 0 (no rounding step).
-template <int MODE>
+// MODE = rounding token, or -1 when shift == 0 (no rounding step).  HAS_BIAS = the layer has a bias vector.
+template <int MODE, bool HAS_BIAS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 dense_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const __grid_constant__ CUtensorMap tmap_y, TcArgs g) {
@@ -302,7 +304,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         uint8_t* my_stage = epi_stage + (size_t)(warp - 2) * EPI_STAGE_BYTES;
         uint32_t acc_phase = 0;
         bool ok = true;
-        const bool bias_resident = g.num_n_tiles * BN <= BIAS_CACHE;
+        const bool bias_resident = HAS_BIAS && g.num_n_tiles * BN <= BIAS_CACHE;
         if (bias_resident) {
             // the whole (zero-padded) bias vector once: no global load on any tile's critical path
             for (int i = threadIdx.x - 64; i < g.num_n_tiles * BN; i += EPI_THREADS)
@@ -323,7 +325,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             mt += step_m; nt += step_n;
             if (nt >= nnt) { nt -= nnt; ++mt; }
             const int32_t* tile_bias = tail->bias + (bias_resident ? n0 : grp * BN);
-            if (!bias_resident) {
+            if (HAS_BIAS && !bias_resident) {
                 // stage this tile's bias slice (zero where there is none); the group's previous tile is done with it
                 asm volatile("bar.sync %0, 128;" :: "r"(2 + grp) : "memory");
                 for (int i = gt; i < BN; i += EPI_GROUP_THREADS) {
@@ -355,7 +357,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     tc_fence_before();
                     mbar_arrive(&tail->tmem_empty[grp]);
                 }
-                if (have) epilogue_pair<MODE>(ra, tile_bias + c * 64, my_stage, lane, g, &tmap_y, row_base, n0 + c * 64);
+                if (have) epilogue_pair<MODE, HAS_BIAS>(ra, tile_bias + c * 64, my_stage, lane, g, &tmap_y, row_base, n0 + c * 64);
             }
         }
         // the stores this warp issued must be complete (not merely read) before the CTA retires
@@ -427,10 +429,16 @@ bool make_out_map(CUtensorMap* map, void* base, long long rows, long long cols, 
 template <int MODE>
 cudaError_t launch_mode(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& my, const TcArgs& g, int grid,
                         cudaStream_t s) {
-    static tc::SmemOptIn opt_in;
-    const cudaError_t attr_err = opt_in.ensure(dense_tc_kernel<MODE>, SMEM_BYTES);
-    if (attr_err != cudaSuccess) return attr_err;
-    dense_tc_kernel<MODE><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(ma, mb, my, g);
+    static tc::SmemOptIn opt_in[2];
+    if (g.bias != nullptr) {
+        const cudaError_t attr_err = opt_in[1].ensure(dense_tc_kernel<MODE, true>, SMEM_BYTES);
+        if (attr_err != cudaSuccess) return attr_err;
+        dense_tc_kernel<MODE, true><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(ma, mb, my, g);
+    } else {
+        const cudaError_t attr_err = opt_in[0].ensure(dense_tc_kernel<MODE, false>, SMEM_BYTES);
+        if (attr_err != cudaSuccess) return attr_err;
+        dense_tc_kernel<MODE, false><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(ma, mb, my, g);
+    }
     return cudaGetLastError();
 }
 

@@ -247,3 +247,88 @@ def test_c_edition_blocked_products_wrap_like_the_numpy_oracle(oracle_c, oracle_
     qt = np.ascontiguousarray(q.transpose(0, 2, 1))
     np.testing.assert_array_equal(C.bmm(lib, qt, k, shift=9, tok='symmetric_inf', trans_a=True, trans_b=True),
                                   oracle.matmul(qt, k, shift=9, tok='symmetric_inf', transpose_a=True, transpose_b=True))
+
+
+# ---- float cross-checks: dequantised oracle output against a float64 evaluation of the same layer ------------------
+# (what the reference's own checker does with ONNX Runtime, scripts/check_onnx_bit_exact.py:37-46,170-179)
+
+@pytest.mark.parametrize('seed', [0, 1, 2])
+def test_matmul_and_add_within_one_lsb_of_float_evaluation(seed):
+    rng = np.random.default_rng(100 + seed)
+    for (bsz, m, k, n), shift in (((3, 16, 64, 24), 9), ((2, 128, 64, 128), 9), ((1, 33, 130, 7), 6)):
+        a = rng.integers(-128, 128, (bsz, m, k)).astype(np.int8)
+        b = rng.integers(-128, 128, (bsz, k, n)).astype(np.int8)
+        f = np.matmul(a.astype(np.float64), b.astype(np.float64)) / float(1 << shift)
+        # an int32 sum of int8 products is exact in float64, so rint of it IS convergent rounding: 0 LSB there,
+        # at most 1 LSB for the other nearest modes (they differ from it on exact ties only) and for floor / ceil
+        np.testing.assert_array_equal(oracle.matmul(a, b, shift=shift, tok='conv_even'), np.clip(np.rint(f), -128, 127))
+        for tok in ('positive_inf', 'symmetric_inf', 'symmetric_zero', 'floor', 'ceil'):
+            assert np.abs(oracle.matmul(a, b, shift=shift, tok=tok) - np.clip(np.rint(f), -128, 127)).max() <= 1, tok
+        bt = np.ascontiguousarray(np.swapaxes(b, 1, 2))
+        np.testing.assert_array_equal(oracle.matmul(a, bt, shift=shift, tok='conv_even', transpose_b=True),
+                                      np.clip(np.rint(f), -128, 127))
+        p = rng.integers(0, 256, (bsz, m, k)).astype(np.uint8)     # probabilities times values: unsigned left operand
+        fp = np.matmul(p.astype(np.float64), b.astype(np.float64)) / 256.0
+        np.testing.assert_array_equal(oracle.matmul(p, b, shift=8, tok='conv_even'), np.clip(np.rint(fp), -128, 127))
+    for dt, lo, hi in (('int8', -128, 127), ('uint8', 0, 255), ('int16', -32768, 32767)):
+        x = rng.integers(lo, hi + 1, (40, 96)).astype(C.NP[dt])
+        y = rng.integers(lo, hi + 1, (40, 96)).astype(x.dtype)
+        # same type on both sides and on the result: shift 0, the float sum clipped to the type IS the result (0 LSB)
+        np.testing.assert_array_equal(oracle.add(x, y, shift=0, tok='conv_even', out_dtype=dt),
+                                      np.clip(x.astype(np.float64) + y.astype(np.float64), lo, hi))
+        for tok in ('conv_even', 'positive_inf', 'floor'):
+            f = (x.astype(np.float64) + y.astype(np.float64)) / 2.0
+            assert np.abs(oracle.add(x, y, shift=1, tok=tok, out_dtype=dt) - np.clip(np.rint(f), lo, hi)).max() <= 1
+
+
+@pytest.mark.parametrize('cols,bound', [(32, 1.5), (128, 1.5), (256, 1.5), (1024, 2.25)])
+def test_softmax_exp_lsb_bound_against_float_softmax_over_widths_and_seeds(cols, bound):
+    """Against a float softmax at the temperature the integer kernel actually uses (2^(-d * EXP_KQ / 256): EXP_KQ is
+    a rounded contract parameter, its rounding is not the kernel's error), in uint8 output steps.  Measured worst
+    cases over these inputs: 1.36 / 1.35 / 1.38 / 2.06 steps at 32 / 128 / 256 / 1024 columns."""
+    worst = 0.0
+    for seed in range(8):
+        for sigma, frac in ((24, 4), (32, 4), (16, 3), (40, 5), (32, 2)):
+            rng = np.random.default_rng(seed)
+            x = np.clip(np.rint(rng.normal(0, sigma, (64, cols))), -128, 127).astype(np.int8)
+            kq = oracle.exp_kq(frac)
+            out = oracle.softmax_exp(x, exp_kq=kq).astype(np.float64)
+            d = x.astype(np.int64).max(axis=1, keepdims=True) - x
+            p = np.exp2(-d * kq / 256.0)
+            p /= p.sum(axis=1, keepdims=True)
+            worst = max(worst, float(np.abs(out - 255.0 * p).max()))
+    assert worst <= bound, worst
+
+
+@pytest.mark.parametrize('cols,params', [(32, (1000, 10, 90)), (128, (200, 3, 66)), (1024, (31, 1, 30))])
+def test_softmax_hccs_lsb_bound_against_its_real_valued_definition(cols, params):
+    """The surrogate normalised in real arithmetic, score / sum(score) * 255: the integer kernel loses at most the
+    two floors (reciprocal, product): 1.03 uint8 steps measured, bound 1.25."""
+    B, S, Dmax = params
+    for seed in range(6):
+        rng = np.random.default_rng(seed)
+        x = np.clip(np.rint(rng.normal(0, 32, (64, cols))), -128, 127).astype(np.int8)
+        out = oracle.softmax_hccs(x, B=B, S=S, Dmax=Dmax).astype(np.float64)
+        d = np.minimum(x.astype(np.int64).max(axis=1, keepdims=True) - x, Dmax)
+        score = (B - S * d).astype(np.float64)
+        assert np.abs(out - 255.0 * score / score.sum(axis=1, keepdims=True)).max() <= 1.25
+
+
+@pytest.mark.parametrize('cols', [64, 256, 1024])
+@pytest.mark.parametrize('tok,bound', [('conv_even', 1.9), ('positive_inf', 1.9), ('floor', 2.4)])
+def test_layer_norm_lsb_bound_against_float_layer_norm_over_widths_and_seeds(cols, tok, bound):
+    """int8 output steps against float64 LayerNorm with the same gamma (Q7), beta (Q15) and epsilon.  Measured worst
+    cases: 1.66 steps with the nearest modes, 2.15 with floor (Q15 reciprocal std, Q7 scale and the mean's rounding
+    each contribute a fraction of a step)."""
+    worst = 0.0
+    for seed in range(6):
+        rng = np.random.default_rng(seed)
+        x = np.clip(np.rint(rng.normal(3, 30, (64, cols))), -128, 127).astype(np.int8)
+        gamma, beta = rng.integers(-256, 257, cols), rng.integers(-256, 257, cols)
+        for out_shift in (4, 5):
+            y = oracle.layer_norm(x, gamma, beta, eps_q0=1, out_shift=out_shift, tok=tok).astype(np.float64)
+            xf = x.astype(np.float64)
+            norm = (xf - xf.mean(axis=1, keepdims=True)) / np.sqrt(xf.var(axis=1, keepdims=True) + 1.0)
+            ref = (norm * (gamma / 128.0) + beta / 32768.0) * (1 << out_shift)
+            worst = max(worst, float(np.abs(y - np.clip(ref, -128, 127)).max()))
+    assert worst <= bound, worst
