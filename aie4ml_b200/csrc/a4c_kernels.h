@@ -103,3 +103,11 @@ bool a4c_note_cuda(cudaError_t e);
 // clears it when non-zero.  *out = 0 and A4C_OK when the array has not been set up on the current device.  The
 // caller has synchronised whatever work could still write the word.  Allocates nothing.
 int a4c_mlp_static_status_take(int* out);
+
+// tcgen05 floating-point Dense (dense_tcf.cu): kind 0 = bfloat16 (kind::f16), 2 = fp8 E4M3 (kind::f8f6f4), float32
+// accumulation.  Pitches in elements.  _supported returns 0 or the A4C_ERR_* code that says why not.
+int a4c_dense_tcf_supported(const void* A, long long lda, const void* Wt, long long ldw, const void* Y, long long ldy,
+                            long long M, int K, int N, int kind);
+int a4c_launch_dense_tcf(const void* A, long long lda, const void* Wt, long long ldw, const float* bias, void* Y,
+                         long long ldy, long long M, int K, int N, int relu, int kind, int* status_word,
+                         cudaStream_t stream);

@@ -14,6 +14,7 @@ int* g_status[kMaxDevices] = {nullptr};
 thread_local const char* t_last_cuda_error = "no error";
 int g_rowop_path = 0;  // 0 auto (fast kernels when they apply), 1 generic kernels only
 int g_bmm_path = 0;    // 0 auto (tcgen05 when its rules hold), 1 dp4a kernel only
+int g_float_path = 0;  // 0 auto (tcgen05 Dense for bfloat16 / fp8 when its rules hold), 1 tiled SIMT kernel only
 
 bool note(cudaError_t e) {
     if (e != cudaSuccess) {
@@ -204,6 +205,13 @@ int a4c_dense_f(const void* A, int fdtype, int64_t lda, const void* Wt, int64_t 
                 int64_t ldy, int64_t M, int K, int N, int relu, void* stream) {
     if (A == nullptr || Wt == nullptr || Y == nullptr) return A4C_ERR_INVALID_ARG;
     if (M < 0 || K <= 0 || N <= 0 || lda < K || ldw < K || ldy < N || (fdtype < 0 || fdtype > 2)) return A4C_ERR_INVALID_ARG;
+    if (g_float_path == 0 && a4c_dense_tcf_supported(A, lda, Wt, ldw, Y, ldy, M, K, N, fdtype) == A4C_OK) {
+        int* word = status_word();
+        if (word == nullptr) return A4C_ERR_CUDA;
+        const int trc = a4c_launch_dense_tcf(A, lda, Wt, ldw, bias, Y, ldy, M, K, N, relu, fdtype, word, (cudaStream_t)stream);
+        if (trc != A4C_OK) { if (trc == A4C_ERR_CUDA) note(cudaGetLastError()); return trc; }
+        return finish();
+    }
     const int rc = a4c_launch_gemm_float(A, lda, 1, 0, Wt, 1, ldw, 0, bias, Y, ldy, 0, 1, M, K, N, relu, fdtype,
                                          (cudaStream_t)stream);
     if (rc != A4C_OK) { if (rc == A4C_ERR_CUDA) note(cudaGetLastError()); return rc; }
@@ -287,6 +295,10 @@ int a4c_set_option(int option, int value) {
     }
     if (option == A4C_OPT_BMM_PATH && (value == 0 || value == 1)) {
         g_bmm_path = value;
+        return A4C_OK;
+    }
+    if (option == A4C_OPT_FLOAT_DENSE_PATH && (value == 0 || value == 1)) {
+        g_float_path = value;
         return A4C_OK;
     }
     if (option == A4C_OPT_DENSE_RESIDENT_W && (value == 0 || value == 1)) {

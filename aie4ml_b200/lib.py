@@ -30,6 +30,7 @@ OPT_ROWOP_MIN_STAGES = 3
 OPT_ROWOP_CONTIG_COPY = 6
 OPT_MLP_PATH = 4
 OPT_DENSE_RESIDENT_W = 5
+OPT_FLOAT_DENSE_PATH = 7
 
 # name -> (restype, argtypes); mirrors the header declaration by declaration
 SIGNATURES = {

@@ -54,6 +54,7 @@ extern "C" {
 #define A4C_OPT_ROWOP_PATH 0 /* 0 = auto (bandwidth-oriented row kernels when they apply), 1 = generic kernels only */
 #define A4C_OPT_BMM_PATH 1   /* 0 = auto (tcgen05 batched MatMul when its alignment rules hold), 1 = dp4a kernel only */
 #define A4C_OPT_DENSE_RESIDENT_W 5 /* tcgen05 Dense, K <= 512: 1 (default) = a CTA keeps its weight tile in shared memory and streams A only, 0 = off */
+#define A4C_OPT_FLOAT_DENSE_PATH 7 /* a4c_dense_f, bfloat16 / fp8: 0 = auto (tcgen05 kernel when its alignment rules hold), 1 = tiled SIMT kernel only */
 #define A4C_OPT_MLP_PATH 4   /* a4c_mlp_i8: 0 = auto, 1 = one Dense launch per layer, 2 = the single-kernel narrow chain only */
 /* Tuning of the bandwidth-oriented row kernels (results do not depend on either): */
 #define A4C_OPT_ROWOP_CHUNKS_PER_LANE 2 /* 0 = automatic (default), else 1, 2 or 4: 16-element chunks of one row per lane */
@@ -187,6 +188,9 @@ A4C_API int a4c_dense_ta(const void* A, int a_dtype, int64_t lda, int64_t stride
  * variant, the reference's 'fp8_e4m3' of src/aie4ml/aie_types.py:38, tensors hold the 8 bits; results beyond
  * +-448 saturate); accumulation in float32, bias float32, optional ReLU, results rounded to nearest-even into the
  * storage type.  Pitches / strides in elements.
+ * a4c_dense_f with bfloat16 or fp8 operands runs on the tensor cores (tcgen05.mma kind::f16 / kind::f8f6f4, float32
+ * accumulators in TMEM) when A, W^T and Y start on 16 bytes, their pitches are multiples of 16 bytes and K spans at
+ * least 32 bytes; otherwise, and for float32, on a tiled SIMT kernel (any shape and stride).
  * Held to the reference's tolerances (tests/test_float_sim.py:87-93), not to bit equality.
  */
 A4C_API int a4c_dense_f(const void* A, int fdtype, int64_t lda, const void* Wt, int64_t ldw, const float* bias, void* Y,

@@ -258,3 +258,39 @@ def bmm16(a, b, *, shift, tok, trans_a=False, trans_b=False, out_dtype='int16'):
                        ROUNDING_CODE[tok], DTYPE_CODE[out_dtype], stream())
     a4c.check(rc, 'a4c_bmm_i16')
     return c_d.cpu().numpy()
+
+
+def dense_float(a, w_kn, bias, *, relu, fmt, simt=False):
+    """Floating-point Dense through a4c_dense_f.  a [M, K] and w_kn [K, N] are float arrays; they are rounded to the
+    storage type `fmt` ('bfloat16' / 'fp8_e4m3' / 'float32') first.  Returns (float32 result, stored a, stored w) so the
+    caller can evaluate its reference on exactly what the kernel saw.  simt=True forces the tiled SIMT kernel."""
+    from aie4ml_b200 import quant_utils as Q
+
+    L = a4c.load()
+    M, K = a.shape
+    N = w_kn.shape[1]
+    esz = {'bfloat16': 2, 'fp8_e4m3': 1, 'float32': 4}[fmt]
+    code = {'bfloat16': 0, 'float32': 1, 'fp8_e4m3': 2}[fmt]
+    pad = lambda n: (n * esz + 15) // 16 * 16 // esz
+    a_bits, a_val = Q.to_storage_float(a, fmt)
+    w_bits, w_val = Q.to_storage_float(np.ascontiguousarray(w_kn.T), fmt)
+    lda, ldw, ldy = pad(K), pad(K), pad(N)
+    a_buf = np.zeros((M, lda), dtype=a_bits.dtype); a_buf[:, :K] = a_bits
+    w_buf = np.zeros((N, ldw), dtype=w_bits.dtype); w_buf[:, :K] = w_bits
+    a_d, w_d = dev(a_buf), dev(w_buf)
+    b_d = dev(bias.astype(np.float32)) if bias is not None else None
+    y_d = torch.zeros((M, ldy), dtype={2: torch.int16, 1: torch.uint8, 4: torch.float32}[esz], device='cuda')
+    L.a4c_set_option(a4c.OPT_FLOAT_DENSE_PATH, 1 if simt else 0)
+    try:
+        rc = L.a4c_dense_f(a_d.data_ptr(), code, lda, w_d.data_ptr(), ldw, b_d.data_ptr() if b_d is not None else None,
+                           y_d.data_ptr(), ldy, M, K, N, int(relu), stream())
+        a4c.check(rc, 'a4c_dense_f')
+        a4c.device_status(stream())
+    finally:
+        L.a4c_set_option(a4c.OPT_FLOAT_DENSE_PATH, 0)
+    y = y_d.cpu().numpy()
+    assert (y[:, N:] == 0).all(), 'kernel wrote into the row padding'
+    bits = y[:, :N]
+    if fmt == 'bfloat16':
+        bits = bits.view(np.uint16) if bits.dtype != np.uint16 else bits
+    return Q.from_storage_float(np.ascontiguousarray(bits), fmt), a_val, w_val.T

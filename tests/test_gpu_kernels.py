@@ -557,3 +557,31 @@ def test_bmm_16_bit_operands_with_transposes():
     np.testing.assert_array_equal(G.bmm16(at, b16[:2], shift=20, tok='floor', trans_a=True),
                                   oracle.matmul(at, b16[:2], shift=20, tok='floor', transpose_a=True, out_dtype='int16',
                                                 acc_bits=64))
+
+
+@pytest.mark.parametrize('fmt', ['bfloat16', 'fp8_e4m3'])
+@pytest.mark.parametrize('shape', [(300, 520, 200), (128, 64, 256), (1000, 2048, 1030), (5, 48, 16)])
+def test_float_dense_on_the_tensor_cores(fmt, shape):
+    """bfloat16 (kind::f16) and fp8 E4M3 (kind::f8f6f4) Dense with float32 accumulation: against a float64 evaluation
+    on the stored operands rounded to the storage type, within one step of that type (the order of the float32
+    additions is not part of the contract), and against the tiled SIMT kernel of the same entry point.  Shapes cover
+    a K tail shorter than a stage, a ragged last column tile, several row and column tiles, and a single narrow tile."""
+    import gpu_util as G
+
+    M, K, N = shape
+    rng = np.random.default_rng(M + K + N)
+    a = rng.normal(0, 1, (M, K))
+    w = rng.normal(0, 0.5 / np.sqrt(K), (K, N)) * (4.0 if fmt == 'fp8_e4m3' else 1.0)
+    bias = rng.normal(0, 0.5, N)
+    for relu, use_bias in ((True, True), (False, False)):
+        got, a_st, w_st = G.dense_float(a, w, bias if use_bias else None, relu=relu, fmt=fmt)
+        ref = a_st.astype(np.float64) @ w_st.astype(np.float64) + (bias.astype(np.float32).astype(np.float64) if use_bias else 0.0)
+        if relu:
+            ref = np.maximum(ref, 0.0)
+        want = oracle.round_float(ref, fmt)
+        np.testing.assert_array_equal(got, oracle.round_float(got, fmt))      # every result is a value of the type
+        step = 2.0 ** -3 if fmt == 'fp8_e4m3' else 2.0 ** -7
+        np.testing.assert_allclose(got, want, rtol=step * 1.01, atol=2.0 ** -8)
+        assert (got == want).mean() > 0.95
+        simt, _, _ = G.dense_float(a, w, bias if use_bias else None, relu=relu, fmt=fmt, simt=True)
+        np.testing.assert_allclose(got, simt, rtol=step * 1.01, atol=2.0 ** -8)
