@@ -30,6 +30,7 @@ int a4c_launch_dense_tc(const void* A, long long lda, const void* Wt, long long 
                         void* Y, long long ldy, long long M, int K, int N, int shift, int rounding, int relu,
                         int out_dtype, int a_unsigned, int cta_pair, int* status_word, cudaStream_t stream);
 void a4c_dense_tc_set_resident_w(int on);
+void a4c_dense_tc_set_panel_mib(int mib);   // weights per column panel of the streaming tile order; 0 = a single panel
 // 0 if the tensor-core path can take this problem, else an A4C_ERR_* code saying why not.
 int a4c_dense_tc_supported(const void* A, long long lda, const void* Wt, long long ldw, const void* Y,
                            long long ldy, long long M, int K, int N, int out_dtype);
@@ -65,8 +66,17 @@ int a4c_bmm_tc_supported(const void* A, long long lda, long long stride_a, const
                          long long stride_b, const void* C, long long ldc, long long stride_c, long long batch, int M,
                          int K, int N, int trans_a, int trans_b, int out_dtype);
 int a4c_launch_bmm_tc(const void* A, long long lda, long long stride_a, const void* B, long long ldb, long long stride_b,
-                      void* C, long long ldc, long long stride_c, long long batch, int M, int K, int N, int trans_b,
-                      int shift, int rounding, int out_dtype, int a_unsigned, int* status_word, cudaStream_t stream);
+                      void* C, long long ldc, long long stride_c, long long batch, int M, int K, int N, int trans_a,
+                      int trans_b, int shift, int rounding, int out_dtype, int a_unsigned, int* status_word,
+                      cudaStream_t stream);
+// Dense over a transposed input view on the same kernel: A_b stored [K, M] (an MN-major A operand), W^T [N, K] shared
+// by every batch entry, int32 bias or NULL, ReLU clamp.
+int a4c_dense_ta_tc_supported(const void* A, long long lda, long long stride_a, const void* Wt, long long ldw, const void* Y,
+                              long long ldy, long long stride_y, long long batch, int M, int K, int N, int out_dtype);
+int a4c_launch_dense_ta_tc(const void* A, long long lda, long long stride_a, const void* Wt, long long ldw,
+                           const int32_t* bias, void* Y, long long ldy, long long stride_y, long long batch, int M, int K,
+                           int N, int shift, int rounding, int relu, int out_dtype, int a_unsigned, int* status_word,
+                           cudaStream_t stream);
 
 // A chain of narrow Dense layers as one kernel (mlp_small.cu), and the choice a4c_mlp_i8 makes (mlp_chain.cu).
 int a4c_mlp_small_supported(int n_layers, const int* dims, int out_dtype);

@@ -12,7 +12,13 @@
 //     the TMA box is [128 k-rows x 64 bytes of n] with 64-byte swizzle, the shared-memory descriptor uses the
 //     64-byte-swizzle MN-major canonical layout (k-rows 64 B apart, 8-row groups 512 B apart) and the
 //     instruction descriptor marks B as MN-major; the N tile is 64 in that case;
-//   * the N tile is a template parameter (64 / 128 / 256).
+//   * the N tile is a template parameter (64 / 128 / 256);
+//   * A stored [K, M] (a folded Transpose on the left operand: TRANSPOSE_A, matmul.cpp:60-67; the transposed input view
+//     of a Dense: TRANSPOSE_INPUT, dense_bias_relu.cpp:99,135) is an MN-major A operand: the TMA box is
+//     [128 k-rows x 128 bytes of m] with 128-byte swizzle, the same shared-memory descriptor as a K-major tile
+//     (rows of 128 bytes, 8-row groups 1024 bytes apart) with the instruction descriptor marking A as MN-major, and
+//     one MMA advances 32 k-rows.  With a bias vector, a ReLU clamp and a B operand shared by all batch entries this
+//     is the Dense over a transposed input view (a4c_dense_ta).
 #include <cuda.h>
 
 #include <mutex>
@@ -51,6 +57,8 @@ struct Tail {
 };
 
 struct BmmArgs {
+    const int32_t* bias;          // per output column, or NULL (Dense over a transposed input view only)
+    int b_shared;                 // every batch entry multiplies by the same B (batch coordinate 0)
     uint8_t* C; long long ldc, stride_c;
     long long batch; int M, K, N;
     int m_tiles, n_tiles;
@@ -83,7 +91,7 @@ __device__ __forceinline__ int requant(int acc, const BmmArgs& g) {
     return min(max(v, g.lo), g.hi);
 }
 
-template <int BN, bool B_MN, int MODE>
+template <int BN, bool B_MN, bool A_MN, int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 bmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, BmmArgs g) {
     using C = Cfg<BN>;
@@ -129,9 +137,11 @@ bmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                     if (!ok) break;
                     uint8_t* sa = smem + (size_t)stage * C::STAGE_BYTES;
                     mbar_arrive_expect_tx(&tail->full[stage], C::STAGE_BYTES);
-                    tma_load_3d(sa, &tmap_a, &tail->full[stage], kb * BK, m0, b);
-                    if (B_MN) tma_load_3d(sa + C::A_BYTES, &tmap_b, &tail->full[stage], n0, kb * BK, b);
-                    else tma_load_3d(sa + C::A_BYTES, &tmap_b, &tail->full[stage], kb * BK, n0, b);
+                    const int bb = g.b_shared ? 0 : b;
+                    if (A_MN) tma_load_3d(sa, &tmap_a, &tail->full[stage], m0, kb * BK, b);
+                    else tma_load_3d(sa, &tmap_a, &tail->full[stage], kb * BK, m0, b);
+                    if (B_MN) tma_load_3d(sa + C::A_BYTES, &tmap_b, &tail->full[stage], n0, kb * BK, bb);
+                    else tma_load_3d(sa + C::A_BYTES, &tmap_b, &tail->full[stage], kb * BK, n0, bb);
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -156,9 +166,9 @@ bmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                     const uint64_t bdesc = B_MN ? make_smem_desc_mn64(sa + C::A_BYTES) : make_smem_desc(sa + C::A_BYTES);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
-                        // K step: A (and K-major B) advance 32 bytes inside the swizzle row; an MN-major B advances
-                        // 32 k-rows of 64 bytes
-                        const uint64_t a_k = adesc + (uint64_t)(k * (UMMA_K >> 4));
+                        // K step: a K-major operand advances 32 bytes inside the swizzle row; an MN-major B advances
+                        // 32 k-rows of 64 bytes, an MN-major A 32 k-rows of 128 bytes
+                        const uint64_t a_k = adesc + (uint64_t)(A_MN ? k * ((UMMA_K * 128) >> 4) : k * (UMMA_K >> 4));
                         const uint64_t b_k = bdesc + (uint64_t)(B_MN ? k * ((UMMA_K * 64) >> 4) : k * (UMMA_K >> 4));
                         umma_i8(d_tmem, a_k, b_k, g.idesc, (uint32_t)((kb | k) != 0));
                     }
@@ -197,7 +207,12 @@ bmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
                     for (int q = 0; q < 8; ++q) {
                         int o[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) o[e] = requant<MODE>((int)r[q * 4 + e], g);
+                        for (int e = 0; e < 4; ++e) {
+                            const int n = n0 + c * 32 + q * 4 + e;
+                            // acc32 wraps when the bias is added (it is the accumulator's initial value in the reference)
+                            const uint32_t bv = (g.bias != nullptr && n < g.N) ? (uint32_t)__ldg(g.bias + n) : 0u;
+                            o[e] = requant<MODE>((int)(r[q * 4 + e] + bv), g);
+                        }
                         w[q] = (uint32_t)(o[0] & 0xFF) | ((uint32_t)(o[1] & 0xFF) << 8) |
                                ((uint32_t)(o[2] & 0xFF) << 16) | ((uint32_t)o[3] << 24);
                     }
@@ -260,29 +275,29 @@ bool make_map3(CUtensorMap* map, const void* base, long long inner, long long ro
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, bool B_MN, int MODE>
+template <int BN, bool B_MN, bool A_MN, int MODE>
 cudaError_t launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const BmmArgs& g, int grid, cudaStream_t s) {
     constexpr size_t smem = 1024 + (size_t)STAGES * Cfg<BN>::STAGE_BYTES + sizeof(Tail);
     static tc::SmemOptIn opt_in;
-    const cudaError_t attr_err = opt_in.ensure(bmm_tc_kernel<BN, B_MN, MODE>, smem);
+    const cudaError_t attr_err = opt_in.ensure(bmm_tc_kernel<BN, B_MN, A_MN, MODE>, smem);
     if (attr_err != cudaSuccess) return attr_err;
-    bmm_tc_kernel<BN, B_MN, MODE><<<grid, NUM_THREADS, smem, s>>>(ma, mb, g);
+    bmm_tc_kernel<BN, B_MN, A_MN, MODE><<<grid, NUM_THREADS, smem, s>>>(ma, mb, g);
     return cudaGetLastError();
 }
 
-template <int BN, bool B_MN>
+template <int BN, bool B_MN, bool A_MN = false>
 cudaError_t launch_mode(int shift, int rounding, const CUtensorMap& ma, const CUtensorMap& mb, const BmmArgs& g, int grid,
                         cudaStream_t s) {
-    if (shift == 0) return launch_one<BN, B_MN, -1>(ma, mb, g, grid, s);
+    if (shift == 0) return launch_one<BN, B_MN, A_MN, -1>(ma, mb, g, grid, s);
     switch (rounding) {
-        case A4C_RND_FLOOR: return launch_one<BN, B_MN, A4C_RND_FLOOR>(ma, mb, g, grid, s);
-        case A4C_RND_CEIL: return launch_one<BN, B_MN, A4C_RND_CEIL>(ma, mb, g, grid, s);
-        case A4C_RND_POSITIVE_INF: return launch_one<BN, B_MN, A4C_RND_POSITIVE_INF>(ma, mb, g, grid, s);
-        case A4C_RND_NEGATIVE_INF: return launch_one<BN, B_MN, A4C_RND_NEGATIVE_INF>(ma, mb, g, grid, s);
-        case A4C_RND_SYMMETRIC_INF: return launch_one<BN, B_MN, A4C_RND_SYMMETRIC_INF>(ma, mb, g, grid, s);
-        case A4C_RND_SYMMETRIC_ZERO: return launch_one<BN, B_MN, A4C_RND_SYMMETRIC_ZERO>(ma, mb, g, grid, s);
-        case A4C_RND_CONV_EVEN: return launch_one<BN, B_MN, A4C_RND_CONV_EVEN>(ma, mb, g, grid, s);
-        default: return launch_one<BN, B_MN, A4C_RND_CONV_ODD>(ma, mb, g, grid, s);
+        case A4C_RND_FLOOR: return launch_one<BN, B_MN, A_MN, A4C_RND_FLOOR>(ma, mb, g, grid, s);
+        case A4C_RND_CEIL: return launch_one<BN, B_MN, A_MN, A4C_RND_CEIL>(ma, mb, g, grid, s);
+        case A4C_RND_POSITIVE_INF: return launch_one<BN, B_MN, A_MN, A4C_RND_POSITIVE_INF>(ma, mb, g, grid, s);
+        case A4C_RND_NEGATIVE_INF: return launch_one<BN, B_MN, A_MN, A4C_RND_NEGATIVE_INF>(ma, mb, g, grid, s);
+        case A4C_RND_SYMMETRIC_INF: return launch_one<BN, B_MN, A_MN, A4C_RND_SYMMETRIC_INF>(ma, mb, g, grid, s);
+        case A4C_RND_SYMMETRIC_ZERO: return launch_one<BN, B_MN, A_MN, A4C_RND_SYMMETRIC_ZERO>(ma, mb, g, grid, s);
+        case A4C_RND_CONV_EVEN: return launch_one<BN, B_MN, A_MN, A4C_RND_CONV_EVEN>(ma, mb, g, grid, s);
+        default: return launch_one<BN, B_MN, A_MN, A4C_RND_CONV_ODD>(ma, mb, g, grid, s);
     }
 }
 
@@ -291,7 +306,7 @@ cudaError_t launch_mode(int shift, int rounding, const CUtensorMap& ma, const CU
 int a4c_bmm_tc_supported(const void* A, long long lda, long long stride_a, const void* B, long long ldb,
                          long long stride_b, const void* C, long long ldc, long long stride_c, long long batch, int M,
                          int K, int N, int trans_a, int trans_b, int out_dtype) {
-    if (trans_a) return A4C_ERR_UNSUPPORTED;
+    if (trans_a && !trans_b) return A4C_ERR_UNSUPPORTED;   // both operands MN-major: left to the any-stride kernel
     if (out_dtype != A4C_I8 && out_dtype != A4C_U8) return A4C_ERR_UNSUPPORTED;
     if (N % 16 != 0 || K < 16) return A4C_ERR_UNSUPPORTED;
     if (lda % 16 || ldb % 16 || ldc % 16) return A4C_ERR_ALIGNMENT;
@@ -301,28 +316,41 @@ int a4c_bmm_tc_supported(const void* A, long long lda, long long stride_a, const
     return A4C_OK;
 }
 
-int a4c_launch_bmm_tc(const void* A, long long lda, long long stride_a, const void* B, long long ldb, long long stride_b,
-                      void* C, long long ldc, long long stride_c, long long batch, int M, int K, int N, int trans_b,
-                      int shift, int rounding, int out_dtype, int a_unsigned, int* status_word, cudaStream_t stream) {
+namespace {
+
+// trans_a: A_b stored [K, M] (MN-major operand).  bias / relu / b_shared: the Dense over a transposed input view.
+int launch_any(const void* A, long long lda, long long stride_a, const void* B, long long ldb, long long stride_b,
+               const int32_t* bias, int relu, int b_shared, void* C, long long ldc, long long stride_c, long long batch, int M,
+               int K, int N, int trans_a, int trans_b, int shift, int rounding, int out_dtype, int a_unsigned, int* status_word,
+               cudaStream_t stream) {
     if (batch == 0) return A4C_OK;
     const bool b_mn = !trans_b;
+    const bool a_mn = trans_a != 0;
+    if (a_mn && b_mn) return A4C_ERR_UNSUPPORTED;
     const int BN = b_mn ? 64 : (N <= 64 ? 64 : (N <= 128 ? 128 : 256));
     CUtensorMap ma, mb;
-    if (!make_map3(&ma, A, K, M, batch, lda, stride_a, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B)) return A4C_ERR_CUDA;
-    if (b_mn) {
-        if (!make_map3(&mb, B, N, K, batch, ldb, stride_b, 64, BK, CU_TENSOR_MAP_SWIZZLE_64B)) return A4C_ERR_CUDA;
+    if (a_mn) {
+        if (!make_map3(&ma, A, M, K, batch, lda, stride_a, 128, BK, CU_TENSOR_MAP_SWIZZLE_128B)) return A4C_ERR_CUDA;
     } else {
-        if (!make_map3(&mb, B, K, N, batch, ldb, stride_b, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B)) return A4C_ERR_CUDA;
+        if (!make_map3(&ma, A, K, M, batch, lda, stride_a, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B)) return A4C_ERR_CUDA;
+    }
+    const long long b_batch = b_shared ? 1 : batch;
+    if (b_mn) {
+        if (!make_map3(&mb, B, N, K, b_batch, ldb, stride_b, 64, BK, CU_TENSOR_MAP_SWIZZLE_64B)) return A4C_ERR_CUDA;
+    } else {
+        if (!make_map3(&mb, B, K, N, b_batch, ldb, stride_b, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B)) return A4C_ERR_CUDA;
     }
     BmmArgs g;
+    g.bias = bias; g.b_shared = b_shared ? 1 : 0;
     g.C = (uint8_t*)C; g.ldc = ldc; g.stride_c = stride_c; g.batch = batch; g.M = M; g.K = K; g.N = N;
     g.m_tiles = (M + BM - 1) / BM;
     g.n_tiles = (N + BN - 1) / BN;
     g.shift = shift;
     dtype_range(out_dtype, g.lo, g.hi);
+    if (relu && g.lo < 0) g.lo = 0;
     const RoundParams rp = make_round_params(shift, rounding);
     g.mask = rp.mask; g.c0 = rp.c0;
-    g.idesc = make_idesc(BM, BN, a_unsigned != 0) | (b_mn ? (1u << 16) : 0u);
+    g.idesc = make_idesc(BM, BN, a_unsigned != 0) | (b_mn ? (1u << 16) : 0u) | (a_mn ? (1u << 15) : 0u);
     g.status = status_word;
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
@@ -330,9 +358,38 @@ int a4c_launch_bmm_tc(const void* A, long long lda, long long stride_a, const vo
     const long long tiles = batch * g.m_tiles * g.n_tiles;
     const int grid = (int)(tiles < sms ? tiles : sms);
     cudaError_t err;
-    if (b_mn) err = launch_mode<64, true>(shift, rounding, ma, mb, g, grid, stream);
+    if (a_mn) {
+        if (BN == 64) err = launch_mode<64, false, true>(shift, rounding, ma, mb, g, grid, stream);
+        else if (BN == 128) err = launch_mode<128, false, true>(shift, rounding, ma, mb, g, grid, stream);
+        else err = launch_mode<256, false, true>(shift, rounding, ma, mb, g, grid, stream);
+    }
+    else if (b_mn) err = launch_mode<64, true>(shift, rounding, ma, mb, g, grid, stream);
     else if (BN == 64) err = launch_mode<64, false>(shift, rounding, ma, mb, g, grid, stream);
     else if (BN == 128) err = launch_mode<128, false>(shift, rounding, ma, mb, g, grid, stream);
     else err = launch_mode<256, false>(shift, rounding, ma, mb, g, grid, stream);
     return err == cudaSuccess ? A4C_OK : A4C_ERR_CUDA;
+}
+
+}  // namespace
+
+int a4c_launch_bmm_tc(const void* A, long long lda, long long stride_a, const void* B, long long ldb, long long stride_b,
+                      void* C, long long ldc, long long stride_c, long long batch, int M, int K, int N, int trans_a,
+                      int trans_b, int shift, int rounding, int out_dtype, int a_unsigned, int* status_word,
+                      cudaStream_t stream) {
+    return launch_any(A, lda, stride_a, B, ldb, stride_b, nullptr, 0, 0, C, ldc, stride_c, batch, M, K, N, trans_a, trans_b,
+                      shift, rounding, out_dtype, a_unsigned, status_word, stream);
+}
+
+int a4c_dense_ta_tc_supported(const void* A, long long lda, long long stride_a, const void* Wt, long long ldw, const void* Y,
+                              long long ldy, long long stride_y, long long batch, int M, int K, int N, int out_dtype) {
+    // stored A_b [K, M]: the m axis is the contiguous one
+    return a4c_bmm_tc_supported(A, lda, stride_a, Wt, ldw, 0, Y, ldy, stride_y, batch, M, K, N, 1, 1, out_dtype);
+}
+
+int a4c_launch_dense_ta_tc(const void* A, long long lda, long long stride_a, const void* Wt, long long ldw,
+                           const int32_t* bias, void* Y, long long ldy, long long stride_y, long long batch, int M, int K,
+                           int N, int shift, int rounding, int relu, int out_dtype, int a_unsigned, int* status_word,
+                           cudaStream_t stream) {
+    return launch_any(A, lda, stride_a, Wt, ldw, 0, bias, relu, 1, Y, ldy, stride_y, batch, M, K, N, 1, 1, shift, rounding,
+                      out_dtype, a_unsigned, status_word, stream);
 }

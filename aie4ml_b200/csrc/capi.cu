@@ -130,8 +130,8 @@ int a4c_bmm_i8(const void* A, int64_t lda, int64_t stride_a, const int8_t* B, in
                                                 trans_a, trans_b, out_dtype) == A4C_OK) {
         int* word = status_word();
         if (word == nullptr) return A4C_ERR_CUDA;
-        const int trc = a4c_launch_bmm_tc(A, lda, stride_a, B, ldb, stride_b, C, ldc, stride_c, batch, M, K, N, trans_b,
-                                          shift, rounding, out_dtype, a_unsigned, word, (cudaStream_t)stream);
+        const int trc = a4c_launch_bmm_tc(A, lda, stride_a, B, ldb, stride_b, C, ldc, stride_c, batch, M, K, N, trans_a,
+                                          trans_b, shift, rounding, out_dtype, a_unsigned, word, (cudaStream_t)stream);
         if (trc != A4C_OK) { if (trc == A4C_ERR_CUDA) note(cudaGetLastError()); return trc; }
         return finish();
     }
@@ -172,6 +172,16 @@ int a4c_dense_ta(const void* A, int a_dtype, int64_t lda, int64_t stride_a, cons
         return A4C_ERR_INVALID_ARG;
     if (shift > (w16 ? 62 : 31)) return A4C_ERR_INVALID_ARG;
     int rc;
+    // 8-bit operands whose pitches and pointers meet the TMA rules: the tensor-core kernel with an MN-major A operand
+    if (!a16 && !w16 && g_bmm_path == 0 &&
+        a4c_dense_ta_tc_supported(A, lda, stride_a, Wt, ldw, Y, ldy, stride_y, batch, M, K, N, out_dtype) == A4C_OK) {
+        int* word = status_word();
+        if (word == nullptr) return A4C_ERR_CUDA;
+        rc = a4c_launch_dense_ta_tc(A, lda, stride_a, Wt, ldw, bias, Y, ldy, stride_y, batch, M, K, N, shift, rounding, relu,
+                                    out_dtype, a_dtype == A4C_U8, word, (cudaStream_t)stream);
+        if (rc != A4C_OK) { if (rc == A4C_ERR_CUDA) note(cudaGetLastError()); return rc; }
+        return finish();
+    }
     // stored [K, M]: the row (m) stride is 1 element, the k stride is the pitch
     if (a16)
         rc = a4c_launch_gemm_wide(A, 2, 1, lda, stride_a, Wt, w16 ? 2 : 1, 1, ldw, 0, bias, Y, ldy, stride_y, batch, M, K, N,
@@ -295,6 +305,10 @@ int a4c_set_option(int option, int value) {
     }
     if (option == A4C_OPT_BMM_PATH && (value == 0 || value == 1)) {
         g_bmm_path = value;
+        return A4C_OK;
+    }
+    if (option == A4C_OPT_DENSE_PANEL_MIB && value >= 0 && value <= 1024) {
+        a4c_dense_tc_set_panel_mib(value);
         return A4C_OK;
     }
     if (option == A4C_OPT_FLOAT_DENSE_PATH && (value == 0 || value == 1)) {

@@ -16,7 +16,10 @@
 //              four int8 per word into the warp's swizzled 32 x 64-byte staging patch, TMA store; the accumulator
 //              goes back to the issuer once its last 64 columns are in registers
 // Tile order: normally CTA c takes global tiles c, c + grid, ... (column tile fastest) and every stage carries an
-// A tile and a W tile.  For K <= 512 with enough row tiles, a CTA instead keeps the whole K extent of ONE weight
+// A tile and a W tile.  When the weights are larger than what the L2 keeps (a B200 L2 holds about 60 MB of data that
+// every SM reads: 64 MiB of weights at K = N = 8192 were fetched from HBM some 80 times per launch, 6.4 GB of reads for
+// 1.1 GB of operands), the column tiles are walked in PANELS of at most 32 MiB of weights: all row tiles of one
+// panel, then the next panel.  A panel stays in the L2 while the rows stream past it; A is then read once per panel.  For K <= 512 with enough row tiles, a CTA instead keeps the whole K extent of ONE weight
 // tile resident in shared memory (loaded once) and the ring holds A tiles only, up to eight of them, so several
 // row tiles are in flight from HBM while one is multiplied; CTAs c .. c + n_tiles - 1 walk the same row tiles, so
 // A reaches HBM once and L2 serves the other column tiles (4-10 % faster than the streaming order at K <= 512).
@@ -79,6 +82,7 @@ constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_
 using namespace tc;
 
 int g_dense_resident_w = 1;   // 0 switches the resident-W tile order off (A4C_OPT_DENSE_RESIDENT_W)
+long long g_dense_panel_bytes = 32ll << 20;   // weights per panel of the streaming order; 0 = one panel (A4C_OPT_DENSE_PANEL_MIB)
 
 struct TcArgs {
     const int32_t* bias;
@@ -93,6 +97,7 @@ struct TcArgs {
     // CTA c then owns output-column tile c % num_n_tiles and row tiles c / num_n_tiles + i * (grid / num_n_tiles).
     int w_resident, a_stages;
     int num_m_tiles, num_n_tiles;
+    int panel;           // column tiles per panel of the streaming tile order (>= num_n_tiles: a single panel)
     int shift, lo, hi;
     uint32_t mask, c0;   // rounding constants (see round_shift_i32_t)
     int half, xhi, xlo;  // MODE_HALF_UP_CLAMP / _FLOAT: 2^(s-1), hi * 2^s, lo * 2^s + 2^(s-1)
@@ -116,6 +121,19 @@ __device__ __forceinline__ int requant(int acc, int bias, const TcArgs& g) {
     if (MODE == A4C_RND_FLOOR) v = v >> g.shift;
     else if (MODE >= 0) v = round_shift_i32_t<MODE>(v, g.shift, g.mask, g.c0);
     return min(max(v, g.lo), g.hi);
+}
+
+// Streaming tile order: global tile index -> (row tile, column tile).  Panels of g.panel column tiles (the last one
+// may be narrower); inside a panel the column tile runs fastest.
+__device__ __forceinline__ void tile_coords(int tile, const TcArgs& g, int& mt, int& nt) {
+    const int nnt = g.num_n_tiles;
+    if (g.panel >= nnt) { mt = tile / nnt; nt = tile - mt * nnt; return; }
+    const int per_panel = g.num_m_tiles * g.panel;
+    const int full = nnt / g.panel;
+    int pz = tile / per_panel, rem = tile - pz * per_panel, width = g.panel;
+    if (pz >= full) { pz = full; rem = tile - full * per_panel; width = nnt - full * g.panel; }
+    mt = rem / width;
+    nt = pz * g.panel + (rem - mt * width);
 }
 
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, const void* src) {
@@ -234,8 +252,9 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             uint32_t phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-                const int m0 = (tile / g.num_n_tiles) * BM;
-                const int n0 = (tile % g.num_n_tiles) * BN;
+                int mt, nt;
+                tile_coords(tile, g, mt, nt);
+                const int m0 = mt * BM, n0 = nt * BN;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(&tail->empty[stage], phase ^ 1u, abort_flag, g.status, 101);
                     if (!ok) break;
@@ -311,19 +330,19 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 tail->bias[i] = (g.bias != nullptr && i < g.N) ? __ldg(g.bias + i) : 0;
             asm volatile("bar.sync 1, 256;" ::: "memory");
         }
-        // This group's tiles are the CTA's local tiles grp, grp + 2, ...; (mt, nt) follow without division.
-        // Streaming order: local tile i is global tile blockIdx.x + i * gridDim.x (column tile fastest).
+        // This group's tiles are the CTA's local tiles grp, grp + 2, ...
+        // Streaming order: local tile i is global tile blockIdx.x + i * gridDim.x (see tile_coords).
         // Resident-W order: column tile fixed, row tile blockIdx.x / nnt + i * (gridDim.x / nnt).
         const int nnt = g.num_n_tiles;
         const int step = g.w_resident ? 2 * ((int)gridDim.x / nnt) : 2 * (int)gridDim.x;
-        const int step_m = g.w_resident ? step : step / nnt, step_n = g.w_resident ? 0 : step % nnt;
-        const int first = g.w_resident ? (int)blockIdx.x / nnt + grp * ((int)gridDim.x / nnt) : (int)blockIdx.x + grp * (int)gridDim.x;
-        int mt = g.w_resident ? first : first / nnt, nt = g.w_resident ? (int)blockIdx.x % nnt : first % nnt;
+        int cursor = g.w_resident ? (int)blockIdx.x / nnt + grp * ((int)gridDim.x / nnt) : (int)blockIdx.x + grp * (int)gridDim.x;
+        const int limit = g.w_resident ? g.num_m_tiles : num_tiles;
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(grp * BN);
-        while (mt < g.num_m_tiles) {
+        for (; cursor < limit; cursor += step) {
+            int mt, nt;
+            if (g.w_resident) { mt = cursor; nt = (int)blockIdx.x % nnt; }
+            else tile_coords(cursor, g, mt, nt);
             const int m0 = mt * BM, n0 = nt * BN;
-            mt += step_m; nt += step_n;
-            if (nt >= nnt) { nt -= nnt; ++mt; }
             const int32_t* tile_bias = tail->bias + (bias_resident ? n0 : grp * BN);
             if (HAS_BIAS && !bias_resident) {
                 // stage this tile's bias slice (zero where there is none); the group's previous tile is done with it
@@ -445,6 +464,7 @@ cudaError_t launch_mode(const CUtensorMap& ma, const CUtensorMap& mb, const CUte
 }  // namespace
 
 void a4c_dense_tc_set_resident_w(int on) { g_dense_resident_w = on ? 1 : 0; }
+void a4c_dense_tc_set_panel_mib(int mib) { g_dense_panel_bytes = (long long)mib << 20; }
 
 int a4c_dense_tc_supported(const void* A, long long lda, const void* Wt, long long ldw, const void* Y,
                            long long ldy, long long M, int K, int N, int out_dtype) {
@@ -502,6 +522,13 @@ int a4c_launch_dense_tc(const void* A, long long lda, const void* Wt, long long 
     const int num_kb = (K + BK - 1) / BK;
     const int per = sms / g.num_n_tiles;
     g.w_resident = 0; g.a_stages = STAGES;
+    // panels of at most 32 MiB of weights (whole column tiles); one panel when the weights are smaller than that
+    {
+        const long long tile_bytes = (long long)BN * (((long long)K + BK - 1) / BK * BK);
+        long long per = g_dense_panel_bytes / tile_bytes;
+        if (per < 1) per = 1;
+        g.panel = g_dense_panel_bytes <= 0 || per >= g.num_n_tiles ? g.num_n_tiles : (int)per;
+    }
     if (g_dense_resident_w && num_kb <= 4 && g.num_n_tiles <= 16 && per >= 1 && g.num_m_tiles >= 4 * per) {
         g.w_resident = 1;
         const int slots = (STAGES * STAGE_BYTES - num_kb * B_BYTES) / A_BYTES;

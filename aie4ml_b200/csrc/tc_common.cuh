@@ -50,6 +50,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
+// The same probe with a suspend-time hint: the thread may sleep in the barrier unit for up to `ns` nanoseconds and is
+// woken when the phase completes.  Without the hint a probe returns after a short, implementation-chosen time, and a
+// warp that waits long re-issues probe, branch and convergence instructions all the while: in the fused attention
+// kernel those made up a quarter of all issued instructions, taken from the warps that had work.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
+
 // Bounded wait.  Returns false when the CTA is aborting (this wait or another one gave up).  The first probe is
 // inline: an out-of-line call costs several hundred cycles in these kernels even when the barrier has long
 // completed (measured with clock stamps: 21 cycles for the probe, ~470 for the call), and the MMA issuer pays that
@@ -73,9 +87,10 @@ static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parit
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
     // a probe that finds the phase incomplete suspends the thread for a while by itself: a few of them cover the
     // ordinary waits without leaving the caller
+    if (mbar_try_wait(bar, parity)) return true;
 #pragma unroll 1
     for (int i = 0; i < 8; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
     return mbar_wait_slow(bar, parity, abort_flag, status, code);
 }
 

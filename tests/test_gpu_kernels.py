@@ -585,3 +585,72 @@ def test_float_dense_on_the_tensor_cores(fmt, shape):
         assert (got == want).mean() > 0.95
         simt, _, _ = G.dense_float(a, w, bias if use_bias else None, relu=relu, fmt=fmt, simt=True)
         np.testing.assert_allclose(got, simt, rtol=step * 1.01, atol=2.0 ** -8)
+
+
+@pytest.mark.parametrize('shape', [(3, 200, 160, 48), (2, 64, 128, 256), (1, 1024, 400, 80), (5, 48, 16, 16)])
+@pytest.mark.parametrize('unsigned', [False, True])
+def test_dense_over_a_transposed_input_on_the_tensor_cores(shape, unsigned):
+    """Stored [K, M] inputs whose pitches meet the TMA rules run on the tcgen05 kernel with an MN-major A operand
+    (128-byte-swizzled [k, m] tiles): K tails shorter than a stage, M tails shorter than a tile, several column tiles,
+    bias that wraps the accumulator, ReLU, both 8-bit input types; and the dp4a kernel on the same arguments."""
+    import gpu_util as G
+    from aie4ml_b200 import lib as a4c
+
+    batch, K, M, N = shape
+    rng = np.random.default_rng(sum(shape) + unsigned)
+    a_t = (rng.integers(0, 256, (batch, K, M)).astype(np.uint8) if unsigned
+           else rng.integers(-128, 128, (batch, K, M)).astype(np.int8))
+    w = rng.integers(-128, 128, (K, N)).astype(np.int8)
+    bias = rng.integers(-(1 << 31), 1 << 31, N).astype(np.int32)
+    a = np.swapaxes(a_t, 1, 2)
+    L = a4c.load()
+    for tok, relu, od, b, shift in (('positive_inf', True, 'int8', bias, 9), ('conv_even', False, 'uint8', None, 8),
+                                    ('floor', False, 'int8', bias, 0)):
+        want = oracle.dense(a, w, b, shift=shift, tok=tok, relu=relu, out_dtype=od)
+        got = G.dense_ta(a_t, w, b, shift=shift, tok=tok, relu=relu, out_dtype=od)
+        np.testing.assert_array_equal(got, want)
+        assert L.a4c_set_option(a4c.OPT_BMM_PATH, 1) == 0          # the any-stride kernel on the same call
+        try:
+            np.testing.assert_array_equal(G.dense_ta(a_t, w, b, shift=shift, tok=tok, relu=relu, out_dtype=od), want)
+        finally:
+            assert L.a4c_set_option(a4c.OPT_BMM_PATH, 0) == 0
+    a4c.device_status(G.stream())
+
+
+def test_bmm_with_a_transposed_left_operand_on_the_tensor_cores():
+    """TRANSPOSE_A with a K-major right operand (both stored transposed): A_b [K, M] is an MN-major operand."""
+    import gpu_util as G
+    from aie4ml_b200 import lib as a4c
+
+    rng = np.random.default_rng(321)
+    for batch, M, K, N in ((7, 128, 64, 128), (3, 80, 200, 48), (2, 272, 32, 16)):
+        at = rng.integers(-128, 128, (batch, K, M)).astype(np.int8)
+        bt = rng.integers(-128, 128, (batch, N, K)).astype(np.int8)
+        want = oracle.matmul(at, bt, shift=7, tok='positive_inf', transpose_a=True, transpose_b=True)
+        np.testing.assert_array_equal(G.bmm(at, bt, shift=7, tok='positive_inf', trans_a=True, trans_b=True), want)
+        ut = rng.integers(0, 256, (batch, K, M)).astype(np.uint8)
+        np.testing.assert_array_equal(G.bmm(ut, bt, shift=9, tok='conv_even', trans_a=True, trans_b=True, out_dtype='uint8'),
+                                      oracle.matmul(ut, bt, shift=9, tok='conv_even', transpose_a=True, transpose_b=True,
+                                                    out_dtype='uint8'))
+    a4c.device_status(G.stream())
+
+
+@pytest.mark.parametrize('panel_mib', [1, 2, 0])
+def test_dense_tcgen05_column_panels(panel_mib):
+    """The streaming tile order walks the column tiles in panels when the weights exceed the panel size: forced here
+    with 1 and 2 MiB panels on a 2.25 MiB weight matrix (nine column tiles: panels of 4 + 4 + 1 and 8 + 1), and the
+    single-panel order (0), all against the oracle, with more tiles than SMs and ragged last row tile."""
+    import gpu_util as G
+    from aie4ml_b200 import lib as a4c
+
+    L = a4c.load()
+    assert L.a4c_set_option(a4c.OPT_DENSE_PANEL_MIB, panel_mib) == 0
+    try:
+        a, w, bias = _rand_dense(500 + panel_mib, 3000, 1024, 2304)
+        got = G.dense(a, w, bias, shift=10, tok='positive_inf', relu=True, algo=TC)
+        np.testing.assert_array_equal(got, oracle.dense(a, w, bias, shift=10, tok='positive_inf', relu=True))
+        a, w, _ = _rand_dense(600 + panel_mib, 700, 2048, 1300)
+        got = G.dense(a, w, None, shift=11, tok='conv_even', relu=False, algo=TC)
+        np.testing.assert_array_equal(got, oracle.dense(a, w, None, shift=11, tok='conv_even', relu=False))
+    finally:
+        assert L.a4c_set_option(a4c.OPT_DENSE_PANEL_MIB, 32) == 0
