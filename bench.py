@@ -588,6 +588,8 @@ def main():
     ap.add_argument('--no-graph', action='store_true')
     ap.add_argument('--no-numa', action='store_true', help='do not place the pinned host buffers next to the GPU')
     ap.add_argument('--algo', type=int, default=0, help='dense kernel: 0 auto, 1 simt, 2 tcgen05')
+    ap.add_argument('--dense-panel-mib', type=int, default=None,
+                    help='tcgen05 Dense: MiB of weights per column panel of the tile order (library default 32; 0 = one panel)')
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
 
@@ -615,6 +617,10 @@ def main():
     peaks = measured_peaks()
     traffic = recorded_traffic()
     c_lib, c_desc = checker.load_c(native=True)
+    if args.dense_panel_mib is not None:
+        from aie4ml_b200 import lib as a4c
+
+        a4c.check(a4c.load().a4c_set_option(a4c.OPT_DENSE_PANEL_MIB, args.dense_panel_mib), 'a4c_set_option')
 
     wl = build_workload(args.workload, args)
     model = from_graph(wl['builder'])
