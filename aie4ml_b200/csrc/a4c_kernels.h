@@ -121,3 +121,11 @@ int a4c_dense_tcf_supported(const void* A, long long lda, const void* Wt, long l
 int a4c_launch_dense_tcf(const void* A, long long lda, const void* Wt, long long ldw, const float* bias, void* Y,
                          long long ldy, long long M, int K, int N, int relu, int kind, int* status_word,
                          cudaStream_t stream);
+
+// tcgen05 int16 x int8 Dense (dense_tc16.cu): the activation's two byte digits against the int8 weights, combined in
+// wrapping 32-bit arithmetic.  Uses a fixed per-device workspace (64 MiB, allocated on first use).  Pitches in elements.
+int a4c_dense_tc16_supported(const void* A, long long lda, const void* Wt, long long ldw, const void* Y, long long ldy,
+                             long long M, int K, int N, int out_dtype);
+int a4c_launch_dense_tc16(const int16_t* A, long long lda, const int8_t* Wt, long long ldw, const int32_t* bias, void* Y,
+                          long long ldy, long long M, int K, int N, int shift, int rounding, int relu, int out_dtype,
+                          int* status_word, cudaStream_t stream);

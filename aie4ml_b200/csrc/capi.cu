@@ -14,6 +14,7 @@ int* g_status[kMaxDevices] = {nullptr};
 thread_local const char* t_last_cuda_error = "no error";
 int g_rowop_path = 0;  // 0 auto (fast kernels when they apply), 1 generic kernels only
 int g_bmm_path = 0;    // 0 auto (tcgen05 when its rules hold), 1 dp4a kernel only
+int g_wide_path = 0;   // 0 auto (tcgen05 digit kernel for int16 x int8 when its rules hold), 1 SIMT kernel only
 int g_float_path = 0;  // 0 auto (tcgen05 Dense for bfloat16 / fp8 when its rules hold), 1 tiled SIMT kernel only
 
 bool note(cudaError_t e) {
@@ -154,6 +155,16 @@ int a4c_dense_i16(const int16_t* A, int64_t lda, const void* Wt, int w_dtype, in
     if ((w_dtype != A4C_I8 && w_dtype != A4C_I16) || !valid_round(rounding) || !valid_dtype(out_dtype))
         return A4C_ERR_INVALID_ARG;
     const int wide = w_dtype == A4C_I16;
+    if (shift < 0 || shift > (wide ? 62 : 31)) return A4C_ERR_INVALID_ARG;
+    // int16 x int8 whose pitches meet the TMA rules: the tensor cores, one digit of the activation at a time
+    if (!wide && g_wide_path == 0 && a4c_dense_tc16_supported(A, lda, Wt, ldw, Y, ldy, M, K, N, out_dtype) == A4C_OK) {
+        int* word = status_word();
+        if (word == nullptr) return A4C_ERR_CUDA;
+        const int trc = a4c_launch_dense_tc16(A, lda, (const int8_t*)Wt, ldw, bias, Y, ldy, M, K, N, shift, rounding, relu,
+                                              out_dtype, word, (cudaStream_t)stream);
+        if (trc != A4C_OK) { if (trc == A4C_ERR_CUDA) note(cudaGetLastError()); return trc; }
+        return finish();
+    }
     // W^T [N, ldw]: k stride 1, n stride ldw.  int16 x int8 accumulates in 32 bits, int16 x int16 in 64.
     const int rc = a4c_launch_gemm_wide(A, 2, lda, 1, 0, Wt, wide ? 2 : 1, 1, ldw, 0, bias, Y, ldy, 0, 1, M, K, N, shift,
                                         rounding, relu, out_dtype, wide ? 64 : 32, (cudaStream_t)stream);
@@ -309,6 +320,10 @@ int a4c_set_option(int option, int value) {
     }
     if (option == A4C_OPT_DENSE_PANEL_MIB && value >= 0 && value <= 1024) {
         a4c_dense_tc_set_panel_mib(value);
+        return A4C_OK;
+    }
+    if (option == A4C_OPT_WIDE_DENSE_PATH && (value == 0 || value == 1)) {
+        g_wide_path = value;
         return A4C_OK;
     }
     if (option == A4C_OPT_FLOAT_DENSE_PATH && (value == 0 || value == 1)) {

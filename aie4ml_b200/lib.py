@@ -32,6 +32,7 @@ OPT_MLP_PATH = 4
 OPT_DENSE_RESIDENT_W = 5
 OPT_FLOAT_DENSE_PATH = 7
 OPT_DENSE_PANEL_MIB = 8
+OPT_WIDE_DENSE_PATH = 9
 
 # name -> (restype, argtypes); mirrors the header declaration by declaration
 SIGNATURES = {

@@ -55,6 +55,7 @@ extern "C" {
 #define A4C_OPT_BMM_PATH 1   /* 0 = auto (tcgen05 batched MatMul when its alignment rules hold), 1 = dp4a kernel only */
 #define A4C_OPT_DENSE_RESIDENT_W 5 /* tcgen05 Dense, K <= 512: 1 (default) = a CTA keeps its weight tile in shared memory and streams A only, 0 = off */
 #define A4C_OPT_DENSE_PANEL_MIB 8 /* tcgen05 Dense, streaming tile order: MiB of weights per column panel (default 32; 0 = one panel, column tile fastest over the whole width) */
+#define A4C_OPT_WIDE_DENSE_PATH 9 /* a4c_dense_i16 with int8 weights: 0 = auto (tcgen05, the activation's two byte digits in turn), 1 = SIMT kernel only */
 #define A4C_OPT_FLOAT_DENSE_PATH 7 /* a4c_dense_f, bfloat16 / fp8: 0 = auto (tcgen05 kernel when its alignment rules hold), 1 = tiled SIMT kernel only */
 #define A4C_OPT_MLP_PATH 4   /* a4c_mlp_i8: 0 = auto, 1 = one Dense launch per layer, 2 = the single-kernel narrow chain only */
 /* Tuning of the bandwidth-oriented row kernels (results do not depend on either): */
@@ -159,6 +160,12 @@ A4C_API int a4c_softmax_i8(const int8_t* x, int64_t ldx, const void* addend, int
  * wraps) or int16 (w_dtype 2: 64-bit accumulator).  Otherwise the contracts of a4c_dense_i8 / a4c_bmm_i8
  * (dense_bias_relu.cpp:67-166, matmul.cpp:32-118): bias int32, SRS, saturation, ReLU after it; shift <= 31
  * (acc32) or <= 62 (acc64).  Pitches and strides in ELEMENTS of the respective tensor.
+ * a4c_dense_i16 with int8 weights runs on the tensor cores when A and W^T start on 16 bytes with 16-byte row pitches
+ * and K >= 16: the activations are split into a signed high-byte plane and an unsigned low-byte plane (in a fixed
+ * 64 MiB workspace the library allocates per device on first use; rows are processed in chunks that fit it), each
+ * plane meets the weights in tcgen05.mma kind::i8, and (high << 8) + low + bias is formed in wrapping 32-bit
+ * arithmetic, which is bit for bit the reference's wrapping accumulation.  Everything else (int16 weights, other
+ * pitches, a4c_bmm_i16) runs on a tiled SIMT kernel.
  */
 A4C_API int a4c_dense_i16(const int16_t* A, int64_t lda, const void* Wt, int w_dtype, int64_t ldw, const int32_t* bias,
                   void* Y, int64_t ldy, int64_t M, int K, int N, int shift, int rounding, int relu, int out_dtype,
@@ -175,7 +182,10 @@ A4C_API int a4c_bmm_i16(const int16_t* A, int64_t lda, int64_t stride_a, const v
  *   W^T [N, K] w_dtype (int8, or int16 with an int16 input), pitch ldw; bias int32 or NULL
  *   Y_b: [M, N] out_dtype, pitch ldy, batch stride stride_y
  * Arithmetic, accumulator width and SRS exactly as a4c_dense_i8 / a4c_dense_i16.  Pitches and strides in
- * ELEMENTS.  Runs on the any-stride dp4a / wide kernels (the tensor-core kernels need a K-contiguous input).
+ * ELEMENTS.  8-bit inputs with int8 weights run on the tensor cores when lda, ldw, ldy, the batch strides and N are
+ * multiples of 16, the pointers start on 16 bytes and the output is int8 / uint8: the stored [K, M] tile is an
+ * MN-major A operand of tcgen05.mma (128-byte-swizzled rows of m).  Other cases run on the any-stride dp4a / wide
+ * kernels.
  */
 A4C_API int a4c_dense_ta(const void* A, int a_dtype, int64_t lda, int64_t stride_a, const void* Wt, int w_dtype,
                  int64_t ldw, const int32_t* bias, void* Y, int64_t ldy, int64_t stride_y, int64_t batch, int M, int K,

@@ -654,3 +654,34 @@ def test_dense_tcgen05_column_panels(panel_mib):
         np.testing.assert_array_equal(got, oracle.dense(a, w, None, shift=11, tok='conv_even', relu=False))
     finally:
         assert L.a4c_set_option(a4c.OPT_DENSE_PANEL_MIB, 32) == 0
+
+
+@pytest.mark.parametrize('shape', [(77, 304, 45), (300, 1024, 272), (1000, 64, 128), (130, 4096, 16), (5, 16, 200)])
+@pytest.mark.parametrize('tok', ['positive_inf', 'conv_even', 'floor'])
+def test_dense_int16_by_int8_on_the_tensor_cores(shape, tok):
+    """int16 activations against int8 weights as two byte digits on tcgen05 (signed high plane, unsigned low plane,
+    combined as (high << 8) + low in wrapping 32-bit arithmetic): full-range codes and long K make the 32-bit
+    accumulator wrap, which the digit form must reproduce bit for bit; every output type, bias, ReLU, ragged widths;
+    and the SIMT kernel on the same arguments."""
+    import gpu_util as G
+    from aie4ml_b200 import lib as a4c
+
+    M, K, N = shape
+    rng = np.random.default_rng(sum(shape))
+    a = rng.integers(-32768, 32768, (M, K)).astype(np.int16)
+    a[0, :] = 32767
+    a[-1, :] = -32768
+    w = rng.integers(-128, 128, (K, N)).astype(np.int8)
+    w[:, 0] = 127
+    bias = rng.integers(-(1 << 31), 1 << 31, N).astype(np.int32)
+    L = a4c.load()
+    for shift, relu, od, b in ((15, False, 'int8', bias), (12, True, 'int16', bias), (17, False, 'uint8', None), (0, False, 'int16', None)):
+        want = oracle.dense(a, w, b, shift=shift, tok=tok, relu=relu, out_dtype=od, acc_bits=32)
+        np.testing.assert_array_equal(G.dense16(a, w, b, shift=shift, tok=tok, relu=relu, out_dtype=od), want)
+    assert L.a4c_set_option(a4c.OPT_WIDE_DENSE_PATH, 1) == 0
+    try:
+        np.testing.assert_array_equal(G.dense16(a, w, bias, shift=15, tok=tok, relu=False, out_dtype='int8'),
+                                      oracle.dense(a, w, bias, shift=15, tok=tok, relu=False, out_dtype='int8', acc_bits=32))
+    finally:
+        assert L.a4c_set_option(a4c.OPT_WIDE_DENSE_PATH, 0) == 0
+    a4c.device_status(G.stream())
