@@ -267,7 +267,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             bool ok = true;
             auto issue_scores = [&](int n) -> bool {
                 const int stage = n % STAGES;
-                if (!mbar_wait(&tail->qkv_full[stage], (uint32_t)(n / STAGES) & 1u, abort_flag, g.status, 122)) return false;
+                if (!mbar_wait_fast(&tail->qkv_full[stage], (uint32_t)(n / STAGES) & 1u, abort_flag, g.status, 122)) return false;
                 tc_fence_after();
                 const uint32_t st = smem_u32(smem + (size_t)stage * STAGE_BYTES);
                 const uint64_t qd = make_smem_desc_k64(st), kd = make_smem_desc_k64(st + TILE_BYTES);
@@ -285,7 +285,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 // already waited for
                 if (n + 1 < n_local) { ok = issue_scores(n + 1); if (!ok) break; }
                 const int grp = n & 1, stage = n % STAGES;
-                ok = mbar_wait(&tail->p_full[grp], (uint32_t)(n >> 1) & 1u, abort_flag, g.status, 123);
+                ok = mbar_wait_fast(&tail->p_full[grp], (uint32_t)(n >> 1) & 1u, abort_flag, g.status, 123);
                 if (!ok) break;
                 tc_fence_after();
                 const uint64_t pd = make_smem_desc(smem_u32(p_smem + (size_t)grp * P_BYTES));
@@ -312,7 +312,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         auto pair_sync = [&]() -> bool {
             __syncwarp();
             if (lane == 0) mbar_arrive(pair_bar);
-            const bool met = mbar_wait(pair_bar, pair_phase, abort_flag, g.status, 126);
+            const bool met = mbar_wait_fast(pair_bar, pair_phase, abort_flag, g.status, 126);
             pair_phase ^= 1u;
             return met;
         };
@@ -337,16 +337,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             const long long b = t / g.m_tiles;
             const int row = (int)(t % g.m_tiles) * BM + r;
             const uint32_t par = (uint32_t)(n >> 1) & 1u;
-            ok = mbar_wait(&tail->s_full[grp], par, abort_flag, g.status, 124);
+            ok = mbar_wait_fast(&tail->s_full[grp], par, abort_flag, g.status, 124);
             if (!ok) break;
             tc_fence_after();
 
             // this thread's 64 scores: accumulators -> codes (score + 128, plus a constant in the upper bits)
             uint32_t v[HALF_COLS];
+            static_assert(HALF_COLS == 64, "one 64-column TMEM load per thread");
+#ifdef A4C_ATT_LD32X2
             tmem_ld32_async(taddr_s, v);
             tmem_ld32_async(taddr_s + 32u, v + 32);
             tmem_ld_wait32(v);
             tmem_ld_wait32(v + 32);
+#else
+            tmem_ld64(taddr_s, v);
+#endif
             int m = (int)0x80000000;
 #pragma unroll
             for (int i = 0; i < HALF_COLS; i += 2) {
@@ -416,12 +421,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             mbar_arrive(&tail->p_full[grp]);
 
             // this thread's 32 columns of the output row
-            ok = mbar_wait(&tail->o_full[grp], par, abort_flag, g.status, 125);
+            ok = mbar_wait_fast(&tail->o_full[grp], par, abort_flag, g.status, 125);
             if (!ok) break;
             tc_fence_after();
             uint32_t oa[DH / HALVES];
-            tmem_ld32_async(taddr_o, oa);
-            tmem_ld_wait32(oa);
+            static_assert(DH / HALVES == 32, "one 32-column TMEM load per thread");
+            tmem_ld32(taddr_o, oa);
             tc_fence_before();
             if (row < g.sq) {
                 uint8_t* orow = g.out + b * g.stride_o + h * g.hstride_o + (long long)row * g.ldo + hf * (DH / HALVES);

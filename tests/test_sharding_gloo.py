@@ -35,6 +35,12 @@ def _worker(rank, world, port, out_dir):
     (name, y), = local.items()
     full = gather_outputs(torch.from_numpy(np.ascontiguousarray(y)), total)
     np.save(Path(out_dir) / f'rank{rank}.npy', full.numpy())
+    # equal shards gather straight into the result (no padding, no trim), also from a strided view
+    even = 2 * (total // 2)
+    s2, e2 = shard_rows(even, rank, world)
+    wide = torch.arange(even * 16, dtype=torch.int32).reshape(even, 16)
+    part = wide[s2:e2, :10]                       # a row pitch wider than the rows, like a 10-wide output in a 16-byte pitch
+    np.save(Path(out_dir) / f'even{rank}.npy', gather_outputs(part, even).numpy())
     dist.barrier()
     dist.destroy_process_group()
 
@@ -53,3 +59,4 @@ def test_two_rank_shard_and_gather_equals_unsharded(tmp_path):
     want = next(iter(oracle.run_plan(from_graph(builder).export_plan(), inputs).values()))
     for r in range(2):
         np.testing.assert_array_equal(np.load(tmp_path / f'rank{r}.npy'), want)
+        np.testing.assert_array_equal(np.load(tmp_path / f'even{r}.npy'), np.arange(36 * 16, dtype=np.int32).reshape(36, 16)[:, :10])
