@@ -16,8 +16,8 @@
 //               4-stage ring
 //   warp 1      MMA issuer: S = Q K^T (M128 N128 K64, both operands K-major) into one of two TMEM score
 //               buffers; later O = P V (M128 N64 K128, P K-major from shared memory, V MN-major) into one of
-//               two TMEM output buffers.  Scores run two items ahead: S(n + 2) is issued as soon as the group
-//               of item n has its scores in registers, so no softmax warp waits for a tensor-core round trip.
+//               two TMEM output buffers.  The next item's S is issued before this item's O, so the tensor
+//               pipe works on scores while the softmax warps are busy.
 //   warps 2-17  softmax: group 0 (even items) and group 1 (odd items) of eight warps each.  TWO threads share a
 //               query row (a TMEM lane): each takes 64 of the 128 score columns -- tcgen05.ld of 64 accumulators,
 //               requantise, maximum, score table lookup (per-lane replicated table in shared memory: no bank
@@ -70,7 +70,6 @@ struct Tail {
     uint64_t qkv_full[STAGES];
     uint64_t qkv_empty[STAGES];
     uint64_t s_full[GROUPS];
-    uint64_t s_free[GROUPS];      // every thread of the group has its scores in registers: the buffer may take the next item's
     uint64_t p_full[GROUPS];
     uint64_t o_full[GROUPS];
     uint64_t pair[GROUPS][4];     // the two warps that share a group's 32 query rows meet here (one arrival per warp)
@@ -200,7 +199,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         for (int s = 0; s < STAGES; ++s) { mbar_init(&tail->qkv_full[s], 1); mbar_init(&tail->qkv_empty[s], 1); }
         for (int s = 0; s < GROUPS; ++s) {
             mbar_init(&tail->s_full[s], 1);
-            mbar_init(&tail->s_free[s], GROUP_THREADS);
             mbar_init(&tail->p_full[s], GROUP_THREADS);
             mbar_init(&tail->o_full[s], 1);
             for (int q = 0; q < 4; ++q) mbar_init(&tail->pair[s][q], HALVES);
@@ -281,21 +279,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 umma_commit(&tail->s_full[n & 1]);
                 return true;
             };
-            // Scores run two items ahead of the value products: S(n + 2) goes into the score buffer of item n as soon as
-            // that group holds S(n) in registers, so a group finds its next scores complete when it comes back for them.
             if (n_local > 0) ok = issue_scores(0);
-            if (ok && n_local > 1) ok = issue_scores(1);
             for (int n = 0; ok && n < n_local; ++n) {
+                // the score buffer of item n+1 was last read for item n-1, whose probabilities this thread has
+                // already waited for
+                if (n + 1 < n_local) { ok = issue_scores(n + 1); if (!ok) break; }
                 const int grp = n & 1, stage = n % STAGES;
-                const uint32_t par = (uint32_t)(n >> 1) & 1u;
-                if (n + 2 < n_local) {
-                    ok = mbar_wait_fast(&tail->s_free[grp], par, abort_flag, g.status, 127);
-                    if (!ok) break;
-                    tc_fence_after();
-                    ok = issue_scores(n + 2);
-                    if (!ok) break;
-                }
-                ok = mbar_wait_fast(&tail->p_full[grp], par, abort_flag, g.status, 123);
+                ok = mbar_wait_fast(&tail->p_full[grp], (uint32_t)(n >> 1) & 1u, abort_flag, g.status, 123);
                 if (!ok) break;
                 tc_fence_after();
                 const uint64_t pd = make_smem_desc(smem_u32(p_smem + (size_t)grp * P_BYTES));
@@ -340,39 +330,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         const float out_mul = __int_as_float((127 - (g.inv_shift + 85)) << 23);  // 2^-(inv_shift + 85)
         const bool clb = g.use_clb && g.mode == 0;
         bool ok = true;
-        // Output rows of one of this group's items: 32 columns of the row this thread shares, out of the group's TMEM
-        // output buffer (complete: the caller has waited for it).
-        auto convert_out = [&](int n_out) {
-            const long long item = first + (long long)n_out * gridDim.x;
+        for (int n = grp; ok && n < n_local; n += GROUPS) {
+            const long long item = first + (long long)n * gridDim.x;
             const int h = (int)(item % g.heads);
             const long long t = item / g.heads;
             const long long b = t / g.m_tiles;
             const int row = (int)(t % g.m_tiles) * BM + r;
-            uint32_t oa[DH / HALVES];
-            static_assert(DH / HALVES == 32, "one 32-column TMEM load per thread");
-            tmem_ld32(taddr_o, oa);
-            if (row < g.sq) {
-                uint8_t* orow = g.out + b * g.stride_o + h * g.hstride_o + (long long)row * g.ldo + hf * (DH / HALVES);
-#pragma unroll
-                for (int c = 0; c < DH / HALVES / 16; ++c) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int i = c * 16 + q * 4;
-                        w[q] = pack4_i8(requant_out<MODE>((int)oa[i + 0], g), requant_out<MODE>((int)oa[i + 1], g),
-                                        requant_out<MODE>((int)oa[i + 2], g), requant_out<MODE>((int)oa[i + 3], g));
-                    }
-                    *reinterpret_cast<uint4*>(orow + c * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-                }
-            }
-        };
-        // Software pipeline per group: the probabilities of item n are computed first; only then does the thread wait
-        // for the value product of the group's PREVIOUS item n - 2 (long complete), which frees the probability tile
-        // for item n and yields the output rows of item n - 2; those are converted before p_full(n) is signalled, so
-        // the value product of item n cannot overwrite them.  No wait of these warps sits behind a tensor-core
-        // round trip any more.
-        int n = grp;
-        for (; ok && n < n_local; n += GROUPS) {
             const uint32_t par = (uint32_t)(n >> 1) & 1u;
             ok = mbar_wait_fast(&tail->s_full[grp], par, abort_flag, g.status, 124);
             if (!ok) break;
@@ -380,13 +343,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
             // this thread's 64 scores: accumulators -> codes (score + 128, plus a constant in the upper bits)
             uint32_t v[HALF_COLS];
-            static_assert(HALF_COLS == 64, "two 32-column TMEM loads per thread");
+            static_assert(HALF_COLS == 64, "one 64-column TMEM load per thread");
+#ifdef A4C_ATT_LD32X2
             tmem_ld32_async(taddr_s, v);
             tmem_ld32_async(taddr_s + 32u, v + 32);
             tmem_ld_wait32(v);
             tmem_ld_wait32(v + 32);
-            tc_fence_before();
-            mbar_arrive(&tail->s_free[grp]);     // the score buffer may take item n + 2
+#else
+            tmem_ld64(taddr_s, v);
+#endif
             int m = (int)0x80000000;
 #pragma unroll
             for (int i = 0; i < HALF_COLS; i += 2) {
@@ -432,43 +397,50 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             }
             inv = min(max(inv, 0), 32767);
             const float invs = (float)inv * out_mul;
-            uint32_t pw[HALF_COLS / 4];          // the 64 probabilities, four to a word
 #pragma unroll
-            for (int i = 0; i < HALF_COLS; i += 4) {
-                // floor(score * inv / 2^shift) in the low bits of a subnormal (scores are non-negative)
-                // with inv = floor(255 * 2^shift / sum) a score <= sum cannot exceed 255; only the power-of-two
-                // reciprocal (use_clb) needs the saturation
-                int o0 = __float_as_int(__fmaf_rd(__uint_as_float(v[i + 0]), invs, 0.0f));
-                int o1 = __float_as_int(__fmaf_rd(__uint_as_float(v[i + 1]), invs, 0.0f));
-                int o2 = __float_as_int(__fmaf_rd(__uint_as_float(v[i + 2]), invs, 0.0f));
-                int o3 = __float_as_int(__fmaf_rd(__uint_as_float(v[i + 3]), invs, 0.0f));
-                if (clb) { o0 = min(o0, 255); o1 = min(o1, 255); o2 = min(o2, 255); o3 = min(o3, 255); }
-                pw[i >> 2] = pack4_i8(o0, o1, o2, o3);
-            }
-            if (n >= GROUPS) {
-                // the value product of item n - 2 has read the probability tile and left its result in TMEM
-                ok = mbar_wait_fast(&tail->o_full[grp], par ^ 1u, abort_flag, g.status, 125);
-                if (!ok) break;
-                tc_fence_after();
-            }
+            for (int c = 0; c < HALF_COLS / 16; ++c) {
+                uint32_t w[4];
 #pragma unroll
-            for (int c = 0; c < HALF_COLS / 16; ++c)
+                for (int q = 0; q < 4; ++q) {
+                    const int i = c * 16 + q * 4;
+                    // floor(score * inv / 2^shift) in the low bits of a subnormal (scores are non-negative)
+                    // with inv = floor(255 * 2^shift / sum) a score <= sum cannot exceed 255; only the power-of-two
+                    // reciprocal (use_clb) needs the saturation
+                    int o0 = __float_as_int(__fmaf_rd(__uint_as_float(v[i + 0]), invs, 0.0f));
+                    int o1 = __float_as_int(__fmaf_rd(__uint_as_float(v[i + 1]), invs, 0.0f));
+                    int o2 = __float_as_int(__fmaf_rd(__uint_as_float(v[i + 2]), invs, 0.0f));
+                    int o3 = __float_as_int(__fmaf_rd(__uint_as_float(v[i + 3]), invs, 0.0f));
+                    if (clb) { o0 = min(o0, 255); o1 = min(o1, 255); o2 = min(o2, 255); o3 = min(o3, 255); }
+                    w[q] = pack4_i8(o0, o1, o2, o3);
+                }
                 // K-major, 128-byte swizzle: 16-byte piece p of row r sits at piece p ^ (r & 7)
-                sts128(p_row + ((((uint32_t)(hf * (HALF_COLS / 16) + c)) ^ sw) << 4), pw[4 * c], pw[4 * c + 1], pw[4 * c + 2],
-                       pw[4 * c + 3]);
-            if (n >= GROUPS) convert_out(n - GROUPS);
+                sts128(p_row + ((((uint32_t)(hf * (HALF_COLS / 16) + c)) ^ sw) << 4), w[0], w[1], w[2], w[3]);
+            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> tensor-core reads
             tc_fence_before();
             mbar_arrive(&tail->p_full[grp]);
-        }
-        // the group's last item: its value product is still to be collected
-        if (ok && n - GROUPS >= 0 && n - GROUPS < n_local) {
-            const int last = n - GROUPS;
-            ok = mbar_wait_fast(&tail->o_full[grp], (uint32_t)(last >> 1) & 1u, abort_flag, g.status, 125);
-            if (ok) {
-                tc_fence_after();
-                convert_out(last);
-                tc_fence_before();
+
+            // this thread's 32 columns of the output row
+            ok = mbar_wait_fast(&tail->o_full[grp], par, abort_flag, g.status, 125);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t oa[DH / HALVES];
+            static_assert(DH / HALVES == 32, "one 32-column TMEM load per thread");
+            tmem_ld32(taddr_o, oa);
+            tc_fence_before();
+            if (row < g.sq) {
+                uint8_t* orow = g.out + b * g.stride_o + h * g.hstride_o + (long long)row * g.ldo + hf * (DH / HALVES);
+#pragma unroll
+                for (int c = 0; c < DH / HALVES / 16; ++c) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int i = c * 16 + q * 4;
+                        w[q] = pack4_i8(requant_out<MODE>((int)oa[i + 0], g), requant_out<MODE>((int)oa[i + 1], g),
+                                        requant_out<MODE>((int)oa[i + 2], g), requant_out<MODE>((int)oa[i + 3], g));
+                    }
+                    *reinterpret_cast<uint4*>(orow + c * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
             }
         }
     }
