@@ -343,15 +343,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
             // this thread's 64 scores: accumulators -> codes (score + 128, plus a constant in the upper bits)
             uint32_t v[HALF_COLS];
-            static_assert(HALF_COLS == 64, "one 64-column TMEM load per thread");
-#ifdef A4C_ATT_LD32X2
+            static_assert(HALF_COLS == 64, "two 32-column TMEM loads per thread");
             tmem_ld32_async(taddr_s, v);
             tmem_ld32_async(taddr_s + 32u, v + 32);
             tmem_ld_wait32(v);
             tmem_ld_wait32(v + 32);
-#else
-            tmem_ld64(taddr_s, v);
-#endif
             int m = (int)0x80000000;
 #pragma unroll
             for (int i = 0; i < HALF_COLS; i += 2) {
