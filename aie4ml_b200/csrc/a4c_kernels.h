@@ -129,3 +129,11 @@ int a4c_dense_tc16_supported(const void* A, long long lda, const void* Wt, long 
 int a4c_launch_dense_tc16(const int16_t* A, long long lda, const int8_t* Wt, long long ldw, const int32_t* bias, void* Y,
                           long long ldy, long long M, int K, int N, int shift, int rounding, int relu, int out_dtype,
                           int* status_word, cudaStream_t stream);
+
+// tcgen05 int8 Dense for K <= 512 and N a multiple of 128 (dense_tcs.cu): the general kernel's 128 x 256 tiles and
+// resident weight tile, twelve epilogue warps in three groups that take half tiles in rotation.  The caller has checked
+// the alignment rules of a4c_dense_tc_supported.
+int a4c_dense_tcs_supported(long long M, int K, int N, int out_dtype, int sms);
+int a4c_launch_dense_tcs(const void* A, long long lda, const void* Wt, long long ldw, const int32_t* bias, void* Y,
+                         long long ldy, long long M, int K, int N, int shift, int rounding, int relu, int out_dtype,
+                         int a_unsigned, int* status_word, cudaStream_t stream);

@@ -330,7 +330,7 @@ int a4c_set_option(int option, int value) {
         g_float_path = value;
         return A4C_OK;
     }
-    if (option == A4C_OPT_DENSE_RESIDENT_W && (value == 0 || value == 1)) {
+    if (option == A4C_OPT_DENSE_RESIDENT_W && value >= 0 && value <= 2) {
         a4c_dense_tc_set_resident_w(value);
         return A4C_OK;
     }

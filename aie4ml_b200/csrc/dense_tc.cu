@@ -81,7 +81,8 @@ constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_
 
 using namespace tc;
 
-int g_dense_resident_w = 1;   // 0 switches the resident-W tile order off (A4C_OPT_DENSE_RESIDENT_W)
+int g_dense_resident_w = 2;   // A4C_OPT_DENSE_RESIDENT_W: 0 off, 1 resident weight tile in this kernel, 2 = 1 plus the
+                              // short-reduction kernel (dense_tcs.cu, twelve epilogue warps) where it applies
 long long g_dense_panel_bytes = 32ll << 20;   // weights per panel of the streaming order; 0 = one panel (A4C_OPT_DENSE_PANEL_MIB)
 
 struct TcArgs {
@@ -463,7 +464,7 @@ cudaError_t launch_mode(const CUtensorMap& ma, const CUtensorMap& mb, const CUte
 
 }  // namespace
 
-void a4c_dense_tc_set_resident_w(int on) { g_dense_resident_w = on ? 1 : 0; }
+void a4c_dense_tc_set_resident_w(int mode) { g_dense_resident_w = mode < 0 ? 0 : (mode > 2 ? 2 : mode); }
 void a4c_dense_tc_set_panel_mib(int mib) { g_dense_panel_bytes = (long long)mib << 20; }
 
 int a4c_dense_tc_supported(const void* A, long long lda, const void* Wt, long long ldw, const void* Y,
@@ -485,6 +486,15 @@ int a4c_launch_dense_tc(const void* A, long long lda, const void* Wt, long long 
     const int sup = a4c_dense_tc_supported(A, lda, Wt, ldw, Y, ldy, M, K, N, out_dtype);
     if (sup != A4C_OK) return sup;
     if (M == 0) return A4C_OK;
+    {
+        // short reductions with enough row tiles: the kernel with more epilogue warps in flight
+        int dev0 = 0, sms0 = 148;
+        cudaGetDevice(&dev0);
+        cudaDeviceGetAttribute(&sms0, cudaDevAttrMultiProcessorCount, dev0);
+        if (g_dense_resident_w == 2 && a4c_dense_tcs_supported(M, K, N, out_dtype, sms0) == A4C_OK)
+            return a4c_launch_dense_tcs(A, lda, Wt, ldw, bias, Y, ldy, M, K, N, shift, rounding, relu, out_dtype, a_unsigned,
+                                        status_word, stream);
+    }
     CUtensorMap ma, mb, my;
     const int w_box_rows = (N + BN - 1) / BN == 1 ? ((N + 15) / 16) * 16 : BN;
     if (!make_map(&ma, A, M, K, lda, BM) || !make_map(&mb, Wt, N, K, ldw, w_box_rows) ||

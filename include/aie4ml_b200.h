@@ -53,7 +53,7 @@ extern "C" {
 /* Options for a4c_set_option */
 #define A4C_OPT_ROWOP_PATH 0 /* 0 = auto (bandwidth-oriented row kernels when they apply), 1 = generic kernels only */
 #define A4C_OPT_BMM_PATH 1   /* 0 = auto (tcgen05 batched MatMul when its alignment rules hold), 1 = dp4a kernel only */
-#define A4C_OPT_DENSE_RESIDENT_W 5 /* tcgen05 Dense, K <= 512: 1 (default) = a CTA keeps its weight tile in shared memory and streams A only, 0 = off */
+#define A4C_OPT_DENSE_RESIDENT_W 5 /* tcgen05 Dense, K <= 512: a CTA keeps its weight tile in shared memory and streams A only.  0 = off, 1 = in the general kernel (eight epilogue warps), 2 (default) = 1 plus, when N is a multiple of 128, the short-reduction kernel (same tiles, twelve epilogue warps on half tiles) */
 #define A4C_OPT_DENSE_PANEL_MIB 8 /* tcgen05 Dense, streaming tile order: MiB of weights per column panel (default 32; 0 = one panel, column tile fastest over the whole width) */
 #define A4C_OPT_WIDE_DENSE_PATH 9 /* a4c_dense_i16 with int8 weights: 0 = auto (tcgen05, the activation's two byte digits in turn), 1 = SIMT kernel only */
 #define A4C_OPT_FLOAT_DENSE_PATH 7 /* a4c_dense_f, bfloat16 / fp8: 0 = auto (tcgen05 kernel when its alignment rules hold), 1 = tiled SIMT kernel only */

@@ -71,11 +71,15 @@ def test_dense_tcgen05_output_widths_that_are_not_multiples_of_16(shape):
     np.testing.assert_array_equal(got, oracle.dense(a, w, None, shift=6, tok='conv_even', relu=False))
 
 
-@pytest.mark.parametrize('shape', [(76000, 256, 256), (19100, 128, 1024), (25300, 384, 700), (77000, 512, 40)])
-@pytest.mark.parametrize('resident', [1, 0])
+@pytest.mark.parametrize('shape', [(76000, 256, 256), (19100, 128, 1024), (25300, 384, 700), (77000, 512, 40),
+                                   (76100, 256, 768), (30001, 200, 384), (40000, 512, 128), (33000, 512, 640)])
+@pytest.mark.parametrize('resident', [2, 1, 0])
 def test_dense_tcgen05_small_k_with_and_without_a_resident_weight_tile(shape, resident):
     """Shapes large enough for the resident-W tile order (one weight tile per CTA kept in shared memory, A streamed
-    through a deeper ring): one, three and four column tiles, ragged last row tile, a narrow classifier head."""
+    through a deeper ring): one, three and four column tiles, ragged last row tile, a narrow classifier head.  Mode 2
+    (the default) sends widths that are multiples of 128 to the short-reduction kernel (twelve epilogue warps on half
+    tiles): one to four column tiles there, widths whose last column tile is a single half (128, 384, 640), a K tail
+    shorter than a stage, K = 512 (four ring slots)."""
     import gpu_util as G
     from aie4ml_b200 import lib as a4c
 
@@ -88,8 +92,11 @@ def test_dense_tcgen05_small_k_with_and_without_a_resident_weight_tile(shape, re
         np.testing.assert_array_equal(got, oracle.dense(a, w, bias, shift=9, tok='positive_inf', relu=True))
         got = G.dense(a, w, None, shift=8, tok='conv_even', relu=False, algo=TC)
         np.testing.assert_array_equal(got, oracle.dense(a, w, None, shift=8, tok='conv_even', relu=False))
+        u = np.random.default_rng(5).integers(0, 256, (M, K)).astype(np.uint8)
+        got = G.dense(u, w, bias, shift=10, tok='symmetric_inf', relu=False, out_dtype='uint8', algo=TC)
+        np.testing.assert_array_equal(got, oracle.dense(u, w, bias, shift=10, tok='symmetric_inf', relu=False, out_dtype='uint8'))
     finally:
-        assert L.a4c_set_option(a4c.OPT_DENSE_RESIDENT_W, 1) == 0
+        assert L.a4c_set_option(a4c.OPT_DENSE_RESIDENT_W, 2) == 0
 
 
 @pytest.mark.parametrize('tok', TOKENS)
