@@ -137,3 +137,12 @@ int a4c_dense_tcs_supported(long long M, int K, int N, int out_dtype, int sms);
 int a4c_launch_dense_tcs(const void* A, long long lda, const void* Wt, long long ldw, const int32_t* bias, void* Y,
                          long long ldy, long long M, int K, int N, int shift, int rounding, int relu, int out_dtype,
                          int a_unsigned, int* status_word, cudaStream_t stream);
+
+// Dense -> residual Add -> LayerNorm in one kernel for layers 256 features wide (dense_ln.cu).
+int a4c_dense_ln_supported(long long M, int K, int N, long long lda, long long ldw, long long ldr, long long ldo,
+                           int shift, int rounding, int out_shift, int eps_q0, int gamma_absmax);
+int a4c_launch_dense_ln(const void* A, long long lda, int a_unsigned, const void* Wt, long long ldw, const int32_t* bias,
+                        int shift, int relu, const int8_t* residual, long long ldr, const int16_t* gamma,
+                        const int16_t* beta, int8_t* out, long long ldo, long long M, int K, int N, int eps_q0,
+                        int out_shift, int rounding, int gamma_absmax, int* status_word, cudaStream_t stream);
+void a4c_dense_ln_set_enabled(int on);

@@ -326,6 +326,10 @@ int a4c_set_option(int option, int value) {
         g_wide_path = value;
         return A4C_OK;
     }
+    if (option == A4C_OPT_DENSE_LN_PATH && (value == 0 || value == 1)) {
+        a4c_dense_ln_set_enabled(value == 0);
+        return A4C_OK;
+    }
     if (option == A4C_OPT_FLOAT_DENSE_PATH && (value == 0 || value == 1)) {
         g_float_path = value;
         return A4C_OK;
@@ -387,6 +391,27 @@ int a4c_add_layernorm_i8(const int8_t* x, int64_t ldx, const int8_t* residual, i
     if (residual == nullptr) return A4C_ERR_INVALID_ARG;
     return layernorm_any(x, ldx, gamma, beta, residual, ldr, 1, out, ldo, rows, cols, eps_q0, out_shift, rounding,
                          gamma_absmax, stream);
+}
+
+int a4c_dense_add_layernorm_supported(int64_t M, int K, int N, int64_t lda, int64_t ldw, int64_t ldr, int64_t ldo, int shift,
+                                      int rounding, int out_shift, int eps_q0, int gamma_absmax) {
+    return a4c_dense_ln_supported(M, K, N, lda, ldw, ldr, ldo, shift, rounding, out_shift, eps_q0, gamma_absmax);
+}
+
+int a4c_dense_add_layernorm_i8(const void* A, int64_t lda, int a_unsigned, const int8_t* Wt, int64_t ldw,
+                               const int32_t* bias, int shift, int relu, const int8_t* residual, int64_t ldr,
+                               const int16_t* gamma, const int16_t* beta, int8_t* out, int64_t ldo, int64_t M, int K,
+                               int N, int eps_q0, int out_shift, int rounding, int gamma_absmax, void* stream) {
+    if (A == nullptr || Wt == nullptr || residual == nullptr || gamma == nullptr || beta == nullptr || out == nullptr)
+        return A4C_ERR_INVALID_ARG;
+    if (M < 0 || K <= 0 || N <= 0 || !valid_round(rounding)) return A4C_ERR_INVALID_ARG;
+    if (M == 0) return A4C_OK;
+    int* status = status_word();
+    if (status == nullptr) return A4C_ERR_CUDA;
+    const int rc = a4c_launch_dense_ln(A, lda, a_unsigned, Wt, ldw, bias, shift, relu, residual, ldr, gamma, beta, out, ldo, M,
+                                       K, N, eps_q0, out_shift, rounding, gamma_absmax, status, (cudaStream_t)stream);
+    if (rc != A4C_OK) return rc;
+    return finish();
 }
 
 int a4c_softmax_i8(const int8_t* x, int64_t ldx, const void* addend, int64_t ldadd, void* out, int64_t ldo,

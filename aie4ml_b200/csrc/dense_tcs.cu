@@ -201,7 +201,9 @@ dense_tcs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const uint32_t idesc = my_halves == 2 ? g.idesc : make_idesc(BM, HALF_N, (g.idesc & (1u << 7)) == 0);
             for (int i = 0; ok && i < my_tiles; ++i) {
                 const int acc = i & 1;
-                ok = mbar_wait_spin(&tail->tmem_empty[acc], ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag, g.status, 162);
+                // epilogue-bound kernel: the issuer mostly waits here, so it sleeps in the barrier instead of polling (a
+                // polling issuer takes issue slots from the epilogue warps of its scheduler)
+                ok = mbar_wait(&tail->tmem_empty[acc], ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag, g.status, 162);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);

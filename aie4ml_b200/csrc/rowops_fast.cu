@@ -21,16 +21,14 @@
 // integer kernels of rowops.cu.
 #include "a4c_common.cuh"
 #include "a4c_kernels.h"
+#include "ln_math.cuh"
 
 namespace {
 
+using namespace lnm;
+
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr float MAGIC = 12582912.0f;               // 1.5 * 2^23
-constexpr uint32_t MAGIC_BITS = 0x4B400000u;
-constexpr float TWO_M64 = 5.421010862427522e-20f;  // 2^-64
-constexpr float TWO_P64 = 18446744073709551616.0f; // 2^64
-
 // ---- shared-memory / barrier primitives on 32-bit shared addresses ----------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint4 lds128(uint32_t a) {
@@ -85,18 +83,6 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 __device__ __forceinline__ void stg16(void* p, uint4 v) {
     asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
-__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {
-    int d;
-    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-// prmt.b32 in its default mode: selector nibble n picks byte (n & 7) of {b:a}; bit 3 of the nibble
-// replicates that byte's sign bit instead
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-    uint32_t d;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-    return d;
-}
 // Sum / maximum over the G = 2^k adjacent lanes that share a row.  A whole warp (G = 32) uses the warp-wide reduce
 // instruction.  Given several member masks in one warp that instruction is replayed once per mask (eight times for
 // G = 4: 1.3x the run time of a whole LayerNorm at 256 columns), so smaller groups use an xor butterfly, which costs
@@ -111,12 +97,6 @@ __device__ __forceinline__ int group_max(int v, int G) {
     for (int d = G >> 1; d > 0; d >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, d));
     return v;
 }
-// float 2^23 + byte K of w (bytes taken as unsigned)
-template <int K>
-__device__ __forceinline__ float byte_to_f23(uint32_t w) {
-    return __uint_as_float(prmt(w, 0x4B000000u, 0x7540 + K));
-}
-
 // A row of `cols` bytes is nchunks 16-byte chunks.  G lanes share a row (lane gl takes chunks gl, gl + G, ...),
 // a warp works on R = 32 / G rows at once.  Rows sit `pitch` bytes apart in a ring slot: when fewer than
 // eight lanes share a row, a quarter-warp's 128-bit loads touch several rows, and the pad of G * 16 bytes
@@ -183,48 +163,6 @@ struct LnFastArgs {
     RowGeom geom;
     int* status;
 };
-
-// Round a non-negative binary32 value to an integer with an AIE rounding token.
-__device__ __forceinline__ int round_float_tok(float f, int tok) {
-    const float fl = floorf(f);
-    const float frac = f - fl;
-    const int q = (int)fl;
-    switch (tok) {
-        case A4C_RND_FLOOR: return q;
-        case A4C_RND_CEIL: return q + (frac > 0.0f);
-        case A4C_RND_POSITIVE_INF:
-        case A4C_RND_SYMMETRIC_INF: return q + (frac >= 0.5f);
-        case A4C_RND_NEGATIVE_INF:
-        case A4C_RND_SYMMETRIC_ZERO: return q + (frac > 0.5f);
-        case A4C_RND_CONV_EVEN: return q + ((frac > 0.5f) || (frac == 0.5f && (q & 1)));
-        default: return q + ((frac > 0.5f) || (frac == 0.5f && !(q & 1)));
-    }
-}
-
-// The defining expression of the Q15 reciprocal standard deviation (layer_norm.cpp:33-39):
-// clamp(round_tok(2^15 * (1.0f / sqrtf((float)var))), 0, 32767) with correctly rounded sqrt and divide.
-__device__ __noinline__ int inv_std_exact(int var, int tok) {
-    const float inv_f32 = __fdiv_rn(1.0f, __fsqrt_rn(__int2float_rn(var)));
-    return clampi(round_float_tok(__fmul_rn(inv_f32, 32768.0f), tok), 0, 32767);
-}
-
-// Same value, usually in a handful of instructions: y ~= 2^15 * rsqrt(var) from the approximate unit is within
-// 0.02 of the exactly rounded product (both relative errors are below 2^-21.4 and y <= 32768); unless y sits
-// that close to a rounding boundary of the mode, rounding y gives the defined result.  The rare boundary cases
-// (and var < 4, where the clamp is near) take the exact path.
-__device__ __forceinline__ int inv_std_q15(int var, int tok, bool nearest) {
-    float y;
-    asm("rsqrt.approx.f32 %0, %1;" : "=f"(y) : "f"(__int2float_rn(var)));
-    y *= 32768.0f;
-    const float fl = floorf(y);
-    const float frac = y - fl;
-    const float dist = nearest ? fabsf(frac - 0.5f) : fminf(frac, 1.0f - frac);
-    if (dist < 0.02f || var < 4) return inv_std_exact(var, tok);
-    int q = (int)fl;
-    if (nearest) q += frac > 0.5f;
-    else if (tok == A4C_RND_CEIL) q += 1;
-    return q;
-}
 
 // FS = 0: conv_even, fscale = rne(inv_std * gamma / 128) in one nearest-even FMA
 // FS = 1: floor-type modes with |gamma| <= 511: inv_std * gamma + c0 is exact in FP32, then one round-down FMA
@@ -302,18 +240,9 @@ __global__ void __launch_bounds__(kThreads) layernorm_fast_kernel(LnFastArgs a) 
             xv[j] = ok ? lds128(slot + j * G * 16) : make_uint4(0, 0, 0, 0);
             if (RING_ADD) av[j] = ok ? lds128(slot + rc.add_off + j * G * 16) : make_uint4(0, 0, 0, 0);
             if (PRE_ADD) {
-                // x <- saturate_i8(x + addend) (elementwise_add.cpp:30-33, SHIFT = 0): sign-extended byte pairs,
-                // packed add + min(., 127), packed max(., -128), low bytes back into one word
-                uint32_t xs[4] = {xv[j].x, xv[j].y, xv[j].z, xv[j].w};
-                const uint32_t as[4] = {av[j].x, av[j].y, av[j].z, av[j].w};
-#pragma unroll
-                for (int w = 0; w < 4; ++w) {
-                    uint32_t lo = __viaddmin_s16x2(prmt(xs[w], 0, 0x9180), prmt(as[w], 0, 0x9180), 0x007F007Fu);
-                    uint32_t hi = __viaddmin_s16x2(prmt(xs[w], 0, 0xB3A2), prmt(as[w], 0, 0xB3A2), 0x007F007Fu);
-                    lo = __vimax3_s16x2(lo, 0xFF80FF80u, 0xFF80FF80u);
-                    hi = __vimax3_s16x2(hi, 0xFF80FF80u, 0xFF80FF80u);
-                    xs[w] = prmt(lo, hi, 0x6420);
-                }
+                // x <- saturate_i8(x + addend) (elementwise_add.cpp:30-33, SHIFT = 0)
+                const uint32_t xs[4] = {sat_add_i8x4(xv[j].x, av[j].x), sat_add_i8x4(xv[j].y, av[j].y),
+                                        sat_add_i8x4(xv[j].z, av[j].z), sat_add_i8x4(xv[j].w, av[j].w)};
                 xv[j] = make_uint4(xs[0], xs[1], xs[2], xs[3]);
             }
         }

@@ -33,6 +33,7 @@ OPT_DENSE_RESIDENT_W = 5
 OPT_FLOAT_DENSE_PATH = 7
 OPT_DENSE_PANEL_MIB = 8
 OPT_WIDE_DENSE_PATH = 9
+OPT_DENSE_LN_PATH = 10
 
 # name -> (restype, argtypes); mirrors the header declaration by declaration
 SIGNATURES = {
@@ -67,6 +68,11 @@ SIGNATURES = {
     'a4c_add_f': (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
     'a4c_add_layernorm_i8': (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
                                      c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    'a4c_dense_add_layernorm_supported': (c_int, [c_int64, c_int, c_int, c_int64, c_int64, c_int64, c_int64, c_int, c_int,
+                                                  c_int, c_int, c_int]),
+    'a4c_dense_add_layernorm_i8': (c_int, [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p,
+                                           c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int,
+                                           c_int, c_int, c_int, c_void_p]),
     'a4c_attention_i8_supported': (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64,
                                            c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int,
                                            c_int, c_int, c_int, c_int, c_int, c_int]),

@@ -71,6 +71,7 @@ class CudaModel:
                              merge_attention_heads=bool(fusion.get('attention_heads', True)),
                              merge_parallel_dense=bool(fusion.get('parallel_dense', True)),
                              fuse_dense_chain=bool(fusion.get('dense_chain', True)),
+                             fuse_dense_ln=bool(fusion.get('dense_ln', True)),
                              dense_algo=int(self._ctx.aie_config.get('DenseAlgo', 0)))
         return 0
 

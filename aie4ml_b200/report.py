@@ -43,6 +43,10 @@ def op_cost(plan, op: Dict[str, Any]) -> Dict[str, float]:
         M = _numel(plan, op['lhs']) // op['K']
         return {'bytes': M * op['K'] * esz(op['lhs']) + op['K'] * op['N'] + 4 * op['N'] + M * op['N'] * esz(op['out']),
                 'ops': 2.0 * M * op['K'] * op['N']}
+    if kind == 'dense_add_ln':
+        d = op['dense']
+        M = _numel(plan, op['lhs']) // d['K']
+        return {'bytes': M * d['K'] + d['K'] * d['N'] + 8 * d['N'] + 2 * M * d['N'], 'ops': 2.0 * M * d['K'] * d['N']}
     if kind == 'mlp':
         dims = op['dims']
         M = _numel(plan, op['lhs']) // dims[0]

@@ -111,7 +111,8 @@ class Plan:
 
     def __init__(self, ctx: BackendContext, device: Optional[str] = None, fuse_rowop_add: bool = True,
                  dense_algo: int = _lib.ALGO_AUTO, share_params: Optional['Plan'] = None, fuse_attention: bool = True,
-                 fuse_dense_chain: bool = True, merge_attention_heads: bool = True, merge_parallel_dense: bool = True):
+                 fuse_dense_chain: bool = True, merge_attention_heads: bool = True, merge_parallel_dense: bool = True,
+                 fuse_dense_ln: bool = True):
         torch = _torch()
         self.ctx = ctx
         self.lib = _lib.load()
@@ -123,10 +124,10 @@ class Plan:
         # entry into it from this plan runs with the plan's device current, whatever the caller had selected.
         with torch.cuda.device(self.device):
             self._build(ctx, fuse_rowop_add, dense_algo, share_params, fuse_attention, fuse_dense_chain,
-                        merge_attention_heads, merge_parallel_dense)
+                        merge_attention_heads, merge_parallel_dense, fuse_dense_ln)
 
     def _build(self, ctx, fuse_rowop_add, dense_algo, share_params, fuse_attention, fuse_dense_chain,
-               merge_attention_heads, merge_parallel_dense) -> None:
+               merge_attention_heads, merge_parallel_dense, fuse_dense_ln) -> None:
         torch = _torch()
         self.dense_algo = int(dense_algo)
         self.fuse_rowop_add = bool(fuse_rowop_add)
@@ -199,11 +200,13 @@ class Plan:
             self._fuse_dense_chain()
         if fuse_rowop_add:
             self._fuse_add_layernorm()
+            if fuse_dense_ln:
+                self._fuse_dense_add_layernorm()
             self._fuse_rowop_add()
 
         live = set(graph.input_tensor_names) | set(graph.output_tensor_names)
         for op in self.ops:
-            for key in ('lhs', 'rhs', 'out', 'addend', 'pre_addend', 'q', 'k', 'v'):
+            for key in ('lhs', 'rhs', 'out', 'addend', 'pre_addend', 'residual', 'q', 'k', 'v'):
                 if op.get(key):
                     live.add(op[key])
             for member in op.get('members', ()):
@@ -436,6 +439,54 @@ class Plan:
         if drop:
             self.ops = [op for i, op in enumerate(self.ops) if i not in drop]
 
+    def _fuse_dense_add_layernorm(self) -> None:
+        """dense -> add (residual) -> layer_norm becomes one launch when the library has the single kernel for the
+        shapes (a4c_dense_add_layernorm_supported: the layer is 256 features wide, so one accumulator tile holds whole
+        rows).  Runs after the Add has been folded into the LayerNorm; the Dense output must feed only that Add and be
+        neither a graph output nor a view.  Neither the Dense output nor the sum gets a buffer."""
+        graph = self.graph
+        produced_at = {op['out']: i for i, op in enumerate(self.ops)}
+        aliased = set(self.alias) | {p for p, _, _ in self.alias.values()}
+        replace, drop = {}, set()
+        for i, ln in enumerate(self.ops):
+            if ln['kind'] != 'layer_norm' or not ln.get('pre_addend') or ln.get('addend') or ln.get('out_dtype', 'int8') != 'int8':
+                continue
+            for mid, other in ((ln['lhs'], ln['pre_addend']), (ln['pre_addend'], ln['lhs'])):
+                j = produced_at.get(mid)
+                if j is None or j in drop or j >= i:
+                    continue
+                d = self.ops[j]
+                if (d['kind'] != 'dense' or d['transpose_lhs'] or d['lhs_dtype'] not in ('int8', 'uint8')
+                        or d.get('rhs_dtype', 'int8') != 'int8' or d['out_dtype'] != 'int8' or d['rounding'] != ln['rounding']
+                        or d['N'] != ln['cols']):
+                    continue
+                if len(graph.tensors[mid].consumers) != 1 or mid in graph.output_tensor_names or mid in aliased:
+                    continue
+                if self.fmt[other] != 'int8' or self.fmt[ln['out']] != 'int8':
+                    continue
+                try:
+                    _, M, K, lda = collapse_2d(self._view(d['lhs']), d['name'])
+                    _, Mr, Nr, ldr = collapse_2d(self._view(other), ln['name'])
+                    _, Mo, No, ldo = collapse_2d(self._view(ln['out']), ln['name'])
+                except NotImplementedError:
+                    continue
+                if (M, d['N']) != (Mr, Nr) or (Mr, Nr) != (Mo, No) or K != d['K']:
+                    continue
+                ldw = int(self.params_np[d['weight']].shape[1])
+                gmax = int(np.abs(self.params_np[ln['gamma']].astype(np.int64)).max())
+                if self.lib.a4c_dense_add_layernorm_supported(M, K, d['N'], lda, ldw, ldr, ldo, d['shift'],
+                                                              ROUNDING_CODE[d['rounding']], ln['out_shift'], ln['eps_q0'],
+                                                              gmax) != 0:
+                    continue
+                name = f"{d['name']}+{ln['name']}"
+                replace[i] = {'kind': 'dense_add_ln', 'name': name, 'lhs': d['lhs'], 'residual': other, 'out': ln['out'],
+                              'dense': d, 'ln': ln, 'gamma_absmax': gmax}
+                drop.add(j)
+                self.fused.append(name)
+                break
+        if replace:
+            self.ops = [replace.get(i, op) for i, op in enumerate(self.ops) if i not in drop]
+
     def _attention_args(self, op: Dict[str, Any]) -> tuple:
         """Positional arguments of a4c_attention_heads_i8 up to (not including) `rounding`, from the four views (of the
         first head when the op covers several)."""
@@ -662,6 +713,21 @@ class Plan:
             args = (self.ptr(a, a_off), lda, int(layers[0]['lhs_dtype'] == 'uint8'), n, c_dims, c_w, c_ldw, c_b, c_shift,
                     c_relu, ROUNDING_CODE[op['rounding']], self.ptr(y, y_off), ldy, DTYPE_CODE[layers[-1]['out_dtype']], M)
             return L.a4c_mlp_i8, args
+        if kind == 'dense_add_ln':
+            d, ln = op['dense'], op['ln']
+            a, r, y = self._view(op['lhs']), self._view(op['residual']), self._view(op['out'])
+            a_off, M, K, lda = collapse_2d(a, f'{name}: input')
+            r_off, Mr, Nr, ldr = collapse_2d(r, f'{name}: residual')
+            y_off, My, N, ldy = collapse_2d(y, f'{name}: output')
+            if (M, K, N) != (My, d['K'], d['N']) or (Mr, Nr) != (M, N):
+                raise ValueError(f'{name}: shape mismatch between views.')
+            w = self.params[d['weight']]
+            bias = self.params[d['bias']] if d['bias'] else None
+            args = (self.ptr(a, a_off), lda, int(d['lhs_dtype'] == 'uint8'), w.data_ptr(), int(w.shape[1]),
+                    bias.data_ptr() if bias is not None else None, d['shift'], int(d['relu']), self.ptr(r, r_off), ldr,
+                    self.params[ln['gamma']].data_ptr(), self.params[ln['beta']].data_ptr(), self.ptr(y, y_off), ldy, M, K, N,
+                    ln['eps_q0'], ln['out_shift'], ROUNDING_CODE[ln['rounding']], op['gamma_absmax'])
+            return L.a4c_dense_add_layernorm_i8, args
         if kind == 'attention':
             args = self._attention_args(op) + (ROUNDING_CODE[op['rounding']], op['sm_mode'], op['B'], op['S'],
                                                op['Dmax'], op['inv_shift'], op['use_clb'], op['exp_kq'])

@@ -56,6 +56,7 @@ extern "C" {
 #define A4C_OPT_DENSE_RESIDENT_W 5 /* tcgen05 Dense, K <= 512: a CTA keeps its weight tile in shared memory and streams A only.  0 = off, 1 = in the general kernel (eight epilogue warps), 2 (default) = 1 plus, when N is a multiple of 128, the short-reduction kernel (same tiles, twelve epilogue warps on half tiles) */
 #define A4C_OPT_DENSE_PANEL_MIB 8 /* tcgen05 Dense, streaming tile order: MiB of weights per column panel (default 32; 0 = one panel, column tile fastest over the whole width) */
 #define A4C_OPT_WIDE_DENSE_PATH 9 /* a4c_dense_i16 with int8 weights: 0 = auto (tcgen05, the activation's two byte digits in turn), 1 = SIMT kernel only */
+#define A4C_OPT_DENSE_LN_PATH 10 /* a4c_dense_add_layernorm_i8 / _supported: 0 = the single kernel where it applies (default), 1 = never (the plan keeps Dense and Add + LayerNorm as two launches) */
 #define A4C_OPT_FLOAT_DENSE_PATH 7 /* a4c_dense_f, bfloat16 / fp8: 0 = auto (tcgen05 kernel when its alignment rules hold), 1 = tiled SIMT kernel only */
 #define A4C_OPT_MLP_PATH 4   /* a4c_mlp_i8: 0 = auto, 1 = one Dense launch per layer, 2 = the single-kernel narrow chain only */
 /* Tuning of the bandwidth-oriented row kernels (results do not depend on either): */
@@ -139,6 +140,27 @@ A4C_API int a4c_layernorm_i8(const int8_t* x, int64_t ldx, const int16_t* gamma,
 A4C_API int a4c_add_layernorm_i8(const int8_t* x, int64_t ldx, const int8_t* residual, int64_t ldr,
                          const int16_t* gamma, const int16_t* beta, int8_t* out, int64_t ldo, int64_t rows,
                          int cols, int eps_q0, int out_shift, int rounding, int gamma_absmax, void* stream);
+
+/*
+ * out = layernorm( saturate_i8( dense(A) + residual ) ) in ONE kernel: the Dense of dense_bias_relu.cpp:67-166
+ * (int8 output, bias / shift / rounding / relu as a4c_dense_i8), the exact-type residual Add of
+ * elementwise_add.cpp:12-37 (SHIFT = 0) and the LayerNorm of layer_norm.cpp:15-121 over the Dense's N columns.
+ * The reference connects the three kernels by streams ("direct" transport, passes/transport/classify.py:25-49), so
+ * neither intermediate touches memory there either; as separate launches here each would make a round trip through HBM.
+ * One accumulator tile must hold whole rows: N = 256, all pitches multiples of 16 bytes, bases 16-byte aligned, and
+ * the LayerNorm within the bandwidth-oriented row kernel's envelope (tokens other than symmetric_* / conv_odd,
+ * gamma_absmax in [1, 16383], eps_q0 in [1, 2^20], out_shift <= 13).  a4c_dense_add_layernorm_supported returns A4C_OK when
+ * the request is inside that envelope and A4C_ERR_UNSUPPORTED otherwise (then run a4c_dense_i8 and
+ * a4c_add_layernorm_i8); the launch entry returns the same codes.  The result is the same bytes as those two calls.
+ *   A: [M, K] int8 (a_unsigned = 1: uint8), pitch lda;  Wt: [N, K] int8, pitch ldw;  bias: int32 [N] or NULL
+ *   residual: [M, N] int8, pitch ldr;  gamma int16 Q7 [N], beta int16 Q15 [N];  out: [M, N] int8, pitch ldo
+ */
+A4C_API int a4c_dense_add_layernorm_supported(int64_t M, int K, int N, int64_t lda, int64_t ldw, int64_t ldr, int64_t ldo,
+                                      int shift, int rounding, int out_shift, int eps_q0, int gamma_absmax);
+A4C_API int a4c_dense_add_layernorm_i8(const void* A, int64_t lda, int a_unsigned, const int8_t* Wt, int64_t ldw,
+                               const int32_t* bias, int shift, int relu, const int8_t* residual, int64_t ldr,
+                               const int16_t* gamma, const int16_t* beta, int8_t* out, int64_t ldo, int64_t M, int K,
+                               int N, int eps_q0, int out_shift, int rounding, int gamma_absmax, void* stream);
 
 /*
  * Quantized Softmax over rows of int8, output uint8 (dtype 1) or int16 (dtype 2).

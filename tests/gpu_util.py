@@ -88,6 +88,33 @@ def add_layer_norm(x, residual, gamma, beta, *, eps_q0, out_shift, tok):
     return o_d.cpu().numpy()
 
 
+def dense_add_layer_norm(a, w_kn, bias, residual, gamma, beta, *, shift, tok, relu, eps_q0, out_shift, ldr=None, ldo=None):
+    """The single kernel through the C ABI; None when the library says the request is outside its envelope."""
+    L = a4c.load()
+    M, K = a.shape
+    N = w_kn.shape[1]
+    lda = (K + 15) // 16 * 16
+    ldr, ldo = ldr or N, ldo or N
+    wt = dev(pack_wt(w_kn))
+    gmax = int(np.abs(gamma.astype(np.int64)).max())
+    if L.a4c_dense_add_layernorm_supported(M, K, N, lda, wt.shape[1], ldr, ldo, shift, ROUNDING_CODE[tok], out_shift, eps_q0,
+                                           gmax) != 0:
+        return None
+    a_d, r_d = dev(padded(a, lda)), dev(padded(residual, ldr))
+    b_d = dev(bias.astype(np.int32)) if bias is not None else None
+    g_d, be_d = dev(gamma.astype(np.int16)), dev(beta.astype(np.int16))
+    o_d = torch.full((M, ldo), 0x5A, dtype=torch.int8, device='cuda')
+    rc = L.a4c_dense_add_layernorm_i8(a_d.data_ptr(), lda, int(a.dtype == np.uint8), wt.data_ptr(), wt.shape[1],
+                                      b_d.data_ptr() if b_d is not None else None, shift, int(relu), r_d.data_ptr(), ldr,
+                                      g_d.data_ptr(), be_d.data_ptr(), o_d.data_ptr(), ldo, M, K, N, eps_q0, out_shift,
+                                      ROUNDING_CODE[tok], gmax, stream())
+    a4c.check(rc, 'a4c_dense_add_layernorm_i8')
+    a4c.device_status(stream())
+    y = o_d.cpu().numpy()
+    assert (y[:, N:] == 0x5A).all(), 'kernel wrote into the row padding'
+    return y[:, :N]
+
+
 def layer_norm(x, gamma, beta, *, eps_q0, out_shift, tok, addend=None):
     L = a4c.load()
     rows, cols = x.shape

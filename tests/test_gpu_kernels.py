@@ -287,6 +287,62 @@ def test_add_then_layer_norm_in_one_pass(cols, tok, rowop_path):
         np.testing.assert_array_equal(got, want)
 
 
+@pytest.mark.parametrize('M,K', [(1, 16), (129, 256), (300, 96), (5000, 256), (2049, 1024), (40000, 384)])
+@pytest.mark.parametrize('tok', ['positive_inf', 'conv_even', 'floor', 'ceil', 'negative_inf'])
+def test_dense_add_layer_norm_single_kernel(M, K, tok):
+    """Dense -> residual Add -> LayerNorm in one kernel (256 features) against the oracle's three steps: both operand
+    layouts (weights resident for K <= 256, streamed above), ragged last row tile, sums that saturate on both sides,
+    with and without bias / ReLU, uint8 activations, large gamma (integer fscale path), padded residual / output rows."""
+    import gpu_util as G
+
+    N = 256
+    rng = np.random.default_rng(M * 131 + K)
+    w = rng.integers(-128, 128, (K, N)).astype(np.int8)
+    residual = rng.integers(-128, 128, (M, N)).astype(np.int8)
+    residual[0] = 127
+    residual[-1] = -128
+    shift = max(1, int(np.ceil(np.log2(K))) + 2)
+    cases = [dict(relu=False, bias=True, unsigned=False, gmax=256, out_shift=4, ld=N),
+             dict(relu=True, bias=False, unsigned=True, gmax=16383, out_shift=13, ld=N + 16)]
+    for c in cases:
+        a = (rng.integers(0, 256, (M, K)).astype(np.uint8) if c['unsigned'] else rng.integers(-128, 128, (M, K)).astype(np.int8))
+        bias = rng.integers(-(1 << 12), 1 << 12, N) if c['bias'] else None
+        gamma = rng.integers(-c['gmax'], c['gmax'] + 1, N)
+        gamma[0] = c['gmax']
+        beta = rng.integers(-20000, 20000, N)
+        sh = shift + (1 if c['unsigned'] else 0)
+        got = G.dense_add_layer_norm(a, w, bias, residual, gamma, beta, shift=sh, tok=tok, relu=c['relu'], eps_q0=1,
+                                     out_shift=c['out_shift'], ldr=c['ld'], ldo=c['ld'])
+        assert got is not None, 'the library refused a request inside the documented envelope'
+        d = oracle.dense(a, w, bias, shift=sh, tok=tok, relu=c['relu'], out_dtype='int8')
+        want = oracle.layer_norm(oracle.add(d, residual, out_dtype='int8'), gamma, beta, eps_q0=1, out_shift=c['out_shift'],
+                                 tok=tok)
+        np.testing.assert_array_equal(got, want, err_msg=str(c))
+
+
+def test_dense_add_layer_norm_envelope():
+    """Outside the single kernel's envelope the query says so (the plan then keeps two launches); the option turns it off."""
+    from aie4ml_b200 import lib as a4c
+
+    L = a4c.load()
+    ok = dict(M=1000, K=256, N=256, lda=256, ldw=256, ldr=256, ldo=256, shift=9, rounding=2, out_shift=4, eps_q0=1, gmax=300)
+
+    def q(**kw):
+        v = dict(ok, **kw)
+        return L.a4c_dense_add_layernorm_supported(v['M'], v['K'], v['N'], v['lda'], v['ldw'], v['ldr'], v['ldo'], v['shift'],
+                                                   v['rounding'], v['out_shift'], v['eps_q0'], v['gmax'])
+
+    assert q() == 0
+    for bad in (dict(N=128), dict(N=512), dict(K=8), dict(lda=264), dict(ldr=250), dict(rounding=4), dict(rounding=7),
+                dict(out_shift=14), dict(gmax=0), dict(gmax=20000), dict(eps_q0=(1 << 20) + 1)):
+        assert q(**bad) == -3, bad
+    a4c.check(L.a4c_set_option(a4c.OPT_DENSE_LN_PATH, 1), 'set_option')
+    try:
+        assert q() == -3
+    finally:
+        a4c.check(L.a4c_set_option(a4c.OPT_DENSE_LN_PATH, 0), 'set_option')
+
+
 def test_layer_norm_every_rounding_mode(rowop_path):
     import gpu_util as G
 

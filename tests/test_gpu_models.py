@@ -47,12 +47,21 @@ def test_cfg3_encoder_block(softmax, rounding):
     att = next(op for op in model.plan.ops if op['kind'] == 'attention')
     assert att['heads'] == 4 and att['head_strides'] == (64, 64, 64, 64)
     # the Q / K / V projections read the same tensor with the same requantisation: one Dense over 768 outputs
-    assert len(model.plan.ops) == 7 and model.plan.ops[0]['kind'] == 'dense' and model.plan.ops[0]['N'] == 768
+    assert model.plan.ops[0]['kind'] == 'dense' and model.plan.ops[0]['N'] == 768
+    # wo and ffn2 are 256 wide and feed residual Add -> LayerNorm: each of the two chains is one kernel, and neither the
+    # Dense output nor the sum has a buffer
+    assert kinds == ['dense', 'attention', 'dense_add_ln', 'dense', 'dense_add_ln']
+    assert not any(n.startswith(('qk', 'sm')) for n in model.plan.buffers)
+    for op in model.plan.ops:
+        if op['kind'] == 'dense_add_ln':
+            assert op['dense']['out'] not in model.plan.buffers and op['dense']['N'] == 256
+    two_step = _check(*W.encoder_cfg3(3, softmax=softmax, rounding=rounding), FusionPolicy={'dense_ln': False})
+    kinds2 = [op['kind'] for op in two_step.plan.ops]
+    # both residual Adds then ride inside their LayerNorm launches
+    assert len(kinds2) == 7 and kinds2.count('layer_norm') == 2 and kinds2.count('add') == 0
+    assert sum(1 for op in two_step.plan.ops if op.get('pre_addend')) == 2
     separate = _check(*W.encoder_cfg3(3, softmax=softmax, rounding=rounding), FusionPolicy={'parallel_dense': False})
-    assert len(separate.plan.ops) == 9 and separate.plan.ops[0]['N'] == 256
-    assert kinds.count('layer_norm') == 2 and not any(n.startswith(('qk', 'sm')) for n in model.plan.buffers)
-    # both residual Adds ride inside their LayerNorm launches
-    assert kinds.count('add') == 0 and sum(1 for op in model.plan.ops if op.get('pre_addend')) == 2
+    assert len(separate.plan.ops) == 7 and separate.plan.ops[0]['N'] == 256
     unfused = _check(*W.encoder_cfg3(3, softmax=softmax, rounding=rounding), FusionPolicy={'attention': False})
     kinds = [op['kind'] for op in unfused.plan.ops]
     assert kinds.count('matmul') == 8 and kinds.count('softmax') == 4 and kinds.count('attention') == 0
@@ -174,10 +183,15 @@ def test_report_times_every_launch_and_names_the_bound():
     rows = profile_plan(model.plan, iters=3)
     assert len(rows) == len(model.plan.launches) and all(r['ms'] > 0 and r['bytes'] > 0 for r in rows)
     kinds = {r['kind'] for r in rows}
-    assert {'dense', 'attention', 'layer_norm'} <= kinds
-    assert all(r['bound'] == 'hbm' for r in rows if r['kind'] == 'layer_norm')
+    assert {'dense', 'attention', 'dense_add_ln'} <= kinds
+    assert all(r['bound'] == 'hbm' for r in rows if r['kind'] == 'dense_add_ln')
     text = format_rows(rows)
     assert 'sum of launches' in text and 'attention' in text
+    model.context.aie_config['FusionPolicy'] = {'dense_ln': False}
+    model.plan = None
+    model.compile()
+    rows = profile_plan(model.plan, iters=3)
+    assert len(rows) == 7 and all(r['bound'] == 'hbm' for r in rows if r['kind'] == 'layer_norm')
 
 
 def test_model_with_a_dense_over_a_transposed_input_view():

@@ -39,12 +39,12 @@ def test_cfg3_encoder_block_as_a_qdq_graph(softmax):
     model = _run(graph, inputs, config)
     kinds = [op['kind'] for op in model.plan.ops]
     # same lowering as the programmatic graph: Q / K / V merged, the four heads fused into one attention launch,
-    # both residual Adds inside their LayerNorm launches
+    # wo / ffn2 with their residual Add and LayerNorm in one kernel each
     assert kinds.count('attention') == 1 and kinds.count('matmul') == 0 and kinds.count('softmax') == 0
     att = next(op for op in model.plan.ops if op['kind'] == 'attention')
     assert att['heads'] == 4 and att['rounding'] == 'conv_even'
     assert (att['sm_mode'] == 1 and att['exp_kq'] == 23) if softmax == 'exp' else (att['sm_mode'] == 0 and att['B'] == 200)
-    assert model.plan.ops[0]['N'] == 768 and kinds.count('add') == 0
+    assert model.plan.ops[0]['N'] == 768 and kinds.count('add') == 0 and kinds.count('dense_add_ln') == 2
 
 
 def test_layer_directives_must_name_nodes_of_the_graph():
