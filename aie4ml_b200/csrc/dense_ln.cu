@@ -17,11 +17,15 @@
 //               epilogue group; it is a role of its own so that waiting for a buffer never holds back operand loads
 //   warps 3-18  epilogue, two groups of eight warps on alternate tiles; the two warps of a TMEM lane quadrant split a
 //               row's 256 columns in halves.  Pass 1: TMEM load 32 columns at a time, requantise, add the residual,
-//               keep the 128 sums as packed bytes in 32 registers, accumulate sum and sum of squares with dp4a; the
-//               accumulator returns to the issuer; the two halves of a row exchange their partial sums through shared
-//               memory (a bounded mbarrier meeting).  Pass 2: normalise out of the registers on the FP32 pipe (the
-//               recipe of the row kernel, ln_math.cuh) and write the bytes over the residual bytes just read; a TMA
-//               store per warp (32 rows x 128 bytes) moves them out, and the buffer goes back to warp 2.
+//               keep the 128 sums as packed bytes (biased by +128) in 32 registers, accumulate sum and sum of squares
+//               with dp4a; the accumulator returns to the issuer and the residual buffer to warp 2 (so the next
+//               residual tile of the group loads while this one is normalised); the two halves of a row exchange
+//               their partial sums through shared memory (a bounded mbarrier meeting).  Pass 2: normalise out of the
+//               registers on the FP32 pipe (the recipe of the row kernel, ln_math.cuh); every thread stores the 128
+//               bytes of its half row (one 128-byte line) straight to global memory.
+// The integer pipe bounds pass 1, so the common rounding tokens requantise off it: (acc + c) >> s is the upper word of
+// one 64-bit multiply-add by 2^(32-s) (FMA pipe), and the saturation to 16 bits happens inside the instruction that
+// packs two values (cvt.pack.sat); the +128 bias rides in the addend.
 // Every wait is bounded: a wait that gives up records a code in the status word, the CTA stops issuing work, lets
 // what is in flight land, frees its TMEM and returns.
 #include <cuda.h>
@@ -57,9 +61,9 @@ constexpr int EPI_WARPS = GROUPS * GROUP_WARPS;
 constexpr int FIRST_EPI_WARP = 3;
 constexpr int NUM_THREADS = (FIRST_EPI_WARP + EPI_WARPS) * 32;   // 608
 constexpr int HALF_COLS = BN / 2;
-constexpr int DMODE_HALF_UP_FLOAT = 102;           // see dense_tc.cu
+constexpr int DMODE_WIDE = 1;                      // floor / ceil / half-up / half-down, shift 2..31: multiply-add + packing saturation
+constexpr int DMODE_WIDE_RELU = 2;                 // the same with ReLU
 constexpr int DMODE_GENERIC = -2;                  // any token, any shift: run-time rounding parameters
-constexpr int DENSE_MAGIC_BITS = 0x4B400000;
 
 struct Tail {
     int32_t bias[BN];
@@ -91,23 +95,59 @@ struct LArgs {
     // Dense requantisation
     int lo;                      // -128, or 0 with ReLU
     RoundParams rp;
-    int half, xhi, xlo;          // DMODE_HALF_UP_FLOAT
-    float fmul, fadd;
+    int wide_mul;                // DMODE_WIDE: 2^(32 - shift)
+    long long wide_add;          // (rounding constant + (128 << shift)) * 2^(32 - shift)
     uint32_t idesc;
+    int8_t* out; long long ldo;
     // LayerNorm
     int eps_q0, rounding, s_out, c0_gamma, gamma_absmax;
     float c0_out;
     int* status;
 };
 
+// DMODE_WIDE: round_shift(t, s) + 128 for the floor-type tokens = upper word of t * 2^(32-s) + (c + (128 << s)) * 2^(32-s),
+// exact for every int32 t (the 64-bit sum cannot overflow); t = acc + bias wraps like the reference's 32-bit accumulator.
+__device__ __forceinline__ int requant_wide(int t, const LArgs& g) {
+    long long d;
+    asm("mad.wide.s32 %0, %1, %2, %3;" : "=l"(d) : "r"(t), "r"(g.wide_mul), "l"(g.wide_add));
+    return (int)(d >> 32);
+}
+// two 32-bit values -> one register of two 16-bit lanes (a above b), each saturated to [-32768, 32767]
+__device__ __forceinline__ uint32_t pack_sat_s16x2(int a, int b) {
+    uint32_t d;
+    asm("cvt.pack.sat.s16.s32 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// Four accumulators -> four bytes of saturate_i8(dense + residual) + 128.  `rw` holds the four residual bytes.
 template <int DMODE>
-__device__ __forceinline__ int requant(int acc, int bias, const LArgs& g) {
-    if (DMODE == DMODE_HALF_UP_FLOAT) {
-        const int t = __viaddmin_s32(acc, bias, g.xhi);
-        const int u = __viaddmax_s32(t, g.half + DENSE_MAGIC_BITS, g.xlo + DENSE_MAGIC_BITS);
-        return __float_as_int(__fmaf_rd(__int_as_float(u), g.fmul, g.fadd));   // only the low byte is used
+__device__ __forceinline__ uint32_t dense_plus_residual(const uint32_t* a, int4 b, uint32_t rw, const LArgs& g) {
+    using namespace lnm;
+    uint32_t d01, d23;   // Dense outputs + 128 as 16-bit lanes in [0, 255]
+    if (DMODE == DMODE_GENERIC) {
+        const uint32_t d = pack4_i8(min(max(round_shift_i32((int)a[0] + b.x, g.rp), g.lo), 127),
+                                    min(max(round_shift_i32((int)a[1] + b.y, g.rp), g.lo), 127),
+                                    min(max(round_shift_i32((int)a[2] + b.z, g.rp), g.lo), 127),
+                                    min(max(round_shift_i32((int)a[3] + b.w, g.rp), g.lo), 127)) ^ 0x80808080u;
+        d01 = prmt(d, 0, 0x4140);
+        d23 = prmt(d, 0, 0x4342);
+    } else {
+        d01 = __vimin_s16x2_relu(pack_sat_s16x2(requant_wide((int)a[1] + b.y, g), requant_wide((int)a[0] + b.x, g)), 0x00FF00FFu);
+        d23 = __vimin_s16x2_relu(pack_sat_s16x2(requant_wide((int)a[3] + b.w, g), requant_wide((int)a[2] + b.z, g)), 0x00FF00FFu);
+        if (DMODE == DMODE_WIDE_RELU) {
+            d01 = __vimax3_s16x2(d01, 0x00800080u, 0x00800080u);
+            d23 = __vimax3_s16x2(d23, 0x00800080u, 0x00800080u);
+        }
     }
-    return min(max(round_shift_i32(acc + bias, g.rp), g.lo), 127);
+    // saturating Add in the biased domain (elementwise_add.cpp:30-33, SHIFT = 0): clamp(d + 128 + r, 0, 255) per lane
+    const uint32_t x01 = __viaddmin_s16x2_relu(d01, prmt(rw, 0, 0x9180), 0x00FF00FFu);
+    const uint32_t x23 = __viaddmin_s16x2_relu(d23, prmt(rw, 0, 0xB3A2), 0x00FF00FFu);
+    return prmt(x01, x23, 0x6420);
 }
 
 __device__ __forceinline__ uint4 lds128(uint32_t a) {
@@ -115,16 +155,13 @@ __device__ __forceinline__ uint4 lds128(uint32_t a) {
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
     return v;
 }
-__device__ __forceinline__ void sts128(uint32_t a, uint4 v) {
-    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" :: "r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
 
 // Pass 1 of the epilogue for one thread: its 128 accumulator columns -> requantise -> + residual (saturating) ->
-// packed bytes in xw; partial row sums in sx / sq.  The accumulator is released once its last columns are in registers.
+// packed bytes (biased by +128) in xw; partial sums of the biased bytes and of their squares in sx / sq.  The
+// accumulator is released once its last columns are in registers.
 template <int DMODE, bool HAS_BIAS>
 __device__ __forceinline__ void pass_one(uint32_t taddr, uint32_t my_res, uint32_t sw, const int32_t* my_bias, const LArgs& g,
                                          uint64_t* acc_empty, uint32_t (&xw)[HALF_COLS / 4], int& sx, int& sq) {
-    using namespace lnm;
     int sx0 = 0, sx1 = 0, sq0 = 0, sq1 = 0;
 #pragma unroll
     for (int c = 0; c < HALF_COLS / 32; ++c) {
@@ -143,13 +180,10 @@ __device__ __forceinline__ void pass_one(uint32_t taddr, uint32_t my_res, uint32
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const int4 b = HAS_BIAS ? *reinterpret_cast<const int4*>(my_bias + piece * 16 + q * 4) : make_int4(0, 0, 0, 0);
-                const uint32_t* a = ra + j * 16 + q * 4;
-                const uint32_t d = pack4_i8(requant<DMODE>((int)a[0], b.x, g), requant<DMODE>((int)a[1], b.y, g),
-                                            requant<DMODE>((int)a[2], b.z, g), requant<DMODE>((int)a[3], b.w, g));
-                const uint32_t x = sat_add_i8x4(d, rw[q]);
+                const uint32_t x = dense_plus_residual<DMODE>(ra + j * 16 + q * 4, b, rw[q], g);
                 xw[piece * 4 + q] = x;
-                if (q & 1) { sx1 = dp4a_ss(x, 0x01010101u, sx1); sq1 = dp4a_ss(x, x, sq1); }
-                else { sx0 = dp4a_ss(x, 0x01010101u, sx0); sq0 = dp4a_ss(x, x, sq0); }
+                if (q & 1) { sx1 = dp4a_uu(x, 0x01010101u, sx1); sq1 = dp4a_uu(x, x, sq1); }
+                else { sx0 = dp4a_uu(x, 0x01010101u, sx0); sq0 = dp4a_uu(x, x, sq0); }
             }
         }
     }
@@ -157,12 +191,12 @@ __device__ __forceinline__ void pass_one(uint32_t taddr, uint32_t my_res, uint32
     sq = sq0 + sq1;
 }
 
-// Pass 2: normalise the packed bytes of xw (layer_norm.cpp:44-121 on the FP32 pipe, as the row kernel does) and write
-// them over the residual bytes of the same row.  CLAMP: fscale may leave int16 (inv_std * max|gamma| / 128 > 32767), a
+// Pass 2: normalise the packed (biased) bytes of xw (layer_norm.cpp:44-121 on the FP32 pipe, as the row kernel does) and
+// store them: `orow` is this thread's 128-byte half row in global memory, or null for a row past the end.  CLAMP: fscale may leave int16 (inv_std * max|gamma| / 128 > 32767), a
 // warp-uniform rarity that gets its own copy of the loop so that the common one carries no min / max per value.
 template <int FS, bool CLAMP>
-__device__ __forceinline__ void pass_two(const uint32_t (&xw)[HALF_COLS / 4], uint32_t my_res, uint32_t sw, uint32_t s_gam,
-                                         uint32_t s_bet, int inv_std, float vdc, float c0g, float out_mul, int c0_gamma) {
+__device__ __forceinline__ void pass_two(const uint32_t (&xw)[HALF_COLS / 4], uint8_t* orow, uint32_t s_gam, uint32_t s_bet,
+                                         int inv_std, float vdc, float c0g, float out_mul, int c0_gamma) {
     using namespace lnm;
     constexpr bool RN = FS == 0;
     const float inv_f = (float)inv_std;
@@ -196,7 +230,7 @@ __device__ __forceinline__ void pass_two(const uint32_t (&xw)[HALF_COLS / 4], ui
 #pragma unroll
                 for (int k = 0; k < 4; ++k) F[k] = fminf(fmaxf(F[k], MAGIC - 32768.0f), MAGIC + 32767.0f);
             }
-            const uint32_t xb = xw[piece * 4 + w] ^ 0x80808080u;
+            const uint32_t xb = xw[piece * 4 + w];
             const float xf[4] = {byte_to_f23<0>(xb), byte_to_f23<1>(xb), byte_to_f23<2>(xb), byte_to_f23<3>(xb)};
             int o[4];
 #pragma unroll
@@ -214,7 +248,7 @@ __device__ __forceinline__ void pass_two(const uint32_t (&xw)[HALF_COLS / 4], ui
             asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(w4) : "r"(o[1]), "r"(o[0]), "r"(hi2));
             ow[w] = w4 ^ 0x80808080u;   // un-biased
         }
-        sts128(my_res + (((uint32_t)piece ^ sw) << 4), make_uint4(ow[0], ow[1], ow[2], ow[3]));
+        if (orow != nullptr) *reinterpret_cast<uint4*>(orow + piece * 16) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
 }
 
@@ -222,7 +256,7 @@ __device__ __forceinline__ void pass_two(const uint32_t (&xw)[HALF_COLS / 4], ui
 template <int DMODE, int FS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 dense_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                const __grid_constant__ CUtensorMap tmap_r, const __grid_constant__ CUtensorMap tmap_o, LArgs g) {
+                const __grid_constant__ CUtensorMap tmap_r, LArgs g) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* res = smem + OPERAND_BYTES;                         // 1024-byte aligned: whole swizzle atoms
@@ -373,7 +407,6 @@ dense_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                              g.rounding == A4C_RND_NEGATIVE_INF;
         const uint32_t my_res = smem_u32(res) + (uint32_t)(grp * RES_BYTES + hf * (RES_BYTES / 2) + r_in_tile * 128);
         const uint32_t sw = (uint32_t)(lane & 7);   // 128-byte swizzle: 16-byte piece p of row r sits at piece p ^ (r & 7)
-        const uint32_t warp_patch = smem_u32(res) + (uint32_t)(grp * RES_BYTES + hf * (RES_BYTES / 2) + quad * 32 * 128);
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(grp * BN + hf * HALF_COLS);
         const uint32_t s_gam = smem_u32(tail->gam) + (uint32_t)(hf * HALF_COLS * 4);
         const uint32_t s_bet = smem_u32(tail->bet) + (uint32_t)(hf * HALF_COLS * 4);
@@ -391,14 +424,20 @@ dense_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             int sx, sq;
             if (has_bias) pass_one<DMODE, true>(taddr, my_res, sw, my_bias, g, &tail->tmem_empty[grp], xw, sx, sq);
             else pass_one<DMODE, false>(taddr, my_res, sw, my_bias, g, &tail->tmem_empty[grp], xw, sx, sq);
+            // the residual bytes are consumed: the buffer goes back to warp 2, which loads the group's next tile into it
+            // while this one is normalised
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tail->res_empty[grp]);   // one of the group's eight warps
             // ---- the two halves of a row meet ----
             tail->xch[grp][ph][hf][r_in_tile] = make_int2(sx, sq);
             __syncwarp();
             if (lane == 0) mbar_arrive(pair_bar);
             if (!mbar_wait_fast(pair_bar, ph, abort_flag, g.status, 178)) break;
             const int2 other = tail->xch[grp][ph][hf ^ 1][r_in_tile];
-            const int sum_x = sx + other.x;
-            const int sum_sq = sq + other.y;
+            // sums of the biased bytes b = x + 128 over the 256 columns -> sums of x
+            const int sum_b = sx + other.x;
+            const int sum_x = sum_b - 128 * BN;
+            const int sum_sq = sq + other.y - 256 * sum_b + 128 * 128 * BN;
             // layer_norm.cpp:23-31 with 256 columns
             const int mu = (sum_x + (BN >> 1)) >> 8;
             const int centered = (int)((uint32_t)sum_sq - 2u * (uint32_t)mu * (uint32_t)sum_x + (uint32_t)BN * (uint32_t)mu * (uint32_t)mu);
@@ -406,25 +445,14 @@ dense_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             var = max(var, 0) + g.eps_q0;
             const int inv_std = inv_std_q15(var, g.rounding, nearest);
             const bool need_clamp = __any_sync(0xffffffffu, inv_std > clamp_threshold);
-            const float vdc = 8388608.0f + 128.0f + (float)mu;   // (2^23 + (x ^ 0x80)) - vdc = x - mu
+            const float vdc = 8388608.0f + 128.0f + (float)mu;   // (2^23 + b) - vdc = x - mu
 
-            // ---- pass 2: normalise out of the registers, bytes over the residual bytes ----
-            if (need_clamp) pass_two<FS, true>(xw, my_res, sw, s_gam, s_bet, inv_std, vdc, c0g, out_mul, g.c0_gamma);
-            else pass_two<FS, false>(xw, my_res, sw, s_gam, s_bet, inv_std, vdc, c0g, out_mul, g.c0_gamma);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> TMA read
-            __syncwarp();
-            if (lane == 0) {
-                const int m0 = ((int)blockIdx.x + i * (int)gridDim.x) * BM;
-                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
-                             :: "l"(&tmap_o), "r"(hf * HALF_COLS), "r"(m0 + quad * 32), "r"(warp_patch) : "memory");
-                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the store has read the patch
-                mbar_arrive(&tail->res_empty[grp]);                              // one of the group's eight warps
-            }
-            __syncwarp();
+            // ---- pass 2: normalise out of the registers, one 128-byte line per thread straight to global memory ----
+            const long long row = (long long)((int)blockIdx.x + i * (int)gridDim.x) * BM + r_in_tile;
+            uint8_t* orow = row < g.M ? reinterpret_cast<uint8_t*>(g.out) + row * g.ldo + hf * HALF_COLS : nullptr;
+            if (need_clamp) pass_two<FS, true>(xw, orow, s_gam, s_bet, inv_std, vdc, c0g, out_mul, g.c0_gamma);
+            else pass_two<FS, false>(xw, orow, s_gam, s_bet, inv_std, vdc, c0g, out_mul, g.c0_gamma);
         }
-        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // stores complete before the CTA retires
-        __syncwarp();
     }
 
     // ---------------- teardown ----------------
@@ -471,12 +499,12 @@ bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols
 }
 
 template <int DMODE, int FS>
-cudaError_t launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mr, const CUtensorMap& mo,
-                       const LArgs& g, int grid, cudaStream_t s) {
+cudaError_t launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mr, const LArgs& g, int grid,
+                       cudaStream_t s) {
     static tc::SmemOptIn opt_in;
     const cudaError_t e = opt_in.ensure(dense_ln_kernel<DMODE, FS>, SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    dense_ln_kernel<DMODE, FS><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(ma, mb, mr, mo, g);
+    dense_ln_kernel<DMODE, FS><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(ma, mb, mr, g);
     return cudaGetLastError();
 }
 
@@ -510,23 +538,22 @@ int a4c_launch_dense_ln(const void* A, long long lda, int a_unsigned, const void
     if (sup != A4C_OK) return sup;
     if ((((uintptr_t)A | (uintptr_t)Wt | (uintptr_t)residual | (uintptr_t)out) & 15u) != 0) return A4C_ERR_ALIGNMENT;
     if (status_word == nullptr || gamma == nullptr || beta == nullptr) return A4C_ERR_INVALID_ARG;
-    CUtensorMap ma, mb, mr, mo;
+    CUtensorMap ma, mb, mr;
     if (!make_map(&ma, A, M, K, lda, BM, CU_TENSOR_MAP_L2_PROMOTION_L2_256B) ||
         !make_map(&mb, Wt, N, K, ldw, BN, CU_TENSOR_MAP_L2_PROMOTION_L2_256B) ||
-        !make_map(&mr, residual, M, N, ldr, BM, CU_TENSOR_MAP_L2_PROMOTION_L2_256B) ||
-        !make_map(&mo, out, M, N, ldo, 32, CU_TENSOR_MAP_L2_PROMOTION_NONE))
+        !make_map(&mr, residual, M, N, ldr, BM, CU_TENSOR_MAP_L2_PROMOTION_L2_256B))
         return A4C_ERR_CUDA;
     LArgs g;
     g.bias = bias; g.gamma = gamma; g.beta = beta; g.M = M; g.K = K;
     g.num_m_tiles = (int)((M + BM - 1) / BM);
     g.lo = relu ? 0 : -128;
     g.rp = make_round_params(shift, rounding);
-    const bool fast_dense = rounding == A4C_RND_POSITIVE_INF && shift >= 1 && shift <= 13;
-    g.half = fast_dense ? (1 << (shift - 1)) : 0;
-    g.xhi = fast_dense ? 127 * (1 << shift) : 0;
-    g.xlo = fast_dense ? g.lo * (1 << shift) + g.half : 0;
-    g.fmul = fast_dense ? 1.0f / (float)(1 << shift) : 0.0f;
-    g.fadd = 12582912.0f - 12582912.0f * g.fmul;
+    // floor-type tokens with a shift of 2..31: (t + c) >> s as the upper word of a 64-bit multiply-add
+    const bool wide = shift >= 2 && (rounding == A4C_RND_FLOOR || rounding == A4C_RND_CEIL ||
+                                     rounding == A4C_RND_POSITIVE_INF || rounding == A4C_RND_NEGATIVE_INF);
+    g.wide_mul = wide ? (int)(1u << (32 - shift)) : 0;
+    g.wide_add = wide ? ((long long)g.rp.c0 + (128ll << shift)) << (32 - shift) : 0;
+    g.out = out; g.ldo = ldo;
     g.idesc = make_idesc(BM, BN, a_unsigned != 0);
     g.eps_q0 = eps_q0; g.rounding = rounding; g.s_out = 15 - out_shift; g.gamma_absmax = gamma_absmax;
     g.c0_gamma = 0; g.c0_out = 0.0f;
@@ -551,10 +578,12 @@ int a4c_launch_dense_ln(const void* A, long long lda, int a_unsigned, const void
     const int grid = g.num_m_tiles < sms ? g.num_m_tiles : sms;
     const int fs = rounding == A4C_RND_CONV_EVEN ? 0 : (gamma_absmax <= 511 ? 1 : 2);
     cudaError_t err;
-    if (fs == 0) err = launch_one<DMODE_GENERIC, 0>(ma, mb, mr, mo, g, grid, stream);
-    else if (fast_dense) err = fs == 1 ? launch_one<DMODE_HALF_UP_FLOAT, 1>(ma, mb, mr, mo, g, grid, stream)
-                                       : launch_one<DMODE_HALF_UP_FLOAT, 2>(ma, mb, mr, mo, g, grid, stream);
-    else err = fs == 1 ? launch_one<DMODE_GENERIC, 1>(ma, mb, mr, mo, g, grid, stream)
-                       : launch_one<DMODE_GENERIC, 2>(ma, mb, mr, mo, g, grid, stream);
+    if (fs == 0) err = launch_one<DMODE_GENERIC, 0>(ma, mb, mr, g, grid, stream);
+    else if (wide && !relu) err = fs == 1 ? launch_one<DMODE_WIDE, 1>(ma, mb, mr, g, grid, stream)
+                                          : launch_one<DMODE_WIDE, 2>(ma, mb, mr, g, grid, stream);
+    else if (wide) err = fs == 1 ? launch_one<DMODE_WIDE_RELU, 1>(ma, mb, mr, g, grid, stream)
+                                 : launch_one<DMODE_WIDE_RELU, 2>(ma, mb, mr, g, grid, stream);
+    else err = fs == 1 ? launch_one<DMODE_GENERIC, 1>(ma, mb, mr, g, grid, stream)
+                       : launch_one<DMODE_GENERIC, 2>(ma, mb, mr, g, grid, stream);
     return err == cudaSuccess ? A4C_OK : A4C_ERR_CUDA;
 }
