@@ -112,12 +112,6 @@ __device__ __forceinline__ int requant_wide(int t, const LArgs& g) {
     asm("mad.wide.s32 %0, %1, %2, %3;" : "=l"(d) : "r"(t), "r"(g.wide_mul), "l"(g.wide_add));
     return (int)(d >> 32);
 }
-// two 32-bit values -> one register of two 16-bit lanes (a above b), each saturated to [-32768, 32767]
-__device__ __forceinline__ uint32_t pack_sat_s16x2(int a, int b) {
-    uint32_t d;
-    asm("cvt.pack.sat.s16.s32 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
 __device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c) {
     int d;
     asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
@@ -241,12 +235,7 @@ __device__ __forceinline__ void pass_two(const uint32_t (&xw)[HALF_COLS / 4], ui
                 const float r = RN ? __fmaf_rn(acc, out_mul, 0.0f) : __fmaf_rd(acc, out_mul, 0.0f);
                 o[k] = __float_as_int(r);                                          // round(.) + 128 as a (signed) integer
             }
-            // clamp(., 0, 255) and pack in two instructions: saturating conversion of two values into the low bytes,
-            // the earlier pair carried into the upper half
-            uint32_t hi2, w4;
-            asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(hi2) : "r"(o[3]), "r"(o[2]), "r"(0));
-            asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(w4) : "r"(o[1]), "r"(o[0]), "r"(hi2));
-            ow[w] = w4 ^ 0x80808080u;   // un-biased
+            ow[w] = pack_sat_u8x4(o[0], o[1], o[2], o[3]) ^ 0x80808080u;   // clamp(., 0, 255), pack, un-bias
         }
         if (orow != nullptr) *reinterpret_cast<uint4*>(orow + piece * 16) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }

@@ -83,4 +83,18 @@ __device__ __forceinline__ uint32_t sat_add_i8x4(uint32_t x, uint32_t a) {
     return prmt(lo, hi, 0x6420);
 }
 
+// two 32-bit values -> one register of two 16-bit lanes (a above b), each saturated to [-32768, 32767]
+__device__ __forceinline__ uint32_t pack_sat_s16x2(int a, int b) {
+    uint32_t d;
+    asm("cvt.pack.sat.s16.s32 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+// four 32-bit values -> four bytes (o0 lowest), each saturated to [0, 255]: clamp and pack in two instructions
+__device__ __forceinline__ uint32_t pack_sat_u8x4(int o0, int o1, int o2, int o3) {
+    uint32_t hi, w;
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(o3), "r"(o2), "r"(0));
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(o1), "r"(o0), "r"(hi));
+    return w;
+}
+
 }  // namespace lnm

@@ -19,6 +19,8 @@
 // Modes or parameters outside those proofs (symmetric rounding, conv_odd, |gamma| > 16383, shifts < 2,
 // int16 softmax output, negative HCCS scores, inv_shift > 22, rows longer than 2048 / 1024) take the generic
 // integer kernels of rowops.cu.
+#include <type_traits>
+
 #include "a4c_common.cuh"
 #include "a4c_kernels.h"
 #include "ln_math.cuh"
@@ -279,66 +281,76 @@ __global__ void __launch_bounds__(kThreads) layernorm_fast_kernel(LnFastArgs a) 
         const float vdc = 8388608.0f + 128.0f + (float)mu;  // (2^23 + (x ^ 0x80)) - vdc = x - mu
         uint8_t* orow = reinterpret_cast<uint8_t*>(a.out) + row * a.ldo + gl * 16;
 
+        // fscale can leave int16 only for a rare inv_std (warp-uniform test above): the loop exists twice, and the common
+        // copy carries no min / max per value (as a run-time condition the compiler predicates them: two more
+        // instructions per value on the integer pipe)
+        auto normalise = [&](auto clamp_tag) {
+            constexpr bool CLAMP = decltype(clamp_tag)::value;
 #pragma unroll
-        for (int j = 0; j < NCH; ++j) {
-            if (!(row_ok && (j * G + gl) < a.geom.nchunks)) continue;
-            const uint32_t xw[4] = {xv[j].x ^ 0x80808080u, xv[j].y ^ 0x80808080u, xv[j].z ^ 0x80808080u,
-                                    xv[j].w ^ 0x80808080u};
-            uint32_t aw[4] = {0, 0, 0, 0};
-            if (HAS_ADD) { aw[0] = av[j].x; aw[1] = av[j].y; aw[2] = av[j].z; aw[3] = av[j].w; }
-            uint32_t ow[4];
+            for (int j = 0; j < NCH; ++j) {
+                if (!(row_ok && (j * G + gl) < a.geom.nchunks)) continue;
+                const uint32_t xw[4] = {xv[j].x ^ 0x80808080u, xv[j].y ^ 0x80808080u, xv[j].z ^ 0x80808080u,
+                                        xv[j].w ^ 0x80808080u};
+                uint32_t aw[4] = {0, 0, 0, 0};
+                if (HAS_ADD) { aw[0] = av[j].x; aw[1] = av[j].y; aw[2] = av[j].z; aw[3] = av[j].w; }
+                uint32_t ow[4];
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                const uint32_t poff = lane_param + (uint32_t)((j * 4 + w) * 32 * 16);
-                const float4 bq = lds128f(s_bet + poff);
-                const float bet[4] = {bq.x, bq.y, bq.z, bq.w};
-                float F[4];
-                if (FS == 0) {
-                    const float4 gq = lds128f(s_gam + poff);
-                    F[0] = __fmaf_rn(inv_f, gq.x, MAGIC); F[1] = __fmaf_rn(inv_f, gq.y, MAGIC);
-                    F[2] = __fmaf_rn(inv_f, gq.z, MAGIC); F[3] = __fmaf_rn(inv_f, gq.w, MAGIC);
-                } else if (FS == 1) {
-                    const float4 gq = lds128f(s_gam + poff);
-                    // inv_std * gamma + c0 < 2^24 is exact; floor(. / 128) by a round-down FMA
-                    F[0] = __fmaf_rd(__fmaf_rn(inv_f, gq.x, c0g), 0.0078125f, MAGIC);
-                    F[1] = __fmaf_rd(__fmaf_rn(inv_f, gq.y, c0g), 0.0078125f, MAGIC);
-                    F[2] = __fmaf_rd(__fmaf_rn(inv_f, gq.z, c0g), 0.0078125f, MAGIC);
-                    F[3] = __fmaf_rd(__fmaf_rn(inv_f, gq.w, c0g), 0.0078125f, MAGIC);
-                } else {
-                    const uint4 gq = lds128(s_gam + poff);
-                    F[0] = __uint_as_float((uint32_t)((inv_std * (int)gq.x + a.c0_gamma) >> 7) + MAGIC_BITS);
-                    F[1] = __uint_as_float((uint32_t)((inv_std * (int)gq.y + a.c0_gamma) >> 7) + MAGIC_BITS);
-                    F[2] = __uint_as_float((uint32_t)((inv_std * (int)gq.z + a.c0_gamma) >> 7) + MAGIC_BITS);
-                    F[3] = __uint_as_float((uint32_t)((inv_std * (int)gq.w + a.c0_gamma) >> 7) + MAGIC_BITS);
-                }
-                if (need_clamp) {
+                for (int w = 0; w < 4; ++w) {
+                    const uint32_t poff = lane_param + (uint32_t)((j * 4 + w) * 32 * 16);
+                    const float4 bq = lds128f(s_bet + poff);
+                    const float bet[4] = {bq.x, bq.y, bq.z, bq.w};
+                    float F[4];
+                    if (FS == 0) {
+                        const float4 gq = lds128f(s_gam + poff);
+                        F[0] = __fmaf_rn(inv_f, gq.x, MAGIC); F[1] = __fmaf_rn(inv_f, gq.y, MAGIC);
+                        F[2] = __fmaf_rn(inv_f, gq.z, MAGIC); F[3] = __fmaf_rn(inv_f, gq.w, MAGIC);
+                    } else if (FS == 1) {
+                        const float4 gq = lds128f(s_gam + poff);
+                        // inv_std * gamma + c0 < 2^24 is exact; floor(. / 128) by a round-down FMA
+                        F[0] = __fmaf_rd(__fmaf_rn(inv_f, gq.x, c0g), 0.0078125f, MAGIC);
+                        F[1] = __fmaf_rd(__fmaf_rn(inv_f, gq.y, c0g), 0.0078125f, MAGIC);
+                        F[2] = __fmaf_rd(__fmaf_rn(inv_f, gq.z, c0g), 0.0078125f, MAGIC);
+                        F[3] = __fmaf_rd(__fmaf_rn(inv_f, gq.w, c0g), 0.0078125f, MAGIC);
+                    } else {
+                        const uint4 gq = lds128(s_gam + poff);
+                        F[0] = __uint_as_float((uint32_t)((inv_std * (int)gq.x + a.c0_gamma) >> 7) + MAGIC_BITS);
+                        F[1] = __uint_as_float((uint32_t)((inv_std * (int)gq.y + a.c0_gamma) >> 7) + MAGIC_BITS);
+                        F[2] = __uint_as_float((uint32_t)((inv_std * (int)gq.z + a.c0_gamma) >> 7) + MAGIC_BITS);
+                        F[3] = __uint_as_float((uint32_t)((inv_std * (int)gq.w + a.c0_gamma) >> 7) + MAGIC_BITS);
+                    }
+                    if (CLAMP) {
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) F[k] = fminf(fmaxf(F[k], MAGIC - 32768.0f), MAGIC + 32767.0f);
-                }
-                const float xf[4] = {byte_to_f23<0>(xw[w]), byte_to_f23<1>(xw[w]), byte_to_f23<2>(xw[w]),
-                                     byte_to_f23<3>(xw[w])};
-                int o[4];
+                        for (int k = 0; k < 4; ++k) F[k] = fminf(fmaxf(F[k], MAGIC - 32768.0f), MAGIC + 32767.0f);
+                    }
+                    const float xf[4] = {byte_to_f23<0>(xw[w]), byte_to_f23<1>(xw[w]), byte_to_f23<2>(xw[w]),
+                                         byte_to_f23<3>(xw[w])};
+                    int o[4];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const float vd = xf[k] - vdc;                                      // x - mu, exact
-                    const float fs = __fmaf_rn(F[k], TWO_M64, -MAGIC * TWO_M64);       // fscale * 2^-64, exact
-                    const float acc = __fmaf_rn(vd, fs, bet[k]);                       // (vd*fscale + beta + c) * 2^-64
-                    const float r = RN ? __fmaf_rn(acc, out_mul, 0.0f) : __fmaf_rd(acc, out_mul, 0.0f);
-                    o[k] = __vimin_s32_relu(__float_as_int(r), 255);                   // clamp(round(.) + 128, 0, 255)
+                    for (int k = 0; k < 4; ++k) {
+                        const float vd = xf[k] - vdc;                                      // x - mu, exact
+                        const float fs = __fmaf_rn(F[k], TWO_M64, -MAGIC * TWO_M64);       // fscale * 2^-64, exact
+                        const float acc = __fmaf_rn(vd, fs, bet[k]);                       // (vd*fscale + beta + c) * 2^-64
+                        const float r = RN ? __fmaf_rn(acc, out_mul, 0.0f) : __fmaf_rd(acc, out_mul, 0.0f);
+                        o[k] = __float_as_int(r);                                          // round(.) + 128 as a signed integer
+                    }
+                    if (HAS_ADD) {
+                        // clamp(., 0, 255) on two outputs per register (16-bit lanes: the packing saturates to 16 bits, one
+                        // min + relu finishes the clamp), then the fused saturating Add (elementwise_add.cpp:30-33,
+                        // SHIFT = 0): sign-extended addend pairs, packed add + min(., 255) + relu
+                        uint32_t p01 = __vimin_s16x2_relu(pack_sat_s16x2(o[1], o[0]), 0x00FF00FFu);
+                        uint32_t p23 = __vimin_s16x2_relu(pack_sat_s16x2(o[3], o[2]), 0x00FF00FFu);
+                        p01 = __viaddmin_s16x2_relu(p01, prmt(aw[w], 0, 0x9180), 0x00FF00FFu);
+                        p23 = __viaddmin_s16x2_relu(p23, prmt(aw[w], 0, 0xB3A2), 0x00FF00FFu);
+                        ow[w] = prmt(p01, p23, 0x6420) ^ 0x80808080u;  // low bytes of the four lanes, un-biased
+                    } else {
+                        ow[w] = pack_sat_u8x4(o[0], o[1], o[2], o[3]) ^ 0x80808080u;   // clamp(., 0, 255), pack, un-bias
+                    }
                 }
-                // two biased outputs per register as s16x2 lanes
-                uint32_t p01 = prmt((uint32_t)o[0], (uint32_t)o[1], 0x5410);
-                uint32_t p23 = prmt((uint32_t)o[2], (uint32_t)o[3], 0x5410);
-                if (HAS_ADD) {
-                    // fused saturating Add (elementwise_add.cpp:30-33, SHIFT = 0): sign-extended addend pairs,
-                    // packed add + min(., 255) + relu, two elements per instruction
-                    p01 = __viaddmin_s16x2_relu(p01, prmt(aw[w], 0, 0x9180), 0x00FF00FFu);
-                    p23 = __viaddmin_s16x2_relu(p23, prmt(aw[w], 0, 0xB3A2), 0x00FF00FFu);
-                }
-                ow[w] = prmt(p01, p23, 0x6420) ^ 0x80808080u;  // low bytes of the four lanes, un-biased
+                stg16(orow + j * G * 16, make_uint4(ow[0], ow[1], ow[2], ow[3]));
             }
-            stg16(orow + j * G * 16, make_uint4(ow[0], ow[1], ow[2], ow[3]));
-        }
+        };
+        if (need_clamp) normalise(std::true_type{});
+        else normalise(std::false_type{});
     }
 }
 
