@@ -6,7 +6,7 @@ simulator logs into per-kernel cycle counts; here every launch of the plan is ti
 events (each launch replayed ``iters`` times back to back after a warm-up), and the plan dump
 (``cuda_pipeline.json`` + ``params.npz``, ``CudaModel.dump``) can be read back with ``load_plan``.
 
-    python -m aie4ml_b200.report --workload cfg3_exp [--batch N] [--iters 20] [--json]
+    python -m aie4ml_b200.report --workload cfg3_exp [--batch N] [--iters 20] [--json] [--no-dense-ln]
 """
 
 from __future__ import annotations
@@ -124,26 +124,39 @@ def main(argv=None) -> int:
     ap.add_argument('--n', type=int, default=4096)
     ap.add_argument('--iters', type=int, default=20)
     ap.add_argument('--json', action='store_true')
+    ap.add_argument('--no-dense-ln', action='store_true',
+                    help='keep Dense and Add + LayerNorm as two launches (the single kernel for 256-wide layers is the default)')
     a = ap.parse_args(argv)
     from . import from_graph
+    from . import lib as _lib
     from . import workloads as W
+
+    if a.no_dense_ln:
+        _lib.check(_lib.load().a4c_set_option(_lib.OPT_DENSE_LN_PATH, 1), 'a4c_set_option')
 
     name = a.workload
     if name == 'dense':
-        b, _ = W.dense_cfg2(a.m, a.k, a.n)
+        b, inputs = W.dense_cfg2(a.m, a.k, a.n)
     elif name == 'cfg1':
-        b, _ = W.mlp_cfg1(a.batch or 1024)
+        b, inputs = W.mlp_cfg1(a.batch or 1024)
     elif name in ('cfg3_exp', 'cfg3_hccs'):
-        b, _ = W.encoder_cfg3(a.batch or 4096, softmax=name.split('_')[1])
+        b, inputs = W.encoder_cfg3(a.batch or 4096, softmax=name.split('_')[1])
     elif name in ('cfg4_ln', 'cfg4_sm_exp', 'cfg4_sm_hccs'):
-        b, _ = W.rowops_cfg4(a.batch or (1 << 20), 1024, {'cfg4_ln': 'layer_norm', 'cfg4_sm_exp': 'softmax_exp',
+        b, inputs = W.rowops_cfg4(a.batch or (1 << 20), 1024, {'cfg4_ln': 'layer_norm', 'cfg4_sm_exp': 'softmax_exp',
                                                            'cfg4_sm_hccs': 'softmax_hccs'}[name])
     elif name == 'cfg5':
-        b, _ = W.wide_mlp_cfg5(a.batch or 262144)
+        b, inputs = W.wide_mlp_cfg5(a.batch or 262144)
     else:
         ap.error(f'unknown workload {name!r}')
     model = from_graph(b)
     model.compile()
+    # the workload's seeded inputs, then one whole step: every launch is then timed on the data it sees in a real run
+    # (on zero-filled buffers every LayerNorm row has zero variance and takes the kernel's rare exact-reciprocal path)
+    import torch
+
+    for n in model.plan.graph.input_tensor_names:
+        model.plan.tensor_of(n).copy_(torch.from_numpy(np.ascontiguousarray(inputs[n])).to(model.plan.device))
+    model.plan.run(use_graph=False)
     rows = profile_plan(model.plan, a.iters)
     print(json.dumps(rows) if a.json else format_rows(rows))
     return 0

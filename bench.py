@@ -596,6 +596,8 @@ def main():
     ap.add_argument('--algo', type=int, default=0, help='dense kernel: 0 auto, 1 simt, 2 tcgen05')
     ap.add_argument('--dense-panel-mib', type=int, default=None,
                     help='tcgen05 Dense: MiB of weights per column panel of the tile order (library default 32; 0 = one panel)')
+    ap.add_argument('--no-dense-ln', action='store_true',
+                    help='keep Dense and Add + LayerNorm as two launches (the single kernel for 256-wide layers is the default)')
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
 
@@ -627,6 +629,10 @@ def main():
         from aie4ml_b200 import lib as a4c
 
         a4c.check(a4c.load().a4c_set_option(a4c.OPT_DENSE_PANEL_MIB, args.dense_panel_mib), 'a4c_set_option')
+    if args.no_dense_ln:
+        from aie4ml_b200 import lib as a4c
+
+        a4c.check(a4c.load().a4c_set_option(a4c.OPT_DENSE_LN_PATH, 1), 'a4c_set_option')
 
     wl = build_workload(args.workload, args)
     model = from_graph(wl['builder'])
