@@ -59,6 +59,7 @@ struct Tc2Args {
     long long M;
     int K, N;
     int num_m_tiles, num_n_tiles;   // in 256 x 256 tiles
+    int panel;                      // column tiles per panel of the tile order (>= num_n_tiles: one panel)
     int shift, lo, hi;
     uint32_t mask, c0;
     uint32_t idesc;
@@ -101,6 +102,19 @@ __device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t adesc, ui
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                  :: "r"(bar_cluster_addr) : "memory");
+}
+
+// Tile order as in dense_tc.cu: panels of g.panel column tiles (at most 32 MiB of weights, which stay in the L2 while
+// the row tiles stream past); inside a panel the column tile runs fastest.
+__device__ __forceinline__ void tile_coords(int tile, const Tc2Args& g, int& mt, int& nt) {
+    const int nnt = g.num_n_tiles;
+    if (g.panel >= nnt) { mt = tile / nnt; nt = tile - mt * nnt; return; }
+    const int per_panel = g.num_m_tiles * g.panel;
+    const int full = nnt / g.panel;
+    int pz = tile / per_panel, rem = tile - pz * per_panel, width = g.panel;
+    if (pz >= full) { pz = full; rem = tile - full * per_panel; width = nnt - full * g.panel; }
+    mt = rem / width;
+    nt = pz * g.panel + (rem - mt * width);
 }
 
 template <int MODE>
@@ -150,8 +164,10 @@ dense_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             uint32_t phase = 0;
             bool ok = true;
             for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
-                const int m0 = (tile / g.num_n_tiles) * BM + (int)rank * BM_CTA;
-                const int n0 = (tile % g.num_n_tiles) * BN + (int)rank * BN_CTA;
+                int mt, nt;
+                tile_coords(tile, g, mt, nt);
+                const int m0 = mt * BM + (int)rank * BM_CTA;
+                const int n0 = nt * BN + (int)rank * BN_CTA;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(&tail->empty[stage], phase ^ 1u, abort_flag, g.status, 121);
                     if (!ok) break;
@@ -207,8 +223,10 @@ dense_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         uint32_t acc_phase = 0;
         bool ok = true;
         for (int tile = pair; tile < num_tiles; tile += num_pairs) {
-            const int m0 = (tile / g.num_n_tiles) * BM + (int)rank * BM_CTA;
-            const int n0 = (tile % g.num_n_tiles) * BN;
+            int mt, nt;
+            tile_coords(tile, g, mt, nt);
+            const int m0 = mt * BM + (int)rank * BM_CTA;
+            const int n0 = nt * BN;
             for (int i = et; i < BN; i += EPI_THREADS) {
                 const int n = n0 + i;
                 tail->bias[acc][i] = (g.bias != nullptr && n < g.N) ? __ldg(g.bias + n) : 0;
@@ -326,6 +344,12 @@ int a4c_launch_dense_tc2(const void* A, long long lda, const void* Wt, long long
     g.mask = rp.mask; g.c0 = rp.c0;
     g.idesc = make_idesc(BM, BN, a_unsigned != 0);
     g.status = status_word;
+    {
+        const long long tile_bytes = (long long)BN * (((long long)K + BK - 1) / BK * BK);
+        long long per = (32ll << 20) / tile_bytes;
+        if (per < 1) per = 1;
+        g.panel = per >= g.num_n_tiles ? g.num_n_tiles : (int)per;
+    }
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
