@@ -30,7 +30,8 @@ int a4c_launch_dense_tc(const void* A, long long lda, const void* Wt, long long 
                         void* Y, long long ldy, long long M, int K, int N, int shift, int rounding, int relu,
                         int out_dtype, int a_unsigned, int cta_pair, int* status_word, cudaStream_t stream);
 void a4c_dense_tc_set_resident_w(int on);
-void a4c_dense_tc_set_panel_mib(int mib);   // weights per column panel of the streaming tile order; 0 = a single panel
+void a4c_dense_tc_set_panel_mib(int mib);
+long long a4c_dense_tc_panel_bytes();   // weights per column panel of the tile order; 0 = one panel
 // 0 if the tensor-core path can take this problem, else an A4C_ERR_* code saying why not.
 int a4c_dense_tc_supported(const void* A, long long lda, const void* Wt, long long ldw, const void* Y,
                            long long ldy, long long M, int K, int N, int out_dtype);

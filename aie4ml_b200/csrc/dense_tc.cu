@@ -466,6 +466,7 @@ cudaError_t launch_mode(const CUtensorMap& ma, const CUtensorMap& mb, const CUte
 
 void a4c_dense_tc_set_resident_w(int mode) { g_dense_resident_w = mode < 0 ? 0 : (mode > 2 ? 2 : mode); }
 void a4c_dense_tc_set_panel_mib(int mib) { g_dense_panel_bytes = (long long)mib << 20; }
+long long a4c_dense_tc_panel_bytes() { return g_dense_panel_bytes; }
 
 int a4c_dense_tc_supported(const void* A, long long lda, const void* Wt, long long ldw, const void* Y,
                            long long ldy, long long M, int K, int N, int out_dtype) {

@@ -346,9 +346,10 @@ int a4c_launch_dense_tc2(const void* A, long long lda, const void* Wt, long long
     g.status = status_word;
     {
         const long long tile_bytes = (long long)BN * (((long long)K + BK - 1) / BK * BK);
-        long long per = (32ll << 20) / tile_bytes;
+        const long long panel_bytes = a4c_dense_tc_panel_bytes();   // A4C_OPT_DENSE_PANEL_MIB, default 32 MiB
+        long long per = panel_bytes / tile_bytes;
         if (per < 1) per = 1;
-        g.panel = per >= g.num_n_tiles ? g.num_n_tiles : (int)per;
+        g.panel = panel_bytes <= 0 || per >= g.num_n_tiles ? g.num_n_tiles : (int)per;
     }
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);

@@ -710,8 +710,11 @@ def test_dense_tcgen05_column_panels(panel_mib):
     assert L.a4c_set_option(a4c.OPT_DENSE_PANEL_MIB, panel_mib) == 0
     try:
         a, w, bias = _rand_dense(500 + panel_mib, 3000, 1024, 2304)
+        want = oracle.dense(a, w, bias, shift=10, tok='positive_inf', relu=True)
         got = G.dense(a, w, bias, shift=10, tok='positive_inf', relu=True, algo=TC)
-        np.testing.assert_array_equal(got, oracle.dense(a, w, bias, shift=10, tok='positive_inf', relu=True))
+        np.testing.assert_array_equal(got, want)
+        # the CTA-pair kernel walks its 256 x 256 tiles in the same panels
+        np.testing.assert_array_equal(G.dense(a, w, bias, shift=10, tok='positive_inf', relu=True, algo=TC2), want)
         a, w, _ = _rand_dense(600 + panel_mib, 700, 2048, 1300)
         got = G.dense(a, w, None, shift=11, tok='conv_even', relu=False, algo=TC)
         np.testing.assert_array_equal(got, oracle.dense(a, w, None, shift=11, tok='conv_even', relu=False))
