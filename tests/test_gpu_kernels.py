@@ -287,7 +287,7 @@ def test_add_then_layer_norm_in_one_pass(cols, tok, rowop_path):
         np.testing.assert_array_equal(got, want)
 
 
-@pytest.mark.parametrize('M,K', [(1, 16), (129, 256), (300, 96), (5000, 256), (2049, 1024), (40000, 384)])
+@pytest.mark.parametrize('M,K', [(1, 16), (129, 256), (300, 96), (257, 100), (5000, 256), (2049, 1024), (777, 1100), (40000, 384)])
 @pytest.mark.parametrize('tok', ['positive_inf', 'conv_even', 'floor', 'ceil', 'negative_inf'])
 def test_dense_add_layer_norm_single_kernel(M, K, tok):
     """Dense -> residual Add -> LayerNorm in one kernel (256 features) against the oracle's three steps: both operand
