@@ -364,6 +364,7 @@ struct SmFastArgs {
     long long rows; int cols;
     int mode, B, S, Dmax, inv_shift, use_clb, exp_kq;
     int stages;
+    uint32_t lut_row_pitch;   // 128: bytes per row of the score table
     RowGeom geom;
     int* status;
 };
@@ -380,15 +381,16 @@ __device__ __forceinline__ int exp_score16(int d, int kq) {
 }
 
 // score(d) * 2^-64 from the per-lane table: byte K of dw selects the table row (128 bytes per row, one float
-// per lane -> no bank conflicts).  lut_lane = table base + lane * 4 (shared address).
+// per lane -> no bank conflicts).  lut_lane = table base + lane * 4 (shared address).  One byte permute extracts the
+// index and one integer multiply-add forms the address: the multiply-add runs on the FMA pipe, which has room, while
+// shift + mask + add were three instructions on the integer pipe, the busiest unit of this kernel.  `row_pitch` is the
+// table's row pitch (128) passed as a run-time value so that the multiply is not strength-reduced back to the integer pipe.
 template <int K>
-__device__ __forceinline__ float lut_at(uint32_t lut_lane, uint32_t dw) {
-    uint32_t sh;
-    if (K == 0) sh = dw << 7;
-    else if (K == 1) sh = dw >> 1;
-    else if (K == 2) sh = dw >> 9;
-    else sh = dw >> 17;
-    return lds32f((sh & 0x7F80u) + lut_lane);
+__device__ __forceinline__ float lut_at(uint32_t lut_lane, uint32_t dw, uint32_t row_pitch) {
+    const uint32_t idx = prmt(dw, 0, 0x4440 + K);   // byte K, zero-extended
+    uint32_t addr;
+    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(addr) : "r"(idx), "r"(row_pitch), "r"(lut_lane));
+    return lds32f(addr);
 }
 
 template <int NCH, bool HAS_ADD, bool CLB>
@@ -493,10 +495,10 @@ __global__ void __launch_bounds__(kThreads) softmax_fast_kernel(SmFastArgs a) {
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
                 const uint32_t dw = m4 - w4[w];  // per byte: max - x, no borrows
-                e[j][w * 4 + 0] = lut_at<0>(lut_lane, dw);
-                e[j][w * 4 + 1] = lut_at<1>(lut_lane, dw);
-                e[j][w * 4 + 2] = lut_at<2>(lut_lane, dw);
-                e[j][w * 4 + 3] = lut_at<3>(lut_lane, dw);
+                e[j][w * 4 + 0] = lut_at<0>(lut_lane, dw, a.lut_row_pitch);
+                e[j][w * 4 + 1] = lut_at<1>(lut_lane, dw, a.lut_row_pitch);
+                e[j][w * 4 + 2] = lut_at<2>(lut_lane, dw, a.lut_row_pitch);
+                e[j][w * 4 + 3] = lut_at<3>(lut_lane, dw, a.lut_row_pitch);
             }
             if (row_ok && (j * G + gl) < a.geom.nchunks) {
 #pragma unroll
@@ -675,6 +677,7 @@ int a4c_launch_softmax_fast(const int8_t* x, long long ldx, const void* addend, 
     a.x = x; a.ldx = ldx; a.addend = (const uint8_t*)addend; a.ldadd = ldadd; a.out = (uint8_t*)out; a.ldo = ldo;
     a.rows = rows; a.cols = cols; a.mode = mode; a.B = B; a.S = S; a.Dmax = Dmax; a.inv_shift = inv_shift;
     a.use_clb = use_clb; a.exp_kq = exp_kq; a.status = status;
+    a.lut_row_pitch = 128u;
     // four chunks per lane keep 64 scores in registers: worth it only with the fused Add on long rows
     a.geom = make_geom(cols, (addend && cols >= 512) ? 4 : 2, ldx == cols && (!addend || ldadd == cols));
     const int nch = (a.geom.nchunks + a.geom.G - 1) / a.geom.G;
