@@ -365,6 +365,7 @@ struct SmFastArgs {
     int mode, B, S, Dmax, inv_shift, use_clb, exp_kq;
     int stages;
     uint32_t lut_row_pitch;   // 128: bytes per row of the score table
+    uint32_t two16, two8;     // 65536 and 256 as run-time values (multipliers of the lane-forming multiply-adds)
     RowGeom geom;
     int* status;
 };
@@ -542,14 +543,19 @@ __global__ void __launch_bounds__(kThreads) softmax_fast_kernel(SmFastArgs a) {
                 int o2 = __float_as_int(__fmaf_rd(e[j][w * 4 + 2], invs, 0.0f));
                 int o3 = __float_as_int(__fmaf_rd(e[j][w * 4 + 3], invs, 0.0f));
                 if (CLB) { o0 = min(o0, 255); o1 = min(o1, 255); o2 = min(o2, 255); o3 = min(o3, 255); }
-                uint32_t p01 = prmt((uint32_t)o0, (uint32_t)o1, 0x5410);
-                uint32_t p23 = prmt((uint32_t)o2, (uint32_t)o3, 0x5410);
                 if (HAS_ADD) {
-                    // fused saturating uint8 Add: zero-extended addend pairs, packed add + min(., 255)
-                    p01 = __viaddmin_u16x2(p01, prmt(aw[w], 0, 0x4140), 0x00FF00FFu);
-                    p23 = __viaddmin_u16x2(p23, prmt(aw[w], 0, 0x4342), 0x00FF00FFu);
+                    // fused saturating uint8 Add on 16-bit lanes, values 0 / 2 and 1 / 3 paired: the lanes are formed and
+                    // merged by integer multiply-adds (FMA pipe; the multipliers 2^16 and 2^8 come in as run-time values
+                    // so that they stay multiplies), the addend bytes by one mask and one permute, then packed add + min(., 255)
+                    uint32_t p02, p13;
+                    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(p02) : "r"((uint32_t)o2), "r"(a.two16), "r"((uint32_t)o0));
+                    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(p13) : "r"((uint32_t)o3), "r"(a.two16), "r"((uint32_t)o1));
+                    p02 = __viaddmin_u16x2(p02, aw[w] & 0x00FF00FFu, 0x00FF00FFu);
+                    p13 = __viaddmin_u16x2(p13, prmt(aw[w], 0, 0x4341), 0x00FF00FFu);
+                    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(ow[w]) : "r"(p13), "r"(a.two8), "r"(p02));
+                } else {
+                    ow[w] = prmt(prmt((uint32_t)o0, (uint32_t)o1, 0x5410), prmt((uint32_t)o2, (uint32_t)o3, 0x5410), 0x6420);
                 }
-                ow[w] = prmt(p01, p23, 0x6420);
             }
             stg16(orow + j * G * 16, make_uint4(ow[0], ow[1], ow[2], ow[3]));
         }
@@ -677,7 +683,7 @@ int a4c_launch_softmax_fast(const int8_t* x, long long ldx, const void* addend, 
     a.x = x; a.ldx = ldx; a.addend = (const uint8_t*)addend; a.ldadd = ldadd; a.out = (uint8_t*)out; a.ldo = ldo;
     a.rows = rows; a.cols = cols; a.mode = mode; a.B = B; a.S = S; a.Dmax = Dmax; a.inv_shift = inv_shift;
     a.use_clb = use_clb; a.exp_kq = exp_kq; a.status = status;
-    a.lut_row_pitch = 128u;
+    a.lut_row_pitch = 128u; a.two16 = 65536u; a.two8 = 256u;
     // four chunks per lane keep 64 scores in registers: worth it only with the fused Add on long rows
     a.geom = make_geom(cols, (addend && cols >= 512) ? 4 : 2, ldx == cols && (!addend || ldadd == cols));
     const int nch = (a.geom.nchunks + a.geom.G - 1) / a.geom.G;
